@@ -1,0 +1,144 @@
+#pragma once
+// Shared host/device helpers for the sm_100a kernels of this backend.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+
+#include "aicf/backends/cuda/registry/attr_blob.hpp"
+#include "aicf/backends/cuda/registry/kernel_variant.hpp"
+#include "aicf/backends/cuda/registry/status.hpp"
+#include "aicf/backends/cuda/registry/tensor_desc.hpp"
+
+namespace aicf::cuda {
+
+// ------------------------------------------------------------------ host helpers
+inline Status status_of(cudaError_t e) { return e == cudaSuccess ? Status::Ok : Status::Internal; }
+inline Status launch_status() { return status_of(cudaGetLastError()); }
+
+inline const AttrBlob& blob_of(const void* attr) {
+  static const AttrBlob kEmpty{};
+  return attr ? *static_cast<const AttrBlob*>(attr) : kEmpty;
+}
+
+// Copies `n` payload bytes into `dst` when the blob carries schema `want` (or schema 0 when
+// `allow_zero_schema`) and at least `n` bytes. Returns false otherwise and leaves dst untouched.
+inline bool read_attr_payload(const void* attr, uint32_t want, bool allow_zero_schema, void* dst, size_t n) {
+  const AttrBlob& b = blob_of(attr);
+  const bool schema_ok = (b.schema_id == want) || (allow_zero_schema && b.schema_id == 0);
+  if (!schema_ok || !b.data || b.bytes < n) return false;
+  std::memcpy(dst, b.data, n);
+  return true;
+}
+
+inline bool same_shape(const TensorDesc& a, const TensorDesc& b) {
+  if (a.rank() != b.rank()) return false;
+  for (int i = 0; i < a.rank(); ++i)
+    if (a.shape[i] != b.shape[i]) return false;
+  return true;
+}
+
+// Product of the extents; false when a dimension is non-positive or rank < min_rank.
+inline bool positive_numel(const TensorDesc& t, int min_rank, int64_t* out) {
+  if (t.rank() < min_rank || t.rank() > kMaxRank) return false;
+  int64_t n = 1;
+  for (int i = 0; i < t.rank(); ++i) {
+    if (t.shape[i] <= 0) return false;
+    n *= t.shape[i];
+  }
+  *out = n;
+  return true;
+}
+
+// [..., N] viewed as [M, N]; needs rank >= 2 and positive extents.
+inline bool rows_cols_lastdim(const TensorDesc& t, int64_t* M, int64_t* N) {
+  const int r = t.rank();
+  if (r < 2 || r > kMaxRank) return false;
+  int64_t m = 1;
+  for (int i = 0; i < r - 1; ++i) {
+    if (t.shape[i] <= 0) return false;
+    m *= t.shape[i];
+  }
+  if (t.shape[r - 1] <= 0) return false;
+  *M = m;
+  *N = t.shape[r - 1];
+  return true;
+}
+
+inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+// Number of SMs of the current device (148 on B200); cached per device.
+inline int sm_count() {
+  static int cached[16] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// Grid for a grid-stride streaming kernel: whole multiples of the SM count, no more blocks than
+// there is work, at least one.
+inline int streaming_grid(int64_t work_items, int items_per_block, int blocks_per_sm) {
+  int64_t need = (work_items + items_per_block - 1) / items_per_block;
+  if (need < 1) need = 1;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * blocks_per_sm;
+  return static_cast<int>(need < cap ? need : cap);
+}
+
+// ------------------------------------------------------------------ device helpers
+#ifdef __CUDACC__
+
+template <typename T> struct Cvt;
+template <> struct Cvt<float> {
+  __device__ __forceinline__ static float to_f(float v) { return v; }
+  __device__ __forceinline__ static float from_f(float v) { return v; }
+};
+template <> struct Cvt<__half> {
+  __device__ __forceinline__ static float to_f(__half v) { return __half2float(v); }
+  __device__ __forceinline__ static __half from_f(float v) { return __float2half_rn(v); }
+};
+template <> struct Cvt<__nv_bfloat16> {
+  __device__ __forceinline__ static float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  __device__ __forceinline__ static __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+
+// 16-byte packet of T with float unpack/pack.
+template <typename T> struct alignas(16) Pack16 {
+  static constexpr int kN = 16 / sizeof(T);
+  T v[kN];
+};
+
+// Streaming (evict-first) 16-byte global accesses: data touched once should not displace L2 lines.
+template <typename T>
+__device__ __forceinline__ Pack16<T> ld_stream(const Pack16<T>* p) {
+  const int4 raw = __ldcs(reinterpret_cast<const int4*>(p));
+  Pack16<T> out;
+  *reinterpret_cast<int4*>(&out) = raw;
+  return out;
+}
+template <typename T>
+__device__ __forceinline__ void st_stream(Pack16<T>* p, const Pack16<T>& v) {
+  __stcs(reinterpret_cast<int4*>(p), *reinterpret_cast<const int4*>(&v));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace aicf::cuda

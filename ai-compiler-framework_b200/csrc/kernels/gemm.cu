@@ -1,0 +1,107 @@
+// Kernel variants of OpKind::Gemm and OpKind::GemmEpilogue.
+//
+// Each variant validates its contract and then routes to one of two sm_100a kernels:
+//   gemm_tcgen05_run  16-bit operands whose rows are 16-byte aligned (TMA + tcgen05/TMEM)
+//   gemm_simt_run     fp32 operands (exact fp32), or shapes the TMA path cannot express
+// The reference ids keep the reference's dtype contracts
+// (ops/gemm/launcher.cu:272-287,330-361; ops/gemm_epilogue/launcher.cu:333-349,399-431).
+#include "gemm_common.cuh"
+
+namespace aicf::cuda {
+
+namespace {
+
+enum class BiasRule { None, SameAsInput, F32OrInput };
+
+struct GemmContract {
+  DType in, out;
+  BiasRule bias;
+  bool c_rowmajor_contig;  // the reference's tensor-core ids insist on a packed row-major C
+};
+
+bool is_packed_rowmajor(const TensorDesc& t) { return t.rank() == 2 && t.stride[1] == 1 && t.stride[0] == t.shape[1]; }
+
+bool check(const GemmContract& c, const TensorDesc* in, int ni, const TensorDesc* out, int no, const void* attr,
+           GemmProblem* prob) {
+  const bool with_bias = c.bias != BiasRule::None;
+  bool ta, tb, relu = false;
+  if (with_bias) {
+    read_gemm_epilogue_attr(attr, &ta, &tb, &relu);
+  } else {
+    read_gemm_attr(attr, &ta, &tb);
+  }
+  GemmProblem p;
+  if (!build_problem(in, ni, out, no, with_bias, ta, tb, relu, &p)) return false;
+  if (in[0].dtype != c.in || in[1].dtype != c.in || out[0].dtype != c.out) return false;
+  if (with_bias) {
+    const DType bd = in[2].dtype;
+    if (c.bias == BiasRule::SameAsInput && bd != c.in) return false;
+    if (c.bias == BiasRule::F32OrInput && bd != DType::kF32 && bd != c.in) return false;
+  }
+  if (c.c_rowmajor_contig && !is_packed_rowmajor(out[0])) return false;
+  if (prob) *prob = p;
+  return true;
+}
+
+Status run(const GemmProblem& p, cudaStream_t stream) {
+  if (gemm_tcgen05_eligible(p)) return gemm_tcgen05_run(p, stream);
+  return gemm_simt_run(p, stream);
+}
+
+size_t no_workspace(const TensorDesc*, int, const void*) { return 0; }
+
+template <int kId> struct Contracts;
+#define AICF_GEMM_CONTRACT(ID, IN, OUT, BIAS, PACKED)                                                              \
+  template <> struct Contracts<ID> {                                                                              \
+    static constexpr GemmContract value{IN, OUT, BIAS, PACKED};                                                   \
+  };
+AICF_GEMM_CONTRACT(0, DType::kF32, DType::kF32, BiasRule::None, false)
+AICF_GEMM_CONTRACT(1, DType::kF16, DType::kF16, BiasRule::None, true)
+AICF_GEMM_CONTRACT(2, DType::kBF16, DType::kBF16, BiasRule::None, false)
+AICF_GEMM_CONTRACT(3, DType::kBF16, DType::kF32, BiasRule::None, false)
+AICF_GEMM_CONTRACT(4, DType::kF16, DType::kF32, BiasRule::None, false)
+AICF_GEMM_CONTRACT(5, DType::kF16, DType::kF16, BiasRule::None, false)
+AICF_GEMM_CONTRACT(10, DType::kF32, DType::kF32, BiasRule::SameAsInput, false)
+AICF_GEMM_CONTRACT(11, DType::kF16, DType::kF16, BiasRule::SameAsInput, true)
+AICF_GEMM_CONTRACT(12, DType::kBF16, DType::kBF16, BiasRule::F32OrInput, false)
+AICF_GEMM_CONTRACT(13, DType::kBF16, DType::kF32, BiasRule::F32OrInput, false)
+AICF_GEMM_CONTRACT(14, DType::kF16, DType::kF16, BiasRule::F32OrInput, false)
+
+template <int kId>
+bool supported(const TensorDesc* in, int ni, const TensorDesc* out, int no, const void* attr) {
+  return check(Contracts<kId>::value, in, ni, out, no, attr, nullptr);
+}
+template <int kId>
+Status launch(const TensorDesc* in, int ni, TensorDesc* out, int no, const void* attr, void*, size_t,
+              cudaStream_t stream) {
+  GemmProblem p;
+  if (!check(Contracts<kId>::value, in, ni, out, no, attr, &p)) return Status::InvalidArgument;
+  return run(p, stream);
+}
+template <int kId>
+KernelVariant variant(const char* name) {
+  KernelVariant v{};
+  v.name = name;
+  v.flags = kKV_CaptureSafe;
+  v.expected_attr_schema_id = 0;  // schema 0 and the op's own schema are both parsed
+  v.launch = launch<kId>;
+  v.supported = supported<kId>;
+  v.query_workspace = no_workspace;
+  return v;
+}
+
+}  // namespace
+
+KernelVariant make_gemm_f32_naive_variant() { return variant<0>("gemm_f32_simt_sm100"); }
+KernelVariant make_gemm_f16_tc_wmma_out_f16_variant() { return variant<1>("gemm_f16_tcgen05_packed_c"); }
+KernelVariant make_gemm_bf16_tcgen05_out_bf16_variant() { return variant<2>("gemm_bf16_tcgen05_out_bf16"); }
+KernelVariant make_gemm_bf16_tcgen05_out_f32_variant() { return variant<3>("gemm_bf16_tcgen05_out_f32"); }
+KernelVariant make_gemm_f16_tcgen05_out_f32_variant() { return variant<4>("gemm_f16_tcgen05_out_f32"); }
+KernelVariant make_gemm_f16_tcgen05_out_f16_variant() { return variant<5>("gemm_f16_tcgen05_out_f16"); }
+KernelVariant make_gemm_bias_relu_f32_naive_variant() { return variant<10>("gemm_bias_relu_f32_simt_sm100"); }
+KernelVariant make_gemm_bias_relu_f16_tc_wmma_out_f16_variant() { return variant<11>("gemm_bias_relu_f16_tcgen05_packed_c"); }
+KernelVariant make_gemm_bias_relu_bf16_tcgen05_out_bf16_variant() { return variant<12>("gemm_bias_relu_bf16_tcgen05_out_bf16"); }
+KernelVariant make_gemm_bias_relu_bf16_tcgen05_out_f32_variant() { return variant<13>("gemm_bias_relu_bf16_tcgen05_out_f32"); }
+KernelVariant make_gemm_bias_relu_f16_tcgen05_out_f16_variant() { return variant<14>("gemm_bias_relu_f16_tcgen05_out_f16"); }
+
+}  // namespace aicf::cuda

@@ -1,0 +1,496 @@
+// Dense GEMM for Blackwell (sm_100a): C = [relu](op(A) * op(B) [+ bias]) with 16-bit operands
+// (bf16 or f16), fp32 accumulation in tensor memory, output bf16 / f16 / f32.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor 2-D tile loads (no multicast) into a 4-stage
+//               ring of 128B-swizzled shared-memory tiles, completion on mbarriers
+//   warp 1      owns tensor memory (tcgen05.alloc / dealloc of all 512 columns) and issues
+//               tcgen05.mma.cta_group::1.kind::f16 from one elected lane; tcgen05.commit releases
+//               smem stages and publishes finished accumulators
+//   warps 2-5   epilogue: tcgen05.ld of the 128x256 fp32 accumulator (each warp its own 32-lane
+//               TMEM sub-partition), + bias, ReLU, convert, 16-byte global stores
+// Two accumulator buffers (2 x 256 TMEM columns) let the epilogue of tile i overlap the main loop
+// of tile i+1. All four transpose combinations are handled without moving data: an operand whose
+// contiguous dimension is M/N instead of K is loaded as 64x64 boxes and described to the MMA as
+// "MN-major" through the shared-memory and instruction descriptors.
+//
+// Every wait is bounded: after ~2 s without progress a role raises the CTA's abort flag, records a
+// code in the device status word, everybody leaves their loops, tensor memory is released and the
+// kernel returns normally. The host reads the word through gemm_tcgen05_status().
+#include <cuda.h>
+
+#include "gemm_common.cuh"
+
+namespace aicf::cuda {
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kTileN = 256;
+constexpr int kTileK = 64;   // 64 x 2 bytes = one 128-byte swizzle row
+constexpr int kStages = 4;
+constexpr int kUmmaK = 16;
+constexpr int kAStageBytes = kTileM * kTileK * 2;   // 16 KiB
+constexpr int kBStageBytes = kTileN * kTileK * 2;   // 32 KiB
+constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+constexpr int kChunkBytes = 64 * kTileK * 2;        // one 64x64 box = 8 KiB (MN-major operands)
+constexpr int kAccBufs = 2;
+constexpr int kTmemCols = 512;
+constexpr int kThreads = 192;
+constexpr int kGroupM = 16;   // tile rasterisation: 16 row-tiles share their column tiles in L2
+constexpr unsigned long long kWaitBudgetNs = 2000000000ull;
+
+constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + 256 /*barriers etc.*/;
+
+__device__ int g_gemm_status = 0;  // 0 ok; otherwise (role << 8) | reason of the first CTA that gave up
+
+struct GemmParams {
+  void* C;
+  const void* bias;
+  int64_t ldc;          // elements
+  int64_t bias_stride;  // elements
+  int M, N, K;
+  int c_dtype;          // DType value of C
+  int bias_dtype;       // DType value of bias (0 = none)
+  int relu;
+  int a_mn_major, b_mn_major;
+  uint32_t idesc;
+  int c_vec_ok;         // C rows allow 16-byte stores
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait. Returns false when the CTA is aborting (flag raised here on timeout or elsewhere).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int who) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 255u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > kWaitBudgetNs) {
+        *abort_flag = 1;
+        atomicCAS(&g_gemm_status, 0, (who << 8) | 1);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+//   K-major : rows of 128 B (64 elements of K); SBO = 1024 B between 8-row groups; LBO unused (1)
+//   MN-major: 64-element MN chunks of 64 k-rows x 128 B; LBO = 8192 B between chunks,
+//             SBO = 1024 B between 8-k groups
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, int mn_major) {
+  const uint64_t lbo = mn_major ? (kChunkBytes >> 4) : 1;
+  const uint64_t sbo = 1024 >> 4;
+  return static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu) | (lbo << 16) | (sbo << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int* tm, int* tn) {
+  const int per_group = kGroupM * tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * kGroupM;
+  const int rows = min(kGroupM, tiles_m - first_m);
+  const int in_group = tile - group * per_group;
+  *tm = first_m + in_group % rows;
+  *tn = in_group / rows;
+}
+
+__device__ __forceinline__ float bias_at(const GemmParams& p, int col) {
+  if (p.bias_dtype == static_cast<int>(DType::kF32)) return __ldg(static_cast<const float*>(p.bias) + col * p.bias_stride);
+  if (p.bias_dtype == static_cast<int>(DType::kBF16))
+    return __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col * p.bias_stride]);
+  return __half2float(static_cast<const __half*>(p.bias)[col * p.bias_stride]);
+}
+
+// ------------------------------------------------------------------ kernel
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // 128B swizzle atoms repeat every 1024 B
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const uint32_t bars = base + kStages * kStageBytes;
+  // barrier map (8 B each): full[0..3], empty[0..3], acc_full[0..1], acc_empty[0..1]
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * kStages, bar_acc_full = bars + 16 * kStages,
+                 bar_acc_empty = bars + 16 * kStages + 8 * kAccBufs;
+  uint8_t* misc = base_ptr + kStages * kStageBytes + 16 * kStages + 16 * kAccBufs;
+  volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(misc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + kTileN - 1) / kTileN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_blocks = (p.K + kTileK - 1) / kTileK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < kAccBufs; ++b) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_empty + 8 * b, 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+        const int m0 = tm * kTileM, n0 = tn * kTileN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1)) { alive = false; break; }
+          const uint32_t full = bar_full + 8 * stage;
+          const uint32_t sa = base + stage * kStageBytes, sb = sa + kAStageBytes;
+          const int k0 = kb * kTileK;
+          mbar_expect_tx(full, kStageBytes);
+          if (p.a_mn_major) {
+            tma_load_2d(sa, &tmap_a, m0, k0, full);
+            tma_load_2d(sa + kChunkBytes, &tmap_a, m0 + 64, k0, full);
+          } else {
+            tma_load_2d(sa, &tmap_a, k0, m0, full);
+          }
+          if (p.b_mn_major) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tma_load_2d(sb + j * kChunkBytes, &tmap_b, n0 + 64 * j, k0, full);
+          } else {
+            tma_load_2d(sb, &tmap_b, k0, n0, full);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool alive = true;
+      const uint32_t a_step = p.a_mn_major ? (2 * 1024) >> 4 : (kUmmaK * 2) >> 4;  // descriptor units of 16 B
+      const uint32_t b_step = p.b_mn_major ? (2 * 1024) >> 4 : (kUmmaK * 2) >> 4;
+      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+        if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, 2)) { alive = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * kTileN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3)) { alive = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + stage * kStageBytes, sb = sa + kAStageBytes;
+          const uint64_t adesc = make_smem_desc(sa, p.a_mn_major);
+          const uint64_t bdesc = make_smem_desc(sb, p.b_mn_major);
+#pragma unroll
+          for (int k = 0; k < kTileK / kUmmaK; ++k)
+            umma_f16(tmem_d, adesc + k * a_step, bdesc + k * b_step, p.idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit(bar_empty + 8 * stage);  // stage is free once these MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!alive) break;
+        umma_commit(bar_acc_full + 8 * acc);   // accumulator complete
+        if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int sub = warp & 3;  // TMEM sub-partition this warp may read: lanes [32*sub, 32*sub+32)
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+      const int row = tm * kTileM + sub * 32 + lane;
+      const int n0 = tn * kTileN;
+      if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, 4)) { alive = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * kTileN;
+#pragma unroll 1
+      for (int c = 0; c < kTileN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (p.bias_dtype != 0) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) v[j] += bias_at(p, col0 + j);
+        }
+        if (p.relu) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
+        }
+        if (row < p.M) {
+          const int64_t off = static_cast<int64_t>(row) * p.ldc + col0;
+          const bool full_chunk = (col0 + 32 <= p.N) && p.c_vec_ok;
+          if (p.c_dtype == static_cast<int>(DType::kF32)) {
+            float* dst = static_cast<float*>(p.C) + off;
+            if (full_chunk) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                reinterpret_cast<float4*>(dst)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = v[j];
+            }
+          } else {
+            uint32_t packed[16];
+            if (p.c_dtype == static_cast<int>(DType::kBF16)) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+                packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+              }
+            }
+            uint16_t* dst = static_cast<uint16_t*>(p.C) + off;
+            if (full_chunk) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                reinterpret_cast<uint4*>(dst)[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j)
+                dst[j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xFFFFu));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+      if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  if (*abort_flag) {
+    // error path only: give loads that may still be in flight time to land before smem is released
+    for (int i = 0; i < 64; ++i) __nanosleep(16384);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q{};
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      sym = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+// Operand with `inner` contiguous elements per line, `outer` lines `ld` elements apart.
+bool encode_operand(CUtensorMap* map, const void* base, DType dt, int64_t inner, int64_t outer, int64_t ld,
+                    uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  // a single line has no meaningful pitch; any 16-byte multiple that covers it satisfies the encoder
+  const cuuint64_t pitch = outer == 1 ? ((static_cast<cuuint64_t>(inner) * 2 + 15) / 16) * 16 : static_cast<cuuint64_t>(ld) * 2;
+  const cuuint64_t strides[1] = {pitch};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType t = dt == DType::kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return fn(map, t, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// 0 = K-major, 1 = MN-major, -1 = neither stride is 1 / alignment rules not met
+int operand_major(const void* data, int64_t mn_stride, int64_t k_stride, int64_t mn, int64_t k) {
+  if (!aligned_to(data, 16)) return -1;
+  if (k_stride == 1 && (mn == 1 || (mn_stride * 2) % 16 == 0) && mn_stride >= k) return 0;
+  if (mn_stride == 1 && (k == 1 || (k_stride * 2) % 16 == 0) && k_stride >= mn) return 1;
+  return -1;
+}
+
+bool is16(DType t) { return t == DType::kF16 || t == DType::kBF16; }
+
+}  // namespace
+
+bool gemm_tcgen05_eligible(const GemmProblem& p) {
+  if (!is16(p.A.dtype) || p.A.dtype != p.B.dtype) return false;
+  if (p.C.dtype != p.A.dtype && p.C.dtype != DType::kF32) return false;
+  if (p.bias && p.bias_dtype != DType::kF32 && p.bias_dtype != p.A.dtype) return false;
+  if (p.C.cs != 1) return false;
+  if (p.M > 0x7fffff00 || p.N > 0x7fffff00 || p.K > 0x7fffff00) return false;
+  // A is [M,K]: rs walks M, cs walks K.  B is [K,N]: rs walks K, cs walks N.
+  if (operand_major(p.A.data, p.A.rs, p.A.cs, p.M, p.K) < 0) return false;
+  if (operand_major(p.B.data, p.B.cs, p.B.rs, p.N, p.K) < 0) return false;
+  return encode_fn() != nullptr;
+}
+
+Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream) {
+  if (!gemm_tcgen05_eligible(p)) return Status::NotImplemented;
+  const int a_major = operand_major(p.A.data, p.A.rs, p.A.cs, p.M, p.K);
+  const int b_major = operand_major(p.B.data, p.B.cs, p.B.rs, p.N, p.K);
+
+  CUtensorMap ta, tb;
+  bool ok_maps = a_major == 0 ? encode_operand(&ta, p.A.data, p.A.dtype, p.K, p.M, p.A.rs, kTileK, kTileM)
+                              : encode_operand(&ta, p.A.data, p.A.dtype, p.M, p.K, p.A.cs, 64, kTileK);
+  ok_maps = ok_maps && (b_major == 0 ? encode_operand(&tb, p.B.data, p.B.dtype, p.K, p.N, p.B.cs, kTileK, kTileN)
+                                     : encode_operand(&tb, p.B.data, p.B.dtype, p.N, p.K, p.B.rs, 64, kTileK));
+  if (!ok_maps) return Status::Internal;
+
+  GemmParams g{};
+  g.C = const_cast<void*>(p.C.data);
+  g.bias = p.bias;
+  g.ldc = p.C.rs;
+  g.bias_stride = p.bias_stride;
+  g.M = static_cast<int>(p.M);
+  g.N = static_cast<int>(p.N);
+  g.K = static_cast<int>(p.K);
+  g.c_dtype = static_cast<int>(p.C.dtype);
+  g.bias_dtype = p.bias ? static_cast<int>(p.bias_dtype) : 0;
+  g.relu = p.relu ? 1 : 0;
+  g.a_mn_major = a_major;
+  g.b_mn_major = b_major;
+  const uint32_t fmt = p.A.dtype == DType::kBF16 ? 1u : 0u;
+  // instruction descriptor: D=f32 (bits 4-5 = 1), A/B format (bits 7-9 / 10-12), A/B major (bits 15/16),
+  // N>>3 (bits 17-22), M>>4 (bits 24-28)
+  g.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(a_major) << 15) |
+            (static_cast<uint32_t>(b_major) << 16) | (static_cast<uint32_t>(kTileN >> 3) << 17) |
+            (static_cast<uint32_t>(kTileM >> 4) << 24);
+  const int c_elem = dtype_size_bytes(p.C.dtype);
+  g.c_vec_ok = aligned_to(p.C.data, 16) && ((p.C.rs * c_elem) % 16 == 0);
+
+  static bool attr_set[16] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 16 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kSmemBytes)) != cudaSuccess) {
+      cudaGetLastError();
+      return Status::Internal;
+    }
+    attr_set[dev] = true;
+  }
+  const int64_t tiles = ((p.M + kTileM - 1) / kTileM) * ((p.N + kTileN - 1) / kTileN);
+  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  cudaGetLastError();
+  gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, g);
+  return launch_status();
+}
+
+// Reads (and optionally clears) the device status word written by a GEMM that gave up waiting.
+// Synchronises the device: meant for tests and for a check after a step, not for the launch path.
+int gemm_tcgen05_status(bool clear) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (clear && v != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
+  }
+  return v;
+}
+
+}  // namespace aicf::cuda

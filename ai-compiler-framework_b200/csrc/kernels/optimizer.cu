@@ -1,0 +1,414 @@
+// Optimizer-state kernels: fused Adam (two contracts), device step counter, device
+// bias-correction scalars, SGD.
+//
+// Everything here is HBM-bound streaming work: 128-bit loads/stores with evict-first hints,
+// 64-bit indexing, a grid sized in whole multiples of the SM count and a grid-stride loop, so
+// one launch covers any size (the reference caps its grid at 65535 blocks of scalar accesses).
+#include "common.cuh"
+
+namespace aicf::cuda {
+
+namespace {
+
+struct AdamHyper {
+  float lr, beta1, beta2, eps;
+  float weight_decay;  // 0 = none
+  uint32_t decoupled;  // 0: L2 term folded into the gradient, 1: AdamW-style decay of the parameter
+};
+
+// 'ADAM' payload: <ffff> lr,beta1,beta2,eps, optionally followed by <fI> weight_decay, mode.
+// Missing / foreign / short payloads fall back to the defaults the reference uses
+// (ops/adam_step/launcher.cu:47-60).
+AdamHyper read_adam(const void* attr) {
+  AdamHyper h{1e-3f, 0.9f, 0.999f, 1e-8f, 0.0f, 0u};
+  const AttrBlob& b = blob_of(attr);
+  if (b.schema_id != schema::kAdam || !b.data || b.bytes < 16) return h;
+  std::memcpy(&h, b.data, 16);
+  if (b.bytes >= 24) {
+    std::memcpy(&h.weight_decay, static_cast<const uint8_t*>(b.data) + 16, 4);
+    std::memcpy(&h.decoupled, static_cast<const uint8_t*>(b.data) + 20, 4);
+  }
+  return h;
+}
+
+bool f32_contig_rank1p(const TensorDesc& d) { return d.dtype == DType::kF32 && d.contiguous && d.rank() >= 1; }
+bool f32_scalar0(const TensorDesc& d) { return d.dtype == DType::kF32 && d.rank() == 0 && d.contiguous; }
+bool same_ptr(const TensorDesc& a, const TensorDesc& b) { return a.data == b.data; }
+
+int64_t numel_raw(const TensorDesc& d) {
+  int64_t n = 1;
+  for (int i = 0; i < d.rank(); ++i) n *= d.shape[i];
+  return n;
+}
+
+// Aliasing rules of the reference (ops/adam_step/launcher.cu:98-128): each of P/M/V may be updated
+// in place; the gradient aliases nothing; no cross aliasing between the P, M and V groups.
+bool adam_alias_violation(const TensorDesc& P, const TensorDesc& G, const TensorDesc& M, const TensorDesc& V,
+                          const TensorDesc& Po, const TensorDesc& Mo, const TensorDesc& Vo) {
+  const TensorDesc* others[] = {&P, &M, &V, &Po, &Mo, &Vo};
+  for (const TensorDesc* o : others)
+    if (same_ptr(G, *o)) return true;
+  if (!same_ptr(Po, P) && (same_ptr(Po, M) || same_ptr(Po, V) || same_ptr(Po, Mo) || same_ptr(Po, Vo))) return true;
+  if (!same_ptr(Mo, M) && (same_ptr(Mo, P) || same_ptr(Mo, V) || same_ptr(Mo, Po) || same_ptr(Mo, Vo))) return true;
+  if (!same_ptr(Vo, V) && (same_ptr(Vo, P) || same_ptr(Vo, M) || same_ptr(Vo, Po) || same_ptr(Vo, Mo))) return true;
+  return same_ptr(M, V) || same_ptr(P, M) || same_ptr(P, V);
+}
+
+// ----------------------------------------------------------------------------------------------
+// One kernel template serves both contracts:
+//   kDivisorScalars = true : bias corrections are two device scalars used as divisors
+//                            (adam_step_f32_v0; reference kernel ops/adam_step/launcher.cu:257-293)
+//   kDivisorScalars = false: the int32 step counter is read and 1-beta^t formed in the kernel;
+//                            optional weight decay, optional bf16 copy of the new parameter.
+// ----------------------------------------------------------------------------------------------
+struct AdamArgs {
+  const float* p;
+  const float* g;
+  const float* m;
+  const float* v;
+  float* p_out;
+  float* m_out;
+  float* v_out;
+  __nv_bfloat16* p_bf16;  // may be null
+  const float* bc1;       // divisor scalars (v0 contract)
+  const float* bc2;
+  const int32_t* step;    // step counter (fused contract)
+  int64_t n;
+  int64_t nvec;           // number of leading 4-element packets handled with 128-bit accesses
+  AdamHyper h;
+};
+
+template <bool kDivisorScalars>
+__device__ __forceinline__ void adam_one(float p, float g, float m, float v, const AdamHyper& h, float d1,
+                                         float d2, float& p_new, float& m_new, float& v_new) {
+  if (!kDivisorScalars && h.weight_decay != 0.0f && h.decoupled == 0u) g = fmaf(h.weight_decay, p, g);
+  m_new = h.beta1 * m + (1.0f - h.beta1) * g;
+  v_new = h.beta2 * v + (1.0f - h.beta2) * (g * g);
+  const float m_hat = m_new / d1;
+  const float v_hat = v_new / d2;
+  const float denom = sqrtf(v_hat) + h.eps;
+  float base = p;
+  if (!kDivisorScalars && h.weight_decay != 0.0f && h.decoupled != 0u) base = p - h.lr * h.weight_decay * p;
+  p_new = base - h.lr * (m_hat / denom);
+}
+
+__device__ __forceinline__ void store_bf16x4(__nv_bfloat16* dst, int64_t packet, const Pack16<float>& f) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(f.v[0], f.v[1]);
+  const __nv_bfloat162 hi = __floats2bfloat162_rn(f.v[2], f.v[3]);
+  uint2 w;
+  w.x = *reinterpret_cast<const uint32_t*>(&lo);
+  w.y = *reinterpret_cast<const uint32_t*>(&hi);
+  reinterpret_cast<uint2*>(dst)[packet] = w;
+}
+
+template <bool kDivisorScalars, bool kBf16Copy>
+__global__ void __launch_bounds__(256) adam_kernel(AdamArgs a) {
+  float d1, d2;
+  if (kDivisorScalars) {
+    d1 = a.bc1[0];
+    d2 = a.bc2[0];
+  } else {
+    int t = a.step[0];
+    if (t < 1) t = 1;
+    d1 = 1.0f - powf(a.h.beta1, static_cast<float>(t));
+    d2 = 1.0f - powf(a.h.beta2, static_cast<float>(t));
+  }
+  using V4 = Pack16<float>;
+  const V4* P = reinterpret_cast<const V4*>(a.p);
+  const V4* G = reinterpret_cast<const V4*>(a.g);
+  const V4* M = reinterpret_cast<const V4*>(a.m);
+  const V4* V = reinterpret_cast<const V4*>(a.v);
+  V4* Po = reinterpret_cast<V4*>(a.p_out);
+  V4* Mo = reinterpret_cast<V4*>(a.m_out);
+  V4* Vo = reinterpret_cast<V4*>(a.v_out);
+
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+
+  // Two packets per stream per trip: 8 independent 16-byte loads in flight per thread.
+  int64_t i = tid;
+  for (; i + stride < a.nvec; i += 2 * stride) {
+    V4 p[2], g[2], m[2], v[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int64_t j = i + u * stride;
+      p[u] = ld_stream(P + j);
+      g[u] = ld_stream(G + j);
+      m[u] = ld_stream(M + j);
+      v[u] = ld_stream(V + j);
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int64_t j = i + u * stride;
+      V4 po, mo, vo;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        adam_one<kDivisorScalars>(p[u].v[e], g[u].v[e], m[u].v[e], v[u].v[e], a.h, d1, d2, po.v[e], mo.v[e], vo.v[e]);
+      st_stream(Mo + j, mo);
+      st_stream(Vo + j, vo);
+      st_stream(Po + j, po);
+      if (kBf16Copy) store_bf16x4(a.p_bf16, j, po);
+    }
+  }
+  for (; i < a.nvec; i += stride) {
+    const V4 p = ld_stream(P + i), g = ld_stream(G + i), m = ld_stream(M + i), v = ld_stream(V + i);
+    V4 po, mo, vo;
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      adam_one<kDivisorScalars>(p.v[e], g.v[e], m.v[e], v.v[e], a.h, d1, d2, po.v[e], mo.v[e], vo.v[e]);
+    st_stream(Mo + i, mo);
+    st_stream(Vo + i, vo);
+    st_stream(Po + i, po);
+    if (kBf16Copy) store_bf16x4(a.p_bf16, i, po);
+  }
+  // elements not covered by packets: the n % 4 tail, or everything when a buffer is not 16-byte aligned
+  for (int64_t k = (a.nvec << 2) + tid; k < a.n; k += stride) {
+    float po, mo, vo;
+    adam_one<kDivisorScalars>(a.p[k], a.g[k], a.m[k], a.v[k], a.h, d1, d2, po, mo, vo);
+    a.m_out[k] = mo;
+    a.v_out[k] = vo;
+    a.p_out[k] = po;
+    if (kBf16Copy) a.p_bf16[k] = __float2bfloat16_rn(po);
+  }
+}
+
+template <bool kDiv, bool kBf>
+Status launch_adam(AdamArgs a, cudaStream_t stream) {
+  if (a.n <= 0) return Status::Ok;
+  const void* ptrs[] = {a.p, a.g, a.m, a.v, a.p_out, a.m_out, a.v_out};
+  bool vec_ok = true;
+  for (const void* q : ptrs) vec_ok = vec_ok && aligned_to(q, 16);
+  if (kBf) vec_ok = vec_ok && aligned_to(a.p_bf16, 8);
+  a.nvec = vec_ok ? (a.n >> 2) : 0;
+  constexpr int kThreads = 256;
+  const int64_t items = vec_ok ? (a.nvec / 2 + 1) : a.n;
+  const int grid = streaming_grid(items, kThreads, 4);  // 64 regs x 256 threads: 4 blocks resident per SM
+  cudaGetLastError();
+  adam_kernel<kDiv, kBf><<<grid, kThreads, 0, stream>>>(a);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- adam_step_f32_v0 (reference contract)
+// inputs [P,G,M,V,BC1,BC2] -> outputs [Pout,Mout,Vout]; BC1/BC2 are rank-0 f32 divisors.
+bool adam_v0_check(const TensorDesc* in, int ni, const TensorDesc* out, int no) {
+  if (!in || !out || ni != 6 || no != 3) return false;
+  for (int i = 0; i < 4; ++i)
+    if (!f32_contig_rank1p(in[i])) return false;
+  for (int i = 0; i < 3; ++i)
+    if (!f32_contig_rank1p(out[i])) return false;
+  if (!f32_scalar0(in[4]) || !f32_scalar0(in[5])) return false;
+  if (!same_shape(in[0], in[1]) || !same_shape(in[0], in[2]) || !same_shape(in[0], in[3])) return false;
+  if (!same_shape(in[0], out[0]) || !same_shape(in[2], out[1]) || !same_shape(in[3], out[2])) return false;
+  return !adam_alias_violation(in[0], in[1], in[2], in[3], out[0], out[1], out[2]);
+}
+bool adam_v0_supported(const TensorDesc* in, int ni, const TensorDesc* out, int no, const void*) {
+  return adam_v0_check(in, ni, out, no);
+}
+Status adam_v0_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, const void* attr, void*, size_t,
+                      cudaStream_t stream) {
+  if (!adam_v0_check(in, ni, out, no) || !attr) return Status::InvalidArgument;
+  AdamArgs a{};
+  a.p = static_cast<const float*>(in[0].data);  // out-of-place needs no staging copy: p is read, p_out written
+  a.g = static_cast<const float*>(in[1].data);
+  a.m = static_cast<const float*>(in[2].data);
+  a.v = static_cast<const float*>(in[3].data);
+  a.bc1 = static_cast<const float*>(in[4].data);
+  a.bc2 = static_cast<const float*>(in[5].data);
+  a.p_out = static_cast<float*>(out[0].data);
+  a.m_out = static_cast<float*>(out[1].data);
+  a.v_out = static_cast<float*>(out[2].data);
+  a.n = numel_raw(in[0]);
+  a.h = read_adam(attr);
+  a.h.weight_decay = 0.0f;  // the v0 contract has no decay term
+  return launch_adam<true, false>(a, stream);
+}
+size_t no_workspace(const TensorDesc*, int, const void*) { return 0; }
+
+// ---------------------------------------------------------------- adam_step_f32_fused_v1
+// inputs [P,G,M,V,step(i32 scalar)] -> outputs [P,M,V] or [P,M,V,P_bf16]; textbook Adam with
+// bias correction 1-beta^t computed from the device step counter (t clamped to >= 1).
+bool i32_scalar(const TensorDesc& d) {
+  return d.dtype == DType::kI32 && (d.rank() == 0 || (d.rank() == 1 && d.shape[0] == 1));
+}
+bool adam_v1_check(const TensorDesc* in, int ni, const TensorDesc* out, int no) {
+  if (!in || !out || ni != 5 || (no != 3 && no != 4)) return false;
+  for (int i = 0; i < 4; ++i)
+    if (!f32_contig_rank1p(in[i])) return false;
+  for (int i = 0; i < 3; ++i)
+    if (!f32_contig_rank1p(out[i])) return false;
+  if (!i32_scalar(in[4])) return false;
+  if (!same_shape(in[0], in[1]) || !same_shape(in[0], in[2]) || !same_shape(in[0], in[3])) return false;
+  if (!same_shape(in[0], out[0]) || !same_shape(in[2], out[1]) || !same_shape(in[3], out[2])) return false;
+  if (no == 4) {
+    if (out[3].dtype != DType::kBF16 || !out[3].contiguous || !same_shape(in[0], out[3])) return false;
+    for (int i = 0; i < 4; ++i)
+      if (same_ptr(out[3], in[i])) return false;
+  }
+  return !adam_alias_violation(in[0], in[1], in[2], in[3], out[0], out[1], out[2]);
+}
+bool adam_v1_supported(const TensorDesc* in, int ni, const TensorDesc* out, int no, const void*) {
+  return adam_v1_check(in, ni, out, no);
+}
+Status adam_v1_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, const void* attr, void*, size_t,
+                      cudaStream_t stream) {
+  if (!adam_v1_check(in, ni, out, no) || !attr) return Status::InvalidArgument;
+  AdamArgs a{};
+  a.p = static_cast<const float*>(in[0].data);
+  a.g = static_cast<const float*>(in[1].data);
+  a.m = static_cast<const float*>(in[2].data);
+  a.v = static_cast<const float*>(in[3].data);
+  a.step = static_cast<const int32_t*>(in[4].data);
+  a.p_out = static_cast<float*>(out[0].data);
+  a.m_out = static_cast<float*>(out[1].data);
+  a.v_out = static_cast<float*>(out[2].data);
+  a.p_bf16 = no == 4 ? static_cast<__nv_bfloat16*>(out[3].data) : nullptr;
+  a.n = numel_raw(in[0]);
+  a.h = read_adam(attr);
+  return no == 4 ? launch_adam<false, true>(a, stream) : launch_adam<false, false>(a, stream);
+}
+
+// ---------------------------------------------------------------- step_inc
+// Contract (ops/step_inc/launcher.cu:92-144): int32, same shape, rank 0 allowed. The reference
+// increments the OUTPUT buffer and never reads the input, so out-of-place use relies on the caller
+// having copied the input first; that behaviour is kept.
+__global__ void step_inc_kernel(int32_t* s, int64_t n) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) s[i] += 1;
+}
+bool i32_ok(const TensorDesc& t) { return t.dtype == DType::kI32 && (t.rank() == 0 || t.contiguous); }
+bool step_inc_check(const TensorDesc* in, int ni, const TensorDesc* out, int no) {
+  if (!in || !out || ni != 1 || no != 1) return false;
+  if (!i32_ok(in[0]) || !i32_ok(out[0]) || !same_shape(in[0], out[0])) return false;
+  int64_t n = 0;
+  return positive_numel(in[0], 0, &n) && n >= 1;
+}
+bool step_inc_supported(const TensorDesc* in, int ni, const TensorDesc* out, int no, const void*) {
+  return step_inc_check(in, ni, out, no);
+}
+Status step_inc_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, const void*, void*, size_t,
+                       cudaStream_t stream) {
+  if (!step_inc_check(in, ni, out, no)) return Status::InvalidArgument;
+  int64_t n = 0;
+  positive_numel(in[0], 0, &n);
+  cudaGetLastError();
+  step_inc_kernel<<<streaming_grid(n, 256, 4), 256, 0, stream>>>(static_cast<int32_t*>(out[0].data), n);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- bias_corr
+// step (i32 scalar) -> bc1_inv = 1/(1-beta1^t), bc2_inv = 1/(1-beta2^t), t = max(step,1), denominators
+// clamped away from zero at 1e-20 (ops/biascorr/launcher.cu:82-101). Schema 'BCOR' is mandatory.
+__global__ void bias_corr_kernel(const int32_t* step, float beta1, float beta2, float* o1, float* o2) {
+  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+  int t = step[0];
+  if (t < 1) t = 1;
+  float d1 = 1.0f - powf(beta1, static_cast<float>(t));
+  float d2 = 1.0f - powf(beta2, static_cast<float>(t));
+  if (fabsf(d1) < 1e-20f) d1 = 1e-20f;
+  if (fabsf(d2) < 1e-20f) d2 = 1e-20f;
+  o1[0] = 1.0f / d1;
+  o2[0] = 1.0f / d2;
+}
+bool scalar_like(const TensorDesc& d, DType dt) {
+  return d.dtype == dt && d.contiguous && (d.rank() == 0 || (d.rank() == 1 && d.shape[0] == 1));
+}
+bool bias_corr_check(const TensorDesc* in, int ni, const TensorDesc* out, int no, const void* attr, float* betas) {
+  if (!in || !out || ni != 1 || no != 2) return false;
+  if (!scalar_like(in[0], DType::kI32) || !scalar_like(out[0], DType::kF32) || !scalar_like(out[1], DType::kF32))
+    return false;
+  float b[2];
+  if (!read_attr_payload(attr, schema::kBiasCorr, false, b, 8)) return false;
+  if (b[0] != b[0] || b[1] != b[1]) return false;  // NaN betas are rejected
+  if (betas) {
+    betas[0] = b[0];
+    betas[1] = b[1];
+  }
+  return true;
+}
+bool bias_corr_supported(const TensorDesc* in, int ni, const TensorDesc* out, int no, const void* attr) {
+  return bias_corr_check(in, ni, out, no, attr, nullptr);
+}
+Status bias_corr_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, const void* attr, void*, size_t,
+                        cudaStream_t stream) {
+  float b[2];
+  if (!bias_corr_check(in, ni, out, no, attr, b)) return Status::InvalidArgument;
+  cudaGetLastError();
+  bias_corr_kernel<<<1, 32, 0, stream>>>(static_cast<const int32_t*>(in[0].data), b[0], b[1],
+                                         static_cast<float*>(out[0].data), static_cast<float*>(out[1].data));
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- sgd_step
+// O = P - lr*G, in place allowed, O must not alias G; lr from 'SGDS' <f>, default 1e-3
+// (ops/sgd_step/launcher.cu:32-45,163-221). The update is computed in fp32 and rounded once.
+template <typename T>
+__global__ void __launch_bounds__(256) sgd_kernel(const T* p, const T* g, T* o, int64_t n, int64_t nvec, float lr) {
+  using PK = Pack16<T>;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (int64_t i = tid; i < nvec; i += stride) {
+    const PK a = ld_stream(reinterpret_cast<const PK*>(p) + i);
+    const PK b = ld_stream(reinterpret_cast<const PK*>(g) + i);
+    PK r;
+#pragma unroll
+    for (int e = 0; e < PK::kN; ++e) r.v[e] = Cvt<T>::from_f(Cvt<T>::to_f(a.v[e]) - lr * Cvt<T>::to_f(b.v[e]));
+    st_stream(reinterpret_cast<PK*>(o) + i, r);
+  }
+  for (int64_t k = nvec * PK::kN + tid; k < n; k += stride)
+    o[k] = Cvt<T>::from_f(Cvt<T>::to_f(p[k]) - lr * Cvt<T>::to_f(g[k]));
+}
+template <DType kDt>
+bool sgd_check(const TensorDesc* in, int ni, const TensorDesc* out, int no) {
+  if (!in || !out || ni != 2 || no != 1) return false;
+  const TensorDesc* ts[] = {&in[0], &in[1], &out[0]};
+  for (const TensorDesc* t : ts)
+    if (t->dtype != kDt || !t->contiguous || t->rank() < 1) return false;
+  if (!same_shape(in[0], in[1]) || !same_shape(in[0], out[0])) return false;
+  int64_t n = 0;
+  return positive_numel(in[0], 1, &n);
+}
+template <DType kDt>
+bool sgd_supported(const TensorDesc* in, int ni, const TensorDesc* out, int no, const void*) {
+  return sgd_check<kDt>(in, ni, out, no);
+}
+template <DType kDt, typename T>
+Status sgd_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, const void* attr, void*, size_t,
+                  cudaStream_t stream) {
+  if (!sgd_check<kDt>(in, ni, out, no)) return Status::InvalidArgument;
+  if (out[0].data == in[1].data) return Status::InvalidArgument;
+  float lr = 1e-3f;
+  read_attr_payload(attr, schema::kSgd, false, &lr, 4);
+  int64_t n = 0;
+  positive_numel(in[0], 1, &n);
+  const bool vec = aligned_to(in[0].data, 16) && aligned_to(in[1].data, 16) && aligned_to(out[0].data, 16);
+  const int64_t nvec = vec ? n / Pack16<T>::kN : 0;
+  cudaGetLastError();
+  sgd_kernel<T><<<streaming_grid(vec ? nvec + 1 : n, 256, 8), 256, 0, stream>>>(
+      static_cast<const T*>(in[0].data), static_cast<const T*>(in[1].data), static_cast<T*>(out[0].data), n, nvec, lr);
+  return launch_status();
+}
+
+KernelVariant make(const char* name, uint32_t schema_gate,
+                   Status (*launch)(const TensorDesc*, int, TensorDesc*, int, const void*, void*, size_t, cudaStream_t),
+                   bool (*supported)(const TensorDesc*, int, const TensorDesc*, int, const void*)) {
+  KernelVariant v{};
+  v.name = name;
+  v.flags = kKV_CaptureSafe;
+  v.expected_attr_schema_id = schema_gate;
+  v.launch = launch;
+  v.supported = supported;
+  v.query_workspace = no_workspace;
+  return v;
+}
+
+}  // namespace
+
+KernelVariant make_adam_step_f32_variant() { return make("adam_step_f32_sm100", schema::kAdam, adam_v0_launch, adam_v0_supported); }
+KernelVariant make_adam_step_f32_fused_variant() { return make("adam_step_f32_fused_sm100", schema::kAdam, adam_v1_launch, adam_v1_supported); }
+KernelVariant make_step_inc_variant() { return make("step_inc_i32_sm100", 0, step_inc_launch, step_inc_supported); }
+KernelVariant make_biascorr_variant() { return make("bias_corr_f32_sm100", schema::kBiasCorr, bias_corr_launch, bias_corr_supported); }
+KernelVariant make_sgd_step_f32_variant() { return make("sgd_step_f32_sm100", 0, sgd_launch<DType::kF32, float>, sgd_supported<DType::kF32>); }
+KernelVariant make_sgd_step_f16_variant() { return make("sgd_step_f16_sm100", 0, sgd_launch<DType::kF16, __half>, sgd_supported<DType::kF16>); }
+KernelVariant make_sgd_step_bf16_variant() { return make("sgd_step_bf16_sm100", 0, sgd_launch<DType::kBF16, __nv_bfloat16>, sgd_supported<DType::kBF16>); }
+
+}  // namespace aicf::cuda

@@ -1,0 +1,394 @@
+// Row softmax and fused softmax cross-entropy (loss rows + gradient + argmax) over the last axis.
+//
+// Single HBM pass: a block owns one row at a time and keeps it in registers (kPackets 16-byte
+// packets per thread), so the row is read once and the result written once. Row max / sum are
+// warp-shuffle reductions joined through shared memory in a fixed order, hence deterministic.
+// Rows wider than 32768 elements, or rows that are not 16-byte aligned, take a three-read fallback
+// kernel.
+#include "common.cuh"
+
+namespace aicf::cuda {
+
+namespace {
+
+constexpr int kMaxWarps = 32;
+
+// Block-wide max / sum. Every thread returns the same value; partials are folded in warp order.
+template <bool kIsMax>
+__device__ __forceinline__ float block_reduce(float v, float* smem /*[kMaxWarps]*/) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  v = kIsMax ? warp_max(v) : warp_sum(v);
+  __syncthreads();  // smem may still be read by the previous reduction
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  float r = smem[0];
+  for (int w = 1; w < nwarps; ++w) r = kIsMax ? fmaxf(r, smem[w]) : r + smem[w];
+  return r;
+}
+
+struct ArgMax {
+  float v;
+  int idx;
+};
+__device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {  // larger value wins, ties -> lower index
+  if (b.v > a.v || (b.v == a.v && b.idx < a.idx)) return b;
+  return a;
+}
+__device__ __forceinline__ ArgMax block_argmax(ArgMax a, float* sv, int* si) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax b;
+    b.v = __shfl_xor_sync(0xffffffffu, a.v, o);
+    b.idx = __shfl_xor_sync(0xffffffffu, a.idx, o);
+    a = better(a, b);
+  }
+  __syncthreads();
+  if (lane == 0) {
+    sv[warp] = a.v;
+    si[warp] = a.idx;
+  }
+  __syncthreads();
+  ArgMax r{sv[0], si[0]};
+  for (int w = 1; w < nwarps; ++w) r = better(r, ArgMax{sv[w], si[w]});
+  return r;
+}
+
+// ------------------------------------------------------------------ softmax, row in registers
+template <typename T, int kPackets>
+__global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M,
+                                                           int64_t N) {
+  using PK = Pack16<T>;
+  constexpr int kN = PK::kN;
+  __shared__ float red[kMaxWarps];
+  const int64_t np = N / kN;  // N % kN == 0 on this path
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const PK* xr = reinterpret_cast<const PK*>(x + row * N);
+    PK* yr = reinterpret_cast<PK*>(y + row * N);
+    float f[kPackets][kN];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int q = 0; q < kPackets; ++q) {
+      const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
+      if (pi < np) {
+        const PK p = ld_stream(xr + pi);
+#pragma unroll
+        for (int e = 0; e < kN; ++e) {
+          f[q][e] = Cvt<T>::to_f(p.v[e]);
+          mx = fmaxf(mx, f[q][e]);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < kN; ++e) f[q][e] = -INFINITY;
+      }
+    }
+    mx = block_reduce<true>(mx, red);
+    float sum = 0.0f;
+#pragma unroll
+    for (int q = 0; q < kPackets; ++q)
+#pragma unroll
+      for (int e = 0; e < kN; ++e) {
+        f[q][e] = expf(f[q][e] - mx);  // exp(-inf) == 0 for the padding
+        sum += f[q][e];
+      }
+    sum = block_reduce<false>(sum, red);
+    const float inv = 1.0f / sum;
+#pragma unroll
+    for (int q = 0; q < kPackets; ++q) {
+      const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
+      if (pi < np) {
+        PK o;
+#pragma unroll
+        for (int e = 0; e < kN; ++e) o.v[e] = Cvt<T>::from_f(f[q][e] * inv);
+        st_stream(yr + pi, o);
+      }
+    }
+  }
+}
+
+// Fallback: any N, any alignment; reads the row three times.
+template <typename T>
+__global__ void __launch_bounds__(256) softmax_multipass_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M,
+                                                               int64_t N) {
+  __shared__ float red[kMaxWarps];
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const T* xr = x + row * N;
+    T* yr = y + row * N;
+    float mx = -INFINITY;
+    for (int64_t i = threadIdx.x; i < N; i += blockDim.x) mx = fmaxf(mx, Cvt<T>::to_f(xr[i]));
+    mx = block_reduce<true>(mx, red);
+    float sum = 0.0f;
+    for (int64_t i = threadIdx.x; i < N; i += blockDim.x) sum += expf(Cvt<T>::to_f(xr[i]) - mx);
+    sum = block_reduce<false>(sum, red);
+    const float inv = 1.0f / sum;
+    for (int64_t i = threadIdx.x; i < N; i += blockDim.x) yr[i] = Cvt<T>::from_f(expf(Cvt<T>::to_f(xr[i]) - mx) * inv);
+  }
+}
+
+// threads/packets choice shared by softmax and softmax-CE
+struct RowCfg {
+  int threads = 0;
+  int packets = 0;  // 0 -> fallback
+};
+// max_packets bounds the registers a thread spends on the row: 8 packets of fp32 or 4 packets of a
+// 16-bit type are 32 floats after unpacking, which fits the 64-register budget of a 1024-thread block.
+RowCfg pick_row_cfg(int64_t n_packets, int max_packets) {
+  RowCfg c;
+  int threads = 128;
+  while (threads < 1024 && static_cast<int64_t>(threads) * 4 < n_packets) threads *= 2;
+  const int64_t per = (n_packets + threads - 1) / threads;
+  c.threads = threads;
+  c.packets = per <= 1 ? 1 : per <= 2 ? 2 : per <= 4 ? 4 : per <= 8 ? 8 : 0;
+  if (c.packets > max_packets) c.packets = 0;
+  return c;
+}
+
+template <typename T>
+Status softmax_run(const T* x, T* y, int64_t M, int64_t N, cudaStream_t stream) {
+  constexpr int kN = Pack16<T>::kN;
+  constexpr int kMaxPk = sizeof(T) == 4 ? 8 : 4;
+  const bool vec = (N % kN == 0) && aligned_to(x, 16) && aligned_to(y, 16);
+  const RowCfg c = vec ? pick_row_cfg(N / kN, kMaxPk) : RowCfg{};
+  cudaGetLastError();
+  if (c.packets == 0) {
+    softmax_multipass_kernel<T><<<streaming_grid(M, 1, 8), 256, 0, stream>>>(x, y, M, N);
+    return launch_status();
+  }
+  const int per_sm = 2048 / c.threads;
+  const int grid = streaming_grid(M, 1, per_sm < 1 ? 1 : per_sm);
+  switch (c.packets) {
+    case 1: softmax_regs_kernel<T, 1><<<grid, c.threads, 0, stream>>>(x, y, M, N); break;
+    case 2: softmax_regs_kernel<T, 2><<<grid, c.threads, 0, stream>>>(x, y, M, N); break;
+    case 4: softmax_regs_kernel<T, 4><<<grid, c.threads, 0, stream>>>(x, y, M, N); break;
+    default: softmax_regs_kernel<T, kMaxPk><<<grid, c.threads, 0, stream>>>(x, y, M, N); break;
+  }
+  return launch_status();
+}
+
+bool rows_cols_any(const TensorDesc& t, int64_t* M, int64_t* N) {
+  const int r = t.rank();
+  if (r < 1 || r > kMaxRank) return false;
+  int64_t m = 1;
+  for (int i = 0; i < r - 1; ++i) {
+    if (t.shape[i] <= 0) return false;
+    m *= t.shape[i];
+  }
+  if (t.shape[r - 1] <= 0) return false;
+  *M = m;
+  *N = t.shape[r - 1];
+  return true;
+}
+
+template <DType kDt>
+bool softmax_check(const TensorDesc* in, int ni, const TensorDesc* out, int no) {
+  if (!in || !out || ni != 1 || no != 1) return false;
+  if (in[0].dtype != kDt || out[0].dtype != kDt) return false;
+  if (!in[0].contiguous || !out[0].contiguous || !same_shape(in[0], out[0])) return false;
+  int64_t M = 0, N = 0;
+  return rows_cols_any(in[0], &M, &N);
+}
+template <DType kDt>
+bool softmax_supported(const TensorDesc* in, int ni, const TensorDesc* out, int no, const void*) {
+  return softmax_check<kDt>(in, ni, out, no);
+}
+template <DType kDt, typename T>
+Status softmax_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, const void*, void*, size_t,
+                      cudaStream_t stream) {
+  if (!softmax_check<kDt>(in, ni, out, no)) return Status::InvalidArgument;
+  int64_t M = 0, N = 0;
+  rows_cols_any(in[0], &M, &N);
+  return softmax_run<T>(static_cast<const T*>(in[0].data), static_cast<T*>(out[0].data), M, N, stream);
+}
+
+// ------------------------------------------------------------------ softmax cross-entropy
+// inputs  [logits (B,C) f32|bf16|f16, labels (B,) i32]
+// outputs [dlogits (B,C) same dtype, loss_row (B,) f32, argmax (B,) i32]   (argmax optional)
+//   loss_row = logsumexp(z) - z[label];  dlogits = (softmax(z) - onehot(label)) * scale
+// scale: 'SMCE' <f>, default 1/B. A label outside [0,C) contributes no one-hot term and a zero loss.
+template <typename T, int kPackets>
+__global__ void __launch_bounds__(1024)
+    softmax_ce_regs_kernel(const T* __restrict__ z, const int32_t* __restrict__ labels, T* __restrict__ dz,
+                           float* __restrict__ loss_row, int32_t* __restrict__ argmax_out, int64_t B, int64_t C,
+                           float scale) {
+  using PK = Pack16<T>;
+  constexpr int kN = PK::kN;
+  __shared__ float red[kMaxWarps];
+  __shared__ int redi[kMaxWarps];
+  __shared__ float z_label;
+  const int64_t np = C / kN;
+  for (int64_t row = blockIdx.x; row < B; row += gridDim.x) {
+    const PK* zr = reinterpret_cast<const PK*>(z + row * C);
+    PK* dr = reinterpret_cast<PK*>(dz + row * C);
+    const int label = labels[row];
+    float f[kPackets][kN];
+    ArgMax am{-INFINITY, 0x7fffffff};
+#pragma unroll
+    for (int q = 0; q < kPackets; ++q) {
+      const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
+      if (pi < np) {
+        const PK p = ld_stream(zr + pi);
+#pragma unroll
+        for (int e = 0; e < kN; ++e) {
+          const float v = Cvt<T>::to_f(p.v[e]);
+          f[q][e] = v;
+          const int col = static_cast<int>(pi) * kN + e;
+          if (v > am.v) {  // columns are visited in increasing order per thread: strict > keeps the lowest
+            am.v = v;
+            am.idx = col;
+          }
+          if (col == label) z_label = v;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < kN; ++e) f[q][e] = -INFINITY;
+      }
+    }
+    am = block_argmax(am, red, redi);
+    const float mx = am.v;
+    float sum = 0.0f;
+#pragma unroll
+    for (int q = 0; q < kPackets; ++q)
+#pragma unroll
+      for (int e = 0; e < kN; ++e) {
+        f[q][e] = expf(f[q][e] - mx);
+        sum += f[q][e];
+      }
+    sum = block_reduce<false>(sum, red);  // its barriers also publish z_label
+    const float k = scale / sum;
+    const bool label_ok = label >= 0 && label < C;
+#pragma unroll
+    for (int q = 0; q < kPackets; ++q) {
+      const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
+      if (pi < np) {
+        PK o;
+#pragma unroll
+        for (int e = 0; e < kN; ++e) {
+          const int col = static_cast<int>(pi) * kN + e;
+          float g = f[q][e] * k;
+          if (col == label) g -= scale;
+          o.v[e] = Cvt<T>::from_f(g);
+        }
+        st_stream(dr + pi, o);
+      }
+    }
+    if (threadIdx.x == 0) {
+      loss_row[row] = label_ok ? (logf(sum) + mx - z_label) : 0.0f;
+      if (argmax_out) argmax_out[row] = am.idx;
+    }
+    __syncthreads();  // z_label is rewritten by the next row
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+    softmax_ce_multipass_kernel(const T* __restrict__ z, const int32_t* __restrict__ labels, T* __restrict__ dz,
+                                float* __restrict__ loss_row, int32_t* __restrict__ argmax_out, int64_t B, int64_t C,
+                                float scale) {
+  __shared__ float red[kMaxWarps];
+  __shared__ int redi[kMaxWarps];
+  for (int64_t row = blockIdx.x; row < B; row += gridDim.x) {
+    const T* zr = z + row * C;
+    T* dr = dz + row * C;
+    const int label = labels[row];
+    ArgMax am{-INFINITY, 0x7fffffff};
+    for (int64_t i = threadIdx.x; i < C; i += blockDim.x) {
+      const float v = Cvt<T>::to_f(zr[i]);
+      if (v > am.v) {
+        am.v = v;
+        am.idx = static_cast<int>(i);
+      }
+    }
+    am = block_argmax(am, red, redi);
+    const float mx = am.v;
+    float sum = 0.0f;
+    for (int64_t i = threadIdx.x; i < C; i += blockDim.x) sum += expf(Cvt<T>::to_f(zr[i]) - mx);
+    sum = block_reduce<false>(sum, red);
+    const float k = scale / sum;
+    for (int64_t i = threadIdx.x; i < C; i += blockDim.x) {
+      float g = expf(Cvt<T>::to_f(zr[i]) - mx) * k;
+      if (i == label) g -= scale;
+      dr[i] = Cvt<T>::from_f(g);
+    }
+    if (threadIdx.x == 0) {
+      const bool label_ok = label >= 0 && label < C;
+      loss_row[row] = label_ok ? (logf(sum) + mx - Cvt<T>::to_f(zr[label_ok ? label : 0])) : 0.0f;
+      if (argmax_out) argmax_out[row] = am.idx;
+    }
+    __syncthreads();
+  }
+}
+
+template <DType kDt>
+bool softmax_ce_check(const TensorDesc* in, int ni, const TensorDesc* out, int no) {
+  if (!in || !out || ni != 2 || (no != 2 && no != 3)) return false;
+  const TensorDesc &Z = in[0], &L = in[1], &D = out[0], &Lo = out[1];
+  if (Z.dtype != kDt || D.dtype != kDt || Z.rank() != 2 || !Z.contiguous || !D.contiguous || !same_shape(Z, D))
+    return false;
+  if (Z.shape[0] <= 0 || Z.shape[1] <= 0 || Z.shape[1] > 0x7fffffff) return false;
+  if (L.dtype != DType::kI32 || L.rank() != 1 || !L.contiguous || L.shape[0] != Z.shape[0]) return false;
+  if (Lo.dtype != DType::kF32 || Lo.rank() != 1 || !Lo.contiguous || Lo.shape[0] != Z.shape[0]) return false;
+  if (no == 3) {
+    const TensorDesc& A = out[2];
+    if (A.dtype != DType::kI32 || A.rank() != 1 || !A.contiguous || A.shape[0] != Z.shape[0]) return false;
+  }
+  return true;
+}
+template <DType kDt>
+bool softmax_ce_supported(const TensorDesc* in, int ni, const TensorDesc* out, int no, const void*) {
+  return softmax_ce_check<kDt>(in, ni, out, no);
+}
+template <DType kDt, typename T>
+Status softmax_ce_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, const void* attr, void*, size_t,
+                         cudaStream_t stream) {
+  if (!softmax_ce_check<kDt>(in, ni, out, no)) return Status::InvalidArgument;
+  const int64_t B = in[0].shape[0], C = in[0].shape[1];
+  float scale = 1.0f / static_cast<float>(B);
+  read_attr_payload(attr, schema::kSoftmaxCE, false, &scale, 4);
+  const T* z = static_cast<const T*>(in[0].data);
+  const int32_t* lab = static_cast<const int32_t*>(in[1].data);
+  T* dz = static_cast<T*>(out[0].data);
+  float* loss = static_cast<float*>(out[1].data);
+  int32_t* am = no == 3 ? static_cast<int32_t*>(out[2].data) : nullptr;
+  constexpr int kN = Pack16<T>::kN;
+  constexpr int kMaxPk = sizeof(T) == 4 ? 8 : 4;
+  const bool vec = (C % kN == 0) && aligned_to(z, 16) && aligned_to(dz, 16);
+  const RowCfg c = vec ? pick_row_cfg(C / kN, kMaxPk) : RowCfg{};
+  cudaGetLastError();
+  if (c.packets == 0) {
+    softmax_ce_multipass_kernel<T><<<streaming_grid(B, 1, 8), 256, 0, stream>>>(z, lab, dz, loss, am, B, C, scale);
+    return launch_status();
+  }
+  const int per_sm = 2048 / c.threads;
+  const int grid = streaming_grid(B, 1, per_sm < 1 ? 1 : per_sm);
+  switch (c.packets) {
+    case 1: softmax_ce_regs_kernel<T, 1><<<grid, c.threads, 0, stream>>>(z, lab, dz, loss, am, B, C, scale); break;
+    case 2: softmax_ce_regs_kernel<T, 2><<<grid, c.threads, 0, stream>>>(z, lab, dz, loss, am, B, C, scale); break;
+    case 4: softmax_ce_regs_kernel<T, 4><<<grid, c.threads, 0, stream>>>(z, lab, dz, loss, am, B, C, scale); break;
+    default: softmax_ce_regs_kernel<T, kMaxPk><<<grid, c.threads, 0, stream>>>(z, lab, dz, loss, am, B, C, scale); break;
+  }
+  return launch_status();
+}
+
+size_t no_workspace(const TensorDesc*, int, const void*) { return 0; }
+using LaunchFn = Status (*)(const TensorDesc*, int, TensorDesc*, int, const void*, void*, size_t, cudaStream_t);
+using SupportedFn = bool (*)(const TensorDesc*, int, const TensorDesc*, int, const void*);
+KernelVariant make(const char* name, LaunchFn l, SupportedFn s) {
+  KernelVariant v{};
+  v.name = name;
+  v.flags = kKV_CaptureSafe;
+  v.launch = l;
+  v.supported = s;
+  v.query_workspace = no_workspace;
+  return v;
+}
+
+}  // namespace
+
+KernelVariant make_softmax_lastdim_f32_variant() { return make("softmax_f32_sm100", softmax_launch<DType::kF32, float>, softmax_supported<DType::kF32>); }
+KernelVariant make_softmax_lastdim_bf16_variant() { return make("softmax_bf16_sm100", softmax_launch<DType::kBF16, __nv_bfloat16>, softmax_supported<DType::kBF16>); }
+KernelVariant make_softmax_lastdim_f16_variant() { return make("softmax_f16_sm100", softmax_launch<DType::kF16, __half>, softmax_supported<DType::kF16>); }
+KernelVariant make_softmax_ce_f32_variant() { return make("softmax_ce_f32_sm100", softmax_ce_launch<DType::kF32, float>, softmax_ce_supported<DType::kF32>); }
+KernelVariant make_softmax_ce_bf16_variant() { return make("softmax_ce_bf16_sm100", softmax_ce_launch<DType::kBF16, __nv_bfloat16>, softmax_ce_supported<DType::kBF16>); }
+KernelVariant make_softmax_ce_f16_variant() { return make("softmax_ce_f16_sm100", softmax_ce_launch<DType::kF16, __half>, softmax_ce_supported<DType::kF16>); }
+
+}  // namespace aicf::cuda

@@ -1,0 +1,177 @@
+// Registration table of this backend.
+//
+// The 30 kernel ids of the reference's MLP path (register_all.cpp:105-263 there) resolve to sm_100a
+// kernels with the same contracts and the same relative priorities, so lowered plans pinned to
+// those ids run unchanged. The *_vec2 / *_half2 ids are aliases of the one vectorised kernel per
+// dtype (it picks 16-byte or scalar accesses itself). layernorm / batchnorm ids are not registered:
+// by-id dispatch answers NotImplemented for them.
+#include "aicf/backends/cuda/registry/register_all.hpp"
+
+#include <cstdio>
+
+#include "aicf/backends/cuda/registry/kernel_variant.hpp"
+#include "aicf/backends/cuda/registry/op_kind.hpp"
+#include "aicf/backends/cuda/registry/registry.hpp"
+
+namespace aicf::cuda {
+// optimizer.cu
+KernelVariant make_adam_step_f32_variant();
+KernelVariant make_adam_step_f32_fused_variant();
+KernelVariant make_step_inc_variant();
+KernelVariant make_biascorr_variant();
+KernelVariant make_sgd_step_f32_variant();
+KernelVariant make_sgd_step_f16_variant();
+KernelVariant make_sgd_step_bf16_variant();
+// eltwise.cu
+KernelVariant make_relu_f32_variant();
+KernelVariant make_relu_f16_variant();
+KernelVariant make_relu_bf16_variant();
+KernelVariant make_relu_bwd_f32_variant();
+KernelVariant make_relu_bwd_f16_variant();
+KernelVariant make_relu_bwd_bf16_variant();
+KernelVariant make_add_f32_variant();
+KernelVariant make_add_f16_variant();
+KernelVariant make_add_bf16_variant();
+KernelVariant make_mse_grad_f32_variant();
+KernelVariant make_mse_grad_f16_variant();
+KernelVariant make_mse_grad_bf16_variant();
+KernelVariant make_copy_f32_variant();
+KernelVariant make_copy_f16_variant();
+KernelVariant make_copy_bf16_variant();
+KernelVariant make_copy_i32_variant();
+KernelVariant make_grad_zero_variant();
+KernelVariant make_bias_add_f32_variant();
+KernelVariant make_bias_add_f16_variant();
+KernelVariant make_bias_add_bf16_variant();
+KernelVariant make_cast_variant();
+// reduce.cu
+KernelVariant make_reduce_sum_lastdim_f32_variant();
+KernelVariant make_reduce_sum_lastdim_f16_to_f32_variant();
+KernelVariant make_reduce_sum_lastdim_f16_variant();
+KernelVariant make_reduce_sum_lastdim_bf16_to_f32_variant();
+KernelVariant make_reduce_sum_lastdim_bf16_variant();
+KernelVariant make_reduce_sum_lastaxis_f32_variant();
+KernelVariant make_reduce_sum_lastaxis_bf16_variant();
+KernelVariant make_reduce_sum_lastaxis_f16_variant();
+KernelVariant make_reduce_max_lastaxis_f32_variant();
+KernelVariant make_reduce_max_lastaxis_bf16_variant();
+KernelVariant make_reduce_max_lastaxis_f16_variant();
+KernelVariant make_reduce_mean_lastaxis_f32_variant();
+KernelVariant make_reduce_mean_lastaxis_bf16_variant();
+KernelVariant make_reduce_mean_lastaxis_f16_variant();
+// softmax.cu
+KernelVariant make_softmax_lastdim_f32_variant();
+KernelVariant make_softmax_lastdim_bf16_variant();
+KernelVariant make_softmax_lastdim_f16_variant();
+KernelVariant make_softmax_ce_f32_variant();
+KernelVariant make_softmax_ce_bf16_variant();
+KernelVariant make_softmax_ce_f16_variant();
+// gemm.cu
+KernelVariant make_gemm_f32_naive_variant();
+KernelVariant make_gemm_f16_tc_wmma_out_f16_variant();
+KernelVariant make_gemm_bf16_tcgen05_out_bf16_variant();
+KernelVariant make_gemm_bf16_tcgen05_out_f32_variant();
+KernelVariant make_gemm_f16_tcgen05_out_f32_variant();
+KernelVariant make_gemm_f16_tcgen05_out_f16_variant();
+KernelVariant make_gemm_bias_relu_f32_naive_variant();
+KernelVariant make_gemm_bias_relu_f16_tc_wmma_out_f16_variant();
+KernelVariant make_gemm_bias_relu_bf16_tcgen05_out_bf16_variant();
+KernelVariant make_gemm_bias_relu_bf16_tcgen05_out_f32_variant();
+KernelVariant make_gemm_bias_relu_f16_tcgen05_out_f16_variant();
+// allreduce.cpp
+KernelVariant make_all_reduce_nccl_f32_variant();
+}  // namespace aicf::cuda
+
+namespace {
+struct Row {
+  aicf::cuda::OpKind kind;
+  aicf::cuda::KernelVariant (*factory)();
+  int priority;
+  const char* id;
+};
+}  // namespace
+
+extern "C" void aicf_cuda_register_all_kernels() {
+  using namespace aicf::cuda;
+  using K = OpKind;
+  std::fprintf(stderr, "[aicf] register_all: KID_VERSION=2026-01-20\n");
+
+  static const Row kRows[] = {
+      // ---- ids shared with the reference (same kind, id, priority) ----
+      {K::ReduceSum, make_reduce_sum_lastdim_f16_variant, 115, "reduce_sum_keep_lastdim_f16_v0"},
+      {K::ReduceSum, make_reduce_sum_lastdim_f16_to_f32_variant, 110, "reduce_sum_keep_lastdim_f16_to_f32_v0"},
+      {K::ReduceSum, make_reduce_sum_lastdim_f32_variant, 100, "reduce_sum_keep_lastdim_f32_v0"},
+      {K::Gemm, make_gemm_f16_tc_wmma_out_f16_variant, 20, "gemm_f16_tc_wmma_out_f16_v0"},
+      {K::Gemm, make_gemm_f32_naive_variant, 0, "gemm_f32_naive_v0"},
+      {K::GemmEpilogue, make_gemm_bias_relu_f16_tc_wmma_out_f16_variant, 20, "gemm_bias_relu_f16_tc_wmma_out_f16_v0"},
+      {K::GemmEpilogue, make_gemm_bias_relu_f32_naive_variant, 0, "gemm_bias_relu_f32_naive_v0"},
+      {K::BiasAdd, make_bias_add_f16_variant, 30, "bias_add_f16_vec2_v0"},
+      {K::BiasAdd, make_bias_add_f16_variant, 20, "bias_add_f16_v0"},
+      {K::BiasAdd, make_bias_add_f32_variant, 0, "bias_add_f32_v0"},
+      {K::EltwiseAdd, make_add_f16_variant, 30, "add_f16_vec2_v0"},
+      {K::EltwiseAdd, make_add_f16_variant, 20, "add_f16_v0"},
+      {K::EltwiseAdd, make_add_f32_variant, 0, "add_f32_v0"},
+      {K::EltwiseRelu, make_relu_f16_variant, 30, "relu_f16_vec2_v0"},
+      {K::EltwiseRelu, make_relu_f16_variant, 20, "relu_f16_v0"},
+      {K::EltwiseRelu, make_relu_f32_variant, 0, "relu_f32_v0"},
+      {K::MseGrad, make_mse_grad_f16_variant, 20, "mse_grad_f16_v0"},
+      {K::MseGrad, make_mse_grad_f32_variant, 0, "mse_grad_f32_v0"},
+      {K::ReluBwd, make_relu_bwd_f16_variant, 30, "relu_bwd_f16_vec2_v0"},
+      {K::ReluBwd, make_relu_bwd_f16_variant, 20, "relu_bwd_f16_v0"},
+      {K::ReluBwd, make_relu_bwd_f32_variant, 0, "relu_bwd_f32_v0"},
+      {K::SgdStep, make_sgd_step_f16_variant, 30, "sgd_step_f16_half2_v0"},
+      {K::SgdStep, make_sgd_step_f16_variant, 20, "sgd_step_f16_v0"},
+      {K::SgdStep, make_sgd_step_f32_variant, 0, "sgd_step_f32_v0"},
+      {K::Copy, make_copy_f16_variant, 20, "copy_f16_v0"},
+      {K::Copy, make_copy_f32_variant, 0, "copy_f32_v0"},
+      {K::GradZero, make_grad_zero_variant, 0, "grad_zero_v0"},
+      {K::AdamStep, make_adam_step_f32_variant, 0, "adam_step_f32_v0"},
+      {K::StepInc, make_step_inc_variant, 0, "step_inc_v0"},
+      {K::BiasCorr, make_biascorr_variant, 0, "bias_corr_v0"},
+
+      // ---- additions: bf16 everywhere, fp32-output contractions, new ops ----
+      {K::ReduceSum, make_reduce_sum_lastdim_bf16_variant, 95, "reduce_sum_keep_lastdim_bf16_v0"},
+      {K::ReduceSum, make_reduce_sum_lastdim_bf16_to_f32_variant, 90, "reduce_sum_keep_lastdim_bf16_to_f32_v0"},
+      {K::ReduceSum, make_reduce_sum_lastaxis_f32_variant, 50, "reduce_sum_lastaxis_f32_v0"},
+      {K::ReduceSum, make_reduce_sum_lastaxis_bf16_variant, 50, "reduce_sum_lastaxis_bf16_v0"},
+      {K::ReduceSum, make_reduce_sum_lastaxis_f16_variant, 50, "reduce_sum_lastaxis_f16_v0"},
+      {K::ReduceMax, make_reduce_max_lastaxis_f32_variant, 0, "reduce_max_lastaxis_f32_v0"},
+      {K::ReduceMax, make_reduce_max_lastaxis_bf16_variant, 0, "reduce_max_lastaxis_bf16_v0"},
+      {K::ReduceMax, make_reduce_max_lastaxis_f16_variant, 0, "reduce_max_lastaxis_f16_v0"},
+      {K::ReduceMean, make_reduce_mean_lastaxis_f32_variant, 0, "reduce_mean_lastaxis_f32_v0"},
+      {K::ReduceMean, make_reduce_mean_lastaxis_bf16_variant, 0, "reduce_mean_lastaxis_bf16_v0"},
+      {K::ReduceMean, make_reduce_mean_lastaxis_f16_variant, 0, "reduce_mean_lastaxis_f16_v0"},
+      {K::Gemm, make_gemm_bf16_tcgen05_out_bf16_variant, 25, "gemm_bf16_tcgen05_out_bf16_v0"},
+      {K::Gemm, make_gemm_bf16_tcgen05_out_f32_variant, 24, "gemm_bf16_tcgen05_out_f32_v0"},
+      {K::Gemm, make_gemm_f16_tcgen05_out_f16_variant, 19, "gemm_f16_tcgen05_out_f16_v0"},
+      {K::Gemm, make_gemm_f16_tcgen05_out_f32_variant, 18, "gemm_f16_tcgen05_out_f32_v0"},
+      {K::GemmEpilogue, make_gemm_bias_relu_bf16_tcgen05_out_bf16_variant, 25, "gemm_bias_relu_bf16_tcgen05_out_bf16_v0"},
+      {K::GemmEpilogue, make_gemm_bias_relu_bf16_tcgen05_out_f32_variant, 24, "gemm_bias_relu_bf16_tcgen05_out_f32_v0"},
+      {K::GemmEpilogue, make_gemm_bias_relu_f16_tcgen05_out_f16_variant, 19, "gemm_bias_relu_f16_tcgen05_out_f16_v0"},
+      {K::BiasAdd, make_bias_add_bf16_variant, 25, "bias_add_bf16_v0"},
+      {K::EltwiseAdd, make_add_bf16_variant, 25, "add_bf16_v0"},
+      {K::EltwiseRelu, make_relu_bf16_variant, 25, "relu_bf16_v0"},
+      {K::MseGrad, make_mse_grad_bf16_variant, 15, "mse_grad_bf16_v0"},
+      {K::ReluBwd, make_relu_bwd_bf16_variant, 25, "relu_bwd_bf16_v0"},
+      {K::SgdStep, make_sgd_step_bf16_variant, 25, "sgd_step_bf16_v0"},
+      {K::Copy, make_copy_bf16_variant, 15, "copy_bf16_v0"},
+      {K::Copy, make_copy_i32_variant, 10, "copy_i32_v0"},
+      {K::AdamStep, make_adam_step_f32_fused_variant, -10, "adam_step_f32_fused_v1"},
+      {K::Softmax, make_softmax_lastdim_f32_variant, 0, "softmax_lastdim_f32_v0"},
+      {K::Softmax, make_softmax_lastdim_bf16_variant, 0, "softmax_lastdim_bf16_v0"},
+      {K::Softmax, make_softmax_lastdim_f16_variant, 0, "softmax_lastdim_f16_v0"},
+      {K::SoftmaxCE, make_softmax_ce_f32_variant, 0, "softmax_ce_f32_i32_v0"},
+      {K::SoftmaxCE, make_softmax_ce_bf16_variant, 0, "softmax_ce_bf16_i32_v0"},
+      {K::SoftmaxCE, make_softmax_ce_f16_variant, 0, "softmax_ce_f16_i32_v0"},
+      {K::Cast, make_cast_variant, 0, "cast_v0"},
+      {K::AllReduce, make_all_reduce_nccl_f32_variant, 0, "all_reduce_nccl_f32_v0"},
+  };
+
+  KernelRegistry& reg = KernelRegistry::instance();
+  for (const Row& r : kRows) {
+    KernelVariant v = r.factory();
+    v.priority = r.priority;
+    v.kernel_id = r.id;
+    reg.register_kernel(r.kind, v);
+  }
+}

@@ -1,0 +1,58 @@
+#pragma once
+// Kernel registry: per-OpKind priority-ordered variant table plus a by-id index
+// (reference: registry.hpp:16-60, registry.cpp:66-142).
+#include <cstdint>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+#include <cuda_runtime.h>
+
+#include "aicf/backends/cuda/registry/kernel_variant.hpp"
+#include "aicf/backends/cuda/registry/op_kind.hpp"
+#include "aicf/backends/cuda/registry/status.hpp"
+#include "aicf/backends/cuda/registry/tensor_desc.hpp"
+
+namespace aicf::cuda {
+
+struct OpCall {
+  OpKind kind{};
+  const TensorDesc* inputs = nullptr;
+  int32_t num_inputs = 0;
+  TensorDesc* outputs = nullptr;
+  int32_t num_outputs = 0;
+  const void* attrs = nullptr;  // nullptr or AttrBlob*
+  cudaStream_t stream = nullptr;
+};
+
+class KernelRegistry {
+ public:
+  static KernelRegistry& instance();
+
+  // Thread-safe. Variants without a kernel_id are ignored; the first registration of an id wins.
+  void register_kernel(OpKind kind, KernelVariant v);
+
+  // Stable pointers, taken under the lock so supported()/launch() run without it.
+  void variants_snapshot(OpKind kind, std::vector<const KernelVariant*>& out) const;
+
+  const KernelVariant* find_by_id(OpKind kind, const char* kernel_id) const;
+
+  static void ensure_registered();
+
+ private:
+  KernelRegistry() = default;
+  static constexpr int kKinds = static_cast<int>(OpKind::_Count);
+  std::vector<std::unique_ptr<KernelVariant>> table_[kKinds];
+  std::unordered_map<std::string, const KernelVariant*> by_id_[kKinds];
+  mutable std::mutex mu_;
+};
+
+// Legacy runtime dispatch: first supported variant in priority order.
+Status Dispatch(const OpCall& call);
+
+// Scratch arena used by dispatch for variants whose query_workspace() is non-zero.
+// A caller-provided arena replaces the lazily allocated default (ptr == nullptr restores it).
+void set_dispatch_workspace(void* ptr, size_t bytes);
+
+}  // namespace aicf::cuda

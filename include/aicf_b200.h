@@ -1,0 +1,206 @@
+/* aicf_b200.h - C ABI of the B200 (sm_100a) backend.
+ *
+ * Plain C: pointers, sizes and integers only. Every function returns an aicf status code
+ * (0 Ok, 1 InvalidArgument, 2 NotImplemented, 3 Internal) unless stated otherwise, never throws,
+ * and - apart from the helpers in the "device memory" and "plan" sections - neither allocates nor
+ * synchronises: a launch only enqueues work on the given stream.
+ *
+ * Each entry point names the interface of the reference project (jeehun98/ai-compiler-framework,
+ * paths relative to its ai-compiler-framework/ directory) that it stands in for.
+ */
+#ifndef AICF_B200_H_
+#define AICF_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AICF_B200_ABI_VERSION 1
+
+/* ---- handle types ---------------------------------------------------------------------------
+ * Bit-compatible with aicf::cuda::TensorDesc (include/aicf/backends/cuda/registry/tensor_desc.hpp:88-104,
+ * sizeof 96) and aicf::cuda::AttrBlob (attr_blob.hpp:13-17, sizeof 16). */
+enum { AICF_DTYPE_UNKNOWN = 0, AICF_DTYPE_F32 = 1, AICF_DTYPE_F16 = 2, AICF_DTYPE_BF16 = 3, AICF_DTYPE_I32 = 4 };
+enum { AICF_OK = 0, AICF_INVALID_ARGUMENT = 1, AICF_NOT_IMPLEMENTED = 2, AICF_INTERNAL = 3 };
+
+typedef struct aicf_tensor_desc {
+  void* data;        /* device pointer, borrowed */
+  uint8_t dtype;     /* AICF_DTYPE_* */
+  int32_t rank;      /* 0 = scalar, at most 4 */
+  int64_t shape[4];  /* elements */
+  int64_t stride[4]; /* elements */
+  uint8_t contiguous;
+  int32_t alignment; /* bytes, 0 = unknown */
+  int32_t device;
+} aicf_tensor_desc;
+
+typedef struct aicf_attr_blob {
+  uint32_t schema_id; /* 0 = op defaults */
+  uint32_t bytes;
+  const void* data; /* little-endian POD payload */
+} aicf_attr_blob;
+
+/* A CUDA stream handle (cudaStream_t) passed as an integer; 0 = the legacy default stream.
+ * Reference: the uint64 stream argument of _C.op_call / _C.launch_by_id
+ * (src/python_bindings/bindings.cpp:272,295-297). */
+typedef uint64_t aicf_stream;
+
+/* ---- library ------------------------------------------------------------------------------- */
+int aicf_b200_abi_version(void);
+/* Name of a status code. Reference: status_to_string (registry/status.hpp:15-23). */
+const char* aicf_b200_status_string(int status);
+/* Text of the most recent failure on the calling thread ("" if none). */
+const char* aicf_b200_last_error(void);
+/* Lower-case op name of an OpKind value, "unknown" if out of range.
+ * Reference: opkind_to_name (src/python_bindings/bindings.cpp:196-219). */
+const char* aicf_b200_op_name(int op_kind);
+
+/* ---- dispatch ------------------------------------------------------------------------------
+ * Replaces aicf::cuda::dispatch_v0 (include/aicf/backends/cuda/registry/dispatch.hpp:12-17;
+ * src/backends/cuda/registry/registry.cpp:144-215): first supported variant in priority order. */
+int aicf_b200_op_call(int op_kind, const aicf_tensor_desc* inputs, int num_inputs, aicf_tensor_desc* outputs,
+                      int num_outputs, const aicf_attr_blob* attr /* may be NULL */, aicf_stream stream);
+
+/* Replaces aicf::cuda::dispatch_by_id_v0 (dispatch.hpp:19-26; registry.cpp:16-64): the variant
+ * pinned by its kernel id. Unknown id -> NotImplemented; contract mismatch -> InvalidArgument. */
+int aicf_b200_launch_by_id(const char* kernel_id, int op_kind, const aicf_tensor_desc* inputs, int num_inputs,
+                           aicf_tensor_desc* outputs, int num_outputs, const aicf_attr_blob* attr,
+                           aicf_stream stream);
+
+/* The three function pointers of a KernelVariant (kernel_variant.hpp:44-61), addressed by id.
+ * launch_ws passes caller-owned scratch straight to KernelVariant::launch. */
+int aicf_b200_supported(const char* kernel_id, int op_kind, const aicf_tensor_desc* inputs, int num_inputs,
+                        const aicf_tensor_desc* outputs, int num_outputs, const aicf_attr_blob* attr); /* 1/0 */
+size_t aicf_b200_query_workspace(const char* kernel_id, int op_kind, const aicf_tensor_desc* inputs, int num_inputs,
+                                 const aicf_attr_blob* attr);
+int aicf_b200_launch_ws(const char* kernel_id, int op_kind, const aicf_tensor_desc* inputs, int num_inputs,
+                        aicf_tensor_desc* outputs, int num_outputs, const aicf_attr_blob* attr, void* workspace,
+                        size_t workspace_bytes, aicf_stream stream);
+
+/* Scratch arena used by op_call / launch_by_id for variants that need workspace (the reference refuses
+ * such variants, registry.cpp:52-56). NULL restores the library-owned arena, which is allocated on
+ * first need and never while the target stream is capturing. */
+int aicf_b200_set_workspace(void* ptr, size_t bytes);
+
+/* Registry introspection. Reference: KernelRegistry::variants_snapshot / find_by_id
+ * (registry.hpp:38-41); ids are those of register_all.cpp:105-291 plus this backend's additions. */
+int aicf_b200_kernel_count(int op_kind);
+const char* aicf_b200_kernel_id(int op_kind, int index); /* priority order; NULL past the end */
+int aicf_b200_num_op_kinds(void);
+
+/* Status word of the tcgen05 GEMM's bounded waits: 0 = no wait ever expired. Synchronises the
+ * device. No counterpart in the reference (its kernels have no device-side waits). */
+int aicf_b200_gemm_status(int clear);
+
+/* ---- op trace ------------------------------------------------------------------------------
+ * Replaces trace_enable / trace_reset / trace_get of the reference binding
+ * (src/python_bindings/bindings.cpp:193-231,459-472). Entries are "<opname>" for op_call and
+ * "kid:<id> kind:<opname>" for launch_by_id. Enabled by default; kept in a bounded ring (the newest
+ * AICF_B200_TRACE_CAPACITY entries). Only the *_traced launch functions record. */
+#define AICF_B200_TRACE_CAPACITY 65536
+void aicf_b200_trace_enable(int flag);
+void aicf_b200_trace_reset(void);
+int aicf_b200_trace_count(void);
+const char* aicf_b200_trace_get(int index); /* valid until the next trace call on any thread */
+int aicf_b200_op_call_traced(int op_kind, const aicf_tensor_desc* inputs, int num_inputs, aicf_tensor_desc* outputs,
+                             int num_outputs, const aicf_attr_blob* attr, aicf_stream stream);
+int aicf_b200_launch_by_id_traced(const char* kernel_id, int op_kind, const aicf_tensor_desc* inputs, int num_inputs,
+                                  aicf_tensor_desc* outputs, int num_outputs, const aicf_attr_blob* attr,
+                                  aicf_stream stream);
+
+/* ---- process-global CUDA graph ---------------------------------------------------------------
+ * Replaces graph_begin / graph_end / graph_launch / graph_reset / graph_stream
+ * (src/python_bindings/bindings.cpp:137-187,475-547): one graph at a time, captured on and launched
+ * into a dedicated non-blocking stream. graph_begin stores the capture stream in *stream_out. */
+int aicf_b200_graph_begin(aicf_stream* stream_out);
+int aicf_b200_graph_end(void);    /* InvalidArgument + "graph_end called but not capturing" */
+int aicf_b200_graph_launch(void); /* InvalidArgument + "graph_launch called but no captured graph exists" */
+int aicf_b200_graph_reset(void);
+aicf_stream aicf_b200_graph_stream(void); /* 0 before the first graph_begin */
+
+/* ---- device memory / streams / events (host plumbing for callers without a tensor library) -----
+ * The reference borrows all of this from torch (torch.empty, Tensor.copy_, torch.cuda.synchronize);
+ * these are thin wrappers over the CUDA runtime. */
+int aicf_b200_device_count(void);
+int aicf_b200_set_device(int device);
+int aicf_b200_malloc(void** ptr, size_t bytes);
+int aicf_b200_free(void* ptr);
+int aicf_b200_host_alloc_pinned(void** ptr, size_t bytes);
+int aicf_b200_host_free_pinned(void* ptr);
+int aicf_b200_memcpy_h2d(void* dst, const void* src, size_t bytes, aicf_stream stream); /* async on `stream` */
+int aicf_b200_memcpy_d2h(void* dst, const void* src, size_t bytes, aicf_stream stream);
+int aicf_b200_memcpy_d2d(void* dst, const void* src, size_t bytes, aicf_stream stream);
+int aicf_b200_memset(void* dst, int value, size_t bytes, aicf_stream stream);
+int aicf_b200_stream_create(aicf_stream* out);
+int aicf_b200_stream_destroy(aicf_stream s);
+int aicf_b200_stream_sync(aicf_stream s);
+int aicf_b200_device_sync(void);
+int aicf_b200_event_create(uint64_t* out);
+int aicf_b200_event_destroy(uint64_t ev);
+int aicf_b200_event_record(uint64_t ev, aicf_stream s);
+int aicf_b200_event_sync(uint64_t ev);
+int aicf_b200_event_elapsed_ms(uint64_t start, uint64_t stop, float* ms);
+int aicf_b200_stream_wait_event(aicf_stream s, uint64_t ev);
+
+/* ---- captured execution plan ------------------------------------------------------------------
+ * C++ replacement of the reference's Python executor: build_binding_plan / allocate_static_env
+ * (python/aicf_fw/core_v2/plan.py:90-137,174-209) and PlannedExecutor.run / capture / replay /
+ * reset_graph (python/aicf_fw/core_v2/exec.py:337-497). A plan is built from the lowered-op list
+ * (op name, input/output value ids, attr payload, optional kernel id; lower.py:9-21):
+ *   values with role INPUT or PARAM live in caller- or plan-owned pointer-stable buffers,
+ *   STATIC values are carved from one arena with liveness-based reuse,
+ *   kernel variants, attr payloads and workspace slices are resolved once at finalize().
+ * run() enqueues every op; capture() records them into a CUDA graph; replay(n) launches the graph
+ * n times with no host work in between. */
+typedef struct aicf_plan aicf_plan;
+enum { AICF_ROLE_INPUT = 0, AICF_ROLE_PARAM = 1, AICF_ROLE_STATIC = 2 };
+
+aicf_plan* aicf_b200_plan_create(const char* name);
+void aicf_b200_plan_destroy(aicf_plan* plan);
+/* Declares value `vid`. persistent != 0 keeps a STATIC value out of arena reuse (optimizer state,
+ * anything read after the step). zero_init != 0 clears it at finalize (opt.step / opt.m / opt.v,
+ * plan.py:160-171). */
+int aicf_b200_plan_add_value(aicf_plan* plan, int vid, const char* name, int dtype, int rank, const int64_t* shape,
+                             int role, int persistent, int zero_init);
+/* Appends a lowered op. kernel_id NULL -> the variant is chosen by priority at finalize. */
+int aicf_b200_plan_add_op(aicf_plan* plan, const char* op_name, const char* kernel_id, const int* inputs,
+                          int num_inputs, const int* outputs, int num_outputs, uint32_t schema_id,
+                          const void* attr_bytes, uint32_t attr_len);
+/* Makes `vid` an alias of `target_vid` (same buffer). Used to drop copy_saved ops. */
+int aicf_b200_plan_alias(aicf_plan* plan, int vid, int target_vid);
+/* Binds a value to caller-owned device memory (must outlive the plan and stay at that address). */
+int aicf_b200_plan_bind(aicf_plan* plan, int vid, void* device_ptr);
+/* Allocates the arena and every unbound value, resolves variants. No ops may be added afterwards. */
+int aicf_b200_plan_finalize(aicf_plan* plan);
+void* aicf_b200_plan_value_ptr(aicf_plan* plan, int vid);
+size_t aicf_b200_plan_value_bytes(aicf_plan* plan, int vid);
+size_t aicf_b200_plan_arena_bytes(aicf_plan* plan);        /* bytes actually allocated for STATIC values */
+size_t aicf_b200_plan_arena_bytes_no_reuse(aicf_plan* plan); /* what one buffer per value would need */
+int aicf_b200_plan_num_ops(aicf_plan* plan);
+const char* aicf_b200_plan_op_kernel_id(aicf_plan* plan, int op_index);
+int aicf_b200_plan_run(aicf_plan* plan, aicf_stream stream); /* eager: one launch per op */
+int aicf_b200_plan_capture(aicf_plan* plan);                 /* graph on the plan's own stream */
+int aicf_b200_plan_replay(aicf_plan* plan, int n);           /* n graph launches, no sync */
+int aicf_b200_plan_reset_graph(aicf_plan* plan);
+aicf_stream aicf_b200_plan_stream(aicf_plan* plan);
+int aicf_b200_plan_sync(aicf_plan* plan);
+int aicf_b200_plan_graph_nodes(aicf_plan* plan); /* kernel/memset/memcpy nodes in the captured graph, -1 if none */
+
+/* ---- data-parallel gradient exchange -------------------------------------------------------------
+ * No counterpart in the reference (single device, bindings.cpp:123). One process per GPU; rank 0
+ * creates a 128-byte id, every rank calls dp_init with it. all_reduce ops (OpKind 22) then sum fp32
+ * buffers in place over the ranks with NCCL on the launch stream. */
+int aicf_b200_dp_unique_id(void* id128);
+int aicf_b200_dp_init(int rank, int world_size, const void* id128);
+int aicf_b200_dp_finalize(void);
+int aicf_b200_dp_world_size(void); /* 1 when not initialised */
+int aicf_b200_dp_rank(void);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* AICF_B200_H_ */

@@ -14,7 +14,7 @@
 // contiguous dimension is M/N instead of K is loaded as 64x64 boxes and described to the MMA as
 // "MN-major" through the shared-memory and instruction descriptors.
 //
-// Every wait is bounded: after ~2 s without progress a role raises the CTA's abort flag, records a
+// Every wait is bounded: after ~1 s without progress a role raises the CTA's abort flag, records a
 // code in the device status word, everybody leaves their loops, tensor memory is released and the
 // kernel returns normally. The host reads the word through gemm_tcgen05_status().
 #include <cuda.h>
@@ -38,7 +38,7 @@ constexpr int kAccBufs = 2;
 constexpr int kTmemCols = 512;
 constexpr int kThreads = 192;
 constexpr int kGroupM = 16;   // tile rasterisation: 16 row-tiles share their column tiles in L2
-constexpr unsigned long long kWaitBudgetNs = 2000000000ull;
+constexpr unsigned long long kWaitBudgetNs = 1000000000ull;
 
 constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + 256 /*barriers etc.*/;
 
@@ -133,14 +133,14 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"  // same asm statement: the registers are not readable before the wait
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
@@ -286,7 +286,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
       const int row = tm * kTileM + sub * 32 + lane;
       const int n0 = tn * kTileN;
-      if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, 4)) { alive = false; break; }
+      // the TMEM loads below are warp-collective: the whole warp proceeds or the whole warp leaves
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, 4))) { alive = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * kTileN;
 #pragma unroll 1

@@ -190,12 +190,14 @@ size_t assign_arena(std::vector<Value*>& vals, int num_ops, std::map<int, size_t
   return top;
 }
 
-int enqueue_all(aicf_plan* p, cudaStream_t main) {
+int enqueue_all(aicf_plan* p, cudaStream_t main, std::vector<cudaEvent_t>* marks = nullptr) {
   // vid -> event a later op on `main` must wait for (pending all_reduce on the comm stream)
   std::map<int, cudaEvent_t> pending;
-  const bool overlap = aicf_b200_dp_world_size() > 1;
+  const bool overlap = aicf_b200_dp_world_size() > 1 && !marks;
   for (size_t i = 0; i < p->ops.size(); ++i) {
     Op& op = p->ops[i];
+    if (marks)
+      if (int rc = check_cuda(cudaEventRecord((*marks)[i], main), "cudaEventRecord(profile)")) return rc;
     auto wait_for = [&](int vid) -> int {
       Value* v = p->resolve(vid);
       if (!v) return AICF_OK;
@@ -235,6 +237,8 @@ int enqueue_all(aicf_plan* p, cudaStream_t main) {
   }
   for (auto& kv : pending)  // every forked branch rejoins before the step ends
     if (int rc = check_cuda(cudaStreamWaitEvent(main, kv.second, 0), "cudaStreamWaitEvent(final join)")) return rc;
+  if (marks)
+    if (int rc = check_cuda(cudaEventRecord(marks->back(), main), "cudaEventRecord(profile)")) return rc;
   return AICF_OK;
 }
 
@@ -527,6 +531,43 @@ int aicf_b200_plan_graph_nodes(aicf_plan* p) {
     return -1;
   }
   return static_cast<int>(n);
+}
+
+int aicf_b200_plan_graph_kernel_nodes(aicf_plan* p) {
+  if (!p || !p->graph) return -1;
+  size_t n = 0;
+  if (cudaGraphGetNodes(p->graph, nullptr, &n) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  std::vector<cudaGraphNode_t> nodes(n);
+  if (n && cudaGraphGetNodes(p->graph, nodes.data(), &n) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  int kernels = 0;
+  for (cudaGraphNode_t nd : nodes) {
+    cudaGraphNodeType t;
+    if (cudaGraphNodeGetType(nd, &t) == cudaSuccess && t == cudaGraphNodeTypeKernel) ++kernels;
+  }
+  return kernels;
+}
+
+int aicf_b200_plan_profile(aicf_plan* p, float* ms_per_op, int capacity) {
+  if (!p || !p->finalized || !ms_per_op) return fail(Status::InvalidArgument, "plan_profile: plan not finalized or null output");
+  const size_t n = p->ops.size();
+  if (capacity < static_cast<int>(n)) return fail(Status::InvalidArgument, "plan_profile: output too small");
+  std::vector<cudaEvent_t> marks(n + 1, nullptr);
+  int rc = AICF_OK;
+  for (auto& e : marks)
+    if (rc == AICF_OK) rc = check_cuda(cudaEventCreate(&e), "cudaEventCreate(profile)");
+  if (rc == AICF_OK) rc = enqueue_all(p, p->stream, &marks);
+  if (rc == AICF_OK) rc = check_cuda(cudaStreamSynchronize(p->stream), "cudaStreamSynchronize(profile)");
+  for (size_t i = 0; i < n && rc == AICF_OK; ++i)
+    rc = check_cuda(cudaEventElapsedTime(&ms_per_op[i], marks[i], marks[i + 1]), "cudaEventElapsedTime(profile)");
+  for (auto& e : marks)
+    if (e) cudaEventDestroy(e);
+  return rc;
 }
 
 }  // extern "C"

@@ -1,0 +1,15 @@
+"""aicf_cuda: B200 (sm_100a) op backend and captured-plan hot path behind the reference's interfaces.
+
+`aicf_cuda._C` is the drop-in binding module; `aicf_cuda.Plan` is the C++ captured plan;
+`aicf_cuda.Tensor` is a NumPy-only device buffer for callers that do not use torch.
+"""
+from . import _C
+from ._lib import LIB_PATH, lib
+from .lowering import build_mlp_train_step
+from .plan import (ROLE_INPUT, ROLE_PARAM, ROLE_STATIC, Plan, ValueSpec, classify_role, needs_zero_init, pack_attrs,
+                   pack_attrs_like_reference_executor)
+from .tensor import Tensor, bf16_bits_to_f32, f32_to_bf16_bits
+
+__all__ = ["_C", "lib", "LIB_PATH", "Plan", "ValueSpec", "Tensor", "build_mlp_train_step", "pack_attrs",
+           "pack_attrs_like_reference_executor", "classify_role", "needs_zero_init", "f32_to_bf16_bits",
+           "bf16_bits_to_f32", "ROLE_INPUT", "ROLE_PARAM", "ROLE_STATIC"]

@@ -1,0 +1,133 @@
+"""Builds the lowered-op list of an MLP train step (the contract the plan consumes).
+
+The op/attr vocabulary is the reference's (python/aicf_fw/core_v2/lower.py:24-147: Linear ->
+gemm{transB} + bias, LinearBwd -> gemm(dY,W), gemm(dY^T,X), reduce_sum(dY){axis 0}; Stage C fuses
+gemm + bias_add + relu into gemm_epilogue, rewrites/stageC_fuse_epilogue.py:22-74), extended with the
+ops this backend adds: softmax_ce as the loss, the fused Adam that reads the device step counter, bf16
+working copies of fp32 master weights, and all_reduce for data parallelism.
+
+Differences from what the reference's lowering would emit, all of them removing work:
+  * the activation saved for relu_bwd is the gemm_epilogue output itself (no copy_saved op),
+  * no dX for the first layer,
+  * the last Linear is a gemm_epilogue with relu off instead of gemm + bias_add.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Sequence, Tuple
+
+from .plan import ROLE_INPUT, ROLE_PARAM, ROLE_STATIC, ValueSpec
+
+
+def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str = "bf16", global_batch: int | None = None,
+                         lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
+                         weight_decay: float = 0.0, data_parallel: bool = False, with_argmax: bool = False,
+                         input_f32: bool = True) -> Tuple[List[ValueSpec], List[Dict[str, Any]]]:
+    """dims = [in, hidden..., out]. Every Linear but the last is followed by ReLU.
+
+    compute_dtype 'f32': GEMMs run on fp32 parameters directly.
+    compute_dtype 'bf16' / 'f16': parameters, gradients and Adam state stay fp32; GEMMs read 16-bit
+    working copies ('<i>.W.lp') which the fused Adam rewrites every step; activations are 16-bit.
+    The loss gradient is scaled by 1/global_batch so that summed shard gradients equal the
+    single-device gradient.
+    """
+    L = len(dims) - 1
+    assert L >= 1
+    cd = compute_dtype
+    mixed = cd != "f32"
+    gb = int(global_batch or batch)
+    vals: List[ValueSpec] = []
+    ops: List[Dict[str, Any]] = []
+    ids: Dict[str, int] = {}
+
+    def val(name, shape, dtype, role=None, persistent=False, zero=None) -> int:
+        vid = len(vals)
+        vals.append(ValueSpec(vid, name, tuple(shape), dtype, role, persistent, zero))
+        ids[name] = vid
+        return vid
+
+    def op(name, inputs, outputs, attrs=None, kid=None):
+        d: Dict[str, Any] = {"op": name, "inputs": list(inputs), "outputs": list(outputs), "attrs": dict(attrs or {})}
+        if kid:
+            d["kernel_id"] = kid
+        ops.append(d)
+
+    gemm_kid = {"f32": "gemm_f32_naive_v0", "bf16": "gemm_bf16_tcgen05_out_bf16_v0", "f16": "gemm_f16_tcgen05_out_f16_v0"}[cd]
+    gemm_f32out_kid = {"f32": "gemm_f32_naive_v0", "bf16": "gemm_bf16_tcgen05_out_f32_v0", "f16": "gemm_f16_tcgen05_out_f32_v0"}[cd]
+    epi_kid = {"f32": "gemm_bias_relu_f32_naive_v0", "bf16": "gemm_bias_relu_bf16_tcgen05_out_bf16_v0",
+               "f16": "gemm_bias_relu_f16_tcgen05_out_f16_v0"}[cd]
+    colsum_kid = {"f32": "reduce_sum_keep_lastdim_f32_v0", "bf16": "reduce_sum_keep_lastdim_bf16_to_f32_v0",
+                  "f16": "reduce_sum_keep_lastdim_f16_to_f32_v0"}[cd]
+    relu_bwd_kid = {"f32": "relu_bwd_f32_v0", "bf16": "relu_bwd_bf16_v0", "f16": "relu_bwd_f16_v0"}[cd]
+    ce_kid = {"f32": "softmax_ce_f32_i32_v0", "bf16": "softmax_ce_bf16_i32_v0", "f16": "softmax_ce_f16_i32_v0"}[cd]
+
+    # ---- inputs -------------------------------------------------------------------------------
+    if mixed and input_f32:
+        x_in = val("x", (batch, dims[0]), "f32", ROLE_INPUT)
+        x = val("x.lp", (batch, dims[0]), cd)
+        op("cast", [x_in], [x], kid="cast_v0")
+    else:
+        x = val("x", (batch, dims[0]), cd, ROLE_INPUT)
+    labels = val("labels", (batch,), "i32", ROLE_INPUT)
+
+    # ---- parameters and optimizer state ---------------------------------------------------------
+    W, b, Wlp, mW, vW, mb, vb = [], [], [], [], [], [], []
+    for i in range(L):
+        li = 2 * i  # reference naming: Sequential index of the Linear ("0.W", "2.W", ...)
+        W.append(val(f"{li}.W", (dims[i + 1], dims[i]), "f32", ROLE_PARAM))
+        b.append(val(f"{li}.b", (dims[i + 1],), "f32", ROLE_PARAM))
+        Wlp.append(val(f"{li}.W.lp", (dims[i + 1], dims[i]), cd, ROLE_STATIC, persistent=True) if mixed else W[-1])
+        mW.append(val(f"opt.m.{li}.W", (dims[i + 1], dims[i]), "f32", persistent=True))
+        vW.append(val(f"opt.v.{li}.W", (dims[i + 1], dims[i]), "f32", persistent=True))
+        mb.append(val(f"opt.m.{li}.b", (dims[i + 1],), "f32", persistent=True))
+        vb.append(val(f"opt.v.{li}.b", (dims[i + 1],), "f32", persistent=True))
+    step = val("opt.step", (1,), "i32", persistent=True)
+
+    # ---- forward ---------------------------------------------------------------------------------
+    acts = [x]
+    for i in range(L):
+        last = i == L - 1
+        name = "logits" if last else f"relu{i}_out"
+        h = val(name, (batch, dims[i + 1]), cd, persistent=last)
+        op("gemm_epilogue", [acts[-1], Wlp[i], b[i]], [h],
+           {"transB": True, "epilogue": "bias" if last else "bias_relu"}, epi_kid)
+        acts.append(h)
+    logits = acts[-1]
+
+    # ---- loss ------------------------------------------------------------------------------------
+    dlogits = val("d_logits", (batch, dims[-1]), cd)
+    loss_row = val("loss_row", (batch,), "f32")
+    loss = val("loss", (1,), "f32", persistent=True)
+    ce_out = [dlogits, loss_row]
+    if with_argmax:
+        ce_out.append(val("argmax", (batch,), "i32", persistent=True))
+    op("softmax_ce", [logits, labels], ce_out, {"scale": 1.0 / gb}, ce_kid)
+    op("reduce_mean", [loss_row], [loss], None, "reduce_mean_lastaxis_f32_v0")
+
+    # ---- backward ----------------------------------------------------------------------------------
+    dW, db = [None] * L, [None] * L
+    dY = dlogits
+    for i in reversed(range(L)):
+        li = 2 * i
+        dW[i] = val(f"d_{li}.W", (dims[i + 1], dims[i]), "f32")
+        db[i] = val(f"d_{li}.b", (dims[i + 1],), "f32")
+        op("gemm", [dY, acts[i]], [dW[i]], {"transA": True, "transB": False}, gemm_f32out_kid)
+        op("reduce_sum", [dY], [db[i]], {"axis": 0, "keepdim": False}, colsum_kid)
+        if data_parallel:
+            op("all_reduce", [dW[i]], [dW[i]], {"bucket": 2 * i}, "all_reduce_nccl_f32_v0")
+            op("all_reduce", [db[i]], [db[i]], {"bucket": 2 * i + 1}, "all_reduce_nccl_f32_v0")
+        if i > 0:
+            dX = val(f"d_relu{i - 1}_out", (batch, dims[i]), cd)
+            op("gemm", [dY, Wlp[i]], [dX], {"transA": False, "transB": False}, gemm_kid)
+            op("relu_bwd", [dX, acts[i]], [dX], None, relu_bwd_kid)  # in place: dX becomes d(pre-activation)
+            dY = dX
+
+    # ---- optimizer ---------------------------------------------------------------------------------
+    op("step_inc", [step], [step], None, "step_inc_v0")
+    hyper = {"lr": lr, "beta1": beta1, "beta2": beta2, "eps": eps}
+    if weight_decay:
+        hyper["weight_decay"] = weight_decay
+    for i in range(L):
+        outs = [W[i], mW[i], vW[i]] + ([Wlp[i]] if mixed else [])
+        op("adam_step", [W[i], dW[i], mW[i], vW[i], step], outs, hyper, "adam_step_f32_fused_v1")
+        op("adam_step", [b[i], db[i], mb[i], vb[i], step], [b[i], mb[i], vb[i]], hyper, "adam_step_f32_fused_v1")
+    return vals, ops

@@ -1,0 +1,246 @@
+"""Python face of the C++ captured plan (include/aicf_b200.h, "captured execution plan").
+
+Mirrors the reference's executor surface - PlannedExecutor.run / capture / replay / reset_graph
+(python/aicf_fw/core_v2/exec.py:455-497) and build_binding_plan's role rules
+(python/aicf_fw/core_v2/plan.py:65-74,101-112,160-171) - but the per-op loop, the buffers and the
+CUDA graph live in C++: Python only describes the lowered-op list once.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import re
+import struct
+from dataclasses import dataclass, field
+from typing import Any, Dict, Iterable, List, Optional, Sequence, Tuple
+
+from ._lib import check, lib
+from .tensor import DTYPE_CODES, Tensor
+
+ROLE_INPUT, ROLE_PARAM, ROLE_STATIC = 0, 1, 2
+
+# Attr schema tags: the contract is the numeric value (the reference spells some big-endian).
+SCHEMA_GEMM = 0x47454D4D
+SCHEMA_GEMM_EPILOGUE = 0x4750454C
+SCHEMA_REDUCE_SUM = 0x5253554D
+SCHEMA_ADAM = 0x4D414441
+SCHEMA_BIAS_CORR = 0x524F4342
+SCHEMA_SGD = 0x53444753
+SCHEMA_BIAS_ADD = 0x44444142
+SCHEMA_MSE_GRAD = 0x4745534D
+SCHEMA_SOFTMAX_CE = 0x45434D53
+SCHEMA_ALL_REDUCE = 0x44455241
+# What the reference's Python executor sends for gemm_epilogue (exec.py:215-217); the reference's C++
+# does not know this tag and silently applies its defaults.
+SCHEMA_GEPI_AS_SENT_BY_REFERENCE_EXECUTOR = int.from_bytes(b"GEPI", "little")
+
+
+def _relu_flag(attrs: Dict[str, Any]) -> int:
+    if "relu" in attrs:
+        return 1 if attrs["relu"] else 0
+    if "epilogue" in attrs:
+        return 0 if str(attrs["epilogue"]).strip().lower() in ("bias", "bias_only", "biasonly") else 1
+    if "epilogue_act" in attrs:
+        return 1 if str(attrs["epilogue_act"]).strip().lower() == "relu" else 0
+    return 1
+
+
+def pack_attrs(op: str, attrs: Optional[Dict[str, Any]]) -> Tuple[int, bytes]:
+    """(schema_id, payload) for every op that has a schema. Unlike the reference's _pack_attrs
+    (exec.py:263-277), which only packs gemm / gemm_epilogue / adam_step, nothing is dropped."""
+    op = str(op).strip().lower()
+    a = dict(attrs or {})
+    ta, tb = int(bool(a.get("transA", False))), int(bool(a.get("transB", False)))
+    if op == "gemm":
+        return SCHEMA_GEMM, struct.pack("<ii", ta, tb)
+    if op == "gemm_epilogue":
+        return SCHEMA_GEMM_EPILOGUE, struct.pack("<iii", ta, tb, _relu_flag(a))
+    if op == "reduce_sum":
+        return SCHEMA_REDUCE_SUM, struct.pack("<q", int(a.get("axis", 0)))
+    if op == "adam_step":
+        payload = struct.pack("<ffff", float(a.get("lr", 1e-3)), float(a.get("beta1", 0.9)),
+                              float(a.get("beta2", 0.999)), float(a.get("eps", 1e-8)))
+        if "weight_decay" in a or "decoupled" in a:
+            payload += struct.pack("<fI", float(a.get("weight_decay", 0.0)), 1 if a.get("decoupled", False) else 0)
+        return SCHEMA_ADAM, payload
+    if op == "bias_corr":
+        return SCHEMA_BIAS_CORR, struct.pack("<ff", float(a.get("beta1", 0.9)), float(a.get("beta2", 0.999)))
+    if op == "sgd_step" and "lr" in a:
+        return SCHEMA_SGD, struct.pack("<f", float(a["lr"]))
+    if op == "mse_grad" and "scale" in a:
+        return SCHEMA_MSE_GRAD, struct.pack("<f", float(a["scale"]))
+    if op == "bias_add" and "axis" in a:
+        return SCHEMA_BIAS_ADD, struct.pack("<q", int(a["axis"]))
+    if op == "softmax_ce" and "scale" in a:
+        return SCHEMA_SOFTMAX_CE, struct.pack("<f", float(a["scale"]))
+    if op == "all_reduce":
+        return SCHEMA_ALL_REDUCE, struct.pack("<i", int(a.get("bucket", 0)))
+    return 0, b""
+
+
+def pack_attrs_like_reference_executor(op: str, attrs: Optional[Dict[str, Any]]) -> Tuple[int, bytes]:
+    """Bit-for-bit what the reference's exec.py:_pack_attrs emits (for strict-parity comparisons):
+    gemm -> schema 0 <ii>; gemm_epilogue -> 'GEPI' <iii>(ta,tb,kind); adam_step -> 'ADAM' <ffff>;
+    every other op -> no attrs."""
+    op = str(op).strip().lower()
+    a = dict(attrs or {})
+    ta, tb = int(bool(a.get("transA", False))), int(bool(a.get("transB", False)))
+    if op == "gemm":
+        return 0, struct.pack("<ii", ta, tb)
+    if op == "gemm_epilogue":
+        epi = str(a.get("epilogue", "bias_relu")).strip().lower()
+        kind = 1 if epi in ("bias", "bias_only", "biasonly") else 2 if epi in ("relu", "relu_only", "reluonly") else 0
+        return SCHEMA_GEPI_AS_SENT_BY_REFERENCE_EXECUTOR, struct.pack("<iii", ta, tb, kind)
+    if op == "adam_step":
+        return SCHEMA_ADAM, struct.pack("<ffff", float(a.get("lr", 1e-3)), float(a.get("beta1", 0.9)),
+                                        float(a.get("beta2", 0.999)), float(a.get("eps", 1e-8)))
+    return 0, b""
+
+
+_PARAM_RE = re.compile(r"^\d+\.(W|b)$")
+
+
+def classify_role(name: str) -> int:
+    """Role of a value from its name, as the reference's binding plan decides it:
+    'x' / 't' (and 'labels' for the cross-entropy graphs) are inputs, '<n>.W' / '<n>.b' are
+    parameters, everything else is a plan-owned static."""
+    if name in ("x", "t", "labels"):
+        return ROLE_INPUT
+    if _PARAM_RE.match(name):
+        return ROLE_PARAM
+    return ROLE_STATIC
+
+
+def needs_zero_init(name: str) -> bool:
+    return name.startswith("opt.step") or name.startswith("opt.m.") or name.startswith("opt.v.")
+
+
+@dataclass
+class ValueSpec:
+    vid: int
+    name: str
+    shape: Tuple[int, ...]
+    dtype: str
+    role: Optional[int] = None        # None -> classify_role(name)
+    persistent: bool = False          # keep out of arena reuse (read after the step)
+    zero_init: Optional[bool] = None  # None -> needs_zero_init(name)
+    alias_of: Optional[int] = None
+
+
+class Plan:
+    """A finalized execution plan. Buffers are pointer-stable for the plan's lifetime."""
+
+    def __init__(self, name: str, values: Iterable[ValueSpec], lowered: Sequence[Dict[str, Any]],
+                 bind: Optional[Dict[int, Any]] = None, attr_packer=pack_attrs):
+        self._h = lib.aicf_b200_plan_create(name.encode())
+        if not self._h:
+            raise RuntimeError("plan_create failed")
+        self.name = name
+        self.values: Dict[int, ValueSpec] = {}
+        self.by_name: Dict[str, int] = {}
+        self.lowered = [dict(it) for it in lowered]
+        self._keep: List[Any] = []
+        for v in values:
+            role = classify_role(v.name) if v.role is None else v.role
+            zero = needs_zero_init(v.name) if v.zero_init is None else v.zero_init
+            shape = (C.c_int64 * max(len(v.shape), 1))(*v.shape)
+            check(lib.aicf_b200_plan_add_value(self._h, v.vid, v.name.encode(), DTYPE_CODES[v.dtype], len(v.shape),
+                                               shape, role, int(v.persistent), int(zero)), "plan_add_value")
+            self.values[v.vid] = v
+            self.by_name[v.name] = v.vid
+        for v in self.values.values():
+            if v.alias_of is not None:
+                check(lib.aicf_b200_plan_alias(self._h, v.vid, v.alias_of), "plan_alias")
+        for vid, t in (bind or {}).items():
+            check(lib.aicf_b200_plan_bind(self._h, int(vid), int(t.data_ptr())), "plan_bind")
+            self._keep.append(t)
+        for it in self.lowered:
+            op = str(it["op"])
+            ins = [int(x) for x in it.get("inputs", [])]
+            outs = [int(x) for x in it.get("outputs", [])]
+            schema, payload = attr_packer(op, it.get("attrs"))
+            kid = it.get("kernel_id")
+            check(lib.aicf_b200_plan_add_op(
+                self._h, op.encode(), kid.encode() if kid else None,
+                (C.c_int * max(len(ins), 1))(*ins), len(ins), (C.c_int * max(len(outs), 1))(*outs), len(outs),
+                schema, payload if payload else None, len(payload)), "plan_add_op")
+        check(lib.aicf_b200_plan_finalize(self._h), "plan_finalize")
+        self._captured = False
+
+    # ---- buffers -------------------------------------------------------------------------------
+    def vid(self, key) -> int:
+        return self.by_name[key] if isinstance(key, str) else int(key)
+
+    def tensor(self, key) -> Tensor:
+        """Non-owning view of a value's device buffer (valid while the plan lives)."""
+        vid = self.vid(key)
+        spec = self.values[vid]
+        ptr = lib.aicf_b200_plan_value_ptr(self._h, vid)
+        if not ptr:
+            raise KeyError(f"value {key!r} has no buffer")
+        t = Tensor(spec.shape, spec.dtype, ptr=ptr)
+        t._base = self
+        return t
+
+    @property
+    def arena_bytes(self) -> int:
+        return int(lib.aicf_b200_plan_arena_bytes(self._h))
+
+    @property
+    def arena_bytes_no_reuse(self) -> int:
+        return int(lib.aicf_b200_plan_arena_bytes_no_reuse(self._h))
+
+    @property
+    def stream(self) -> int:
+        return int(lib.aicf_b200_plan_stream(self._h))
+
+    def kernel_ids(self) -> List[str]:
+        return [lib.aicf_b200_plan_op_kernel_id(self._h, i).decode() for i in range(lib.aicf_b200_plan_num_ops(self._h))]
+
+    # ---- execution (names follow PlannedExecutor) --------------------------------------------------
+    def run(self, stream: int = 0) -> None:
+        """Eager step: one launch per lowered op on the plan's stream (or `stream`)."""
+        check(lib.aicf_b200_plan_run(self._h, int(stream)), "plan_run")
+
+    def capture(self) -> None:
+        check(lib.aicf_b200_plan_capture(self._h), "plan_capture")
+        self._captured = True
+
+    def replay(self, n: int = 1) -> None:
+        if n <= 0:
+            return
+        if not self._captured:
+            raise RuntimeError("[exec] replay called before capture()")
+        check(lib.aicf_b200_plan_replay(self._h, int(n)), "plan_replay")
+
+    def reset_graph(self) -> None:
+        check(lib.aicf_b200_plan_reset_graph(self._h), "plan_reset_graph")
+        self._captured = False
+
+    def sync(self) -> None:
+        check(lib.aicf_b200_plan_sync(self._h), "plan_sync")
+
+    @property
+    def graph_nodes(self) -> int:
+        return int(lib.aicf_b200_plan_graph_nodes(self._h))
+
+    @property
+    def graph_kernel_nodes(self) -> int:
+        return int(lib.aicf_b200_plan_graph_kernel_nodes(self._h))
+
+    def profile(self) -> List[float]:
+        """One eager step with an event pair around every op; returns milliseconds per lowered op."""
+        n = len(self.lowered)
+        buf = (C.c_float * max(n, 1))()
+        check(lib.aicf_b200_plan_profile(self._h, buf, n), "plan_profile")
+        return [float(buf[i]) for i in range(n)]
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            lib.aicf_b200_plan_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,540 @@
+#!/usr/bin/env python
+"""Benchmark of the op backend + captured-plan hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload mlp|gemm|gemm_f32|softmax|ce|reduce|adam]
+                    [--impl reference] [--small]
+
+Default workload `mlp`: the data-parallel captured MLP train step (4x Linear(8192->8192)+ReLU ->
+Linear(8192->1000), bf16 GEMMs over fp32 master weights, softmax cross-entropy, fused Adam, global batch
+65536 split over the ranks, CUDA-graph replay). One "step" = one replay of the captured graph. Prints ONE
+JSON line on rank 0. Under torchrun (N > 1) every rank drives one GPU; gradients are summed by NCCL
+all-reduce nodes inside the graph.
+
+`--impl reference`: the reference project has no CPU implementation and none of the ops this workload
+needs beyond its f16/f32 MLP ops, so the reference arm is the NumPy (fp32) execution of the same
+lowered-op graph on the host cores, on a bounded sample of the batch.
+
+All inputs are seeded synthetic data of the configured shapes and distributions (no dataset).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import struct
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+REPO = Path(__file__).resolve().parent
+for _p in (REPO, REPO / "ai-compiler-framework_b200" / "python"):
+    if str(_p) not in sys.path:
+        sys.path.insert(0, str(_p))
+
+MLP_DIMS = [8192, 8192, 8192, 8192, 8192, 1000]
+MLP_GLOBAL_BATCH = 65536
+SMALL_MLP_DIMS = [2048, 2048, 2048, 1000]
+SMALL_MLP_BATCH = 8192
+ADAM = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8)
+
+
+# ------------------------------------------------------------------------------------------ helpers
+def measured_peaks():
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.idx = device_index
+        self.rows: list[list[str]] = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, cell in zip(names, r[5:9]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+class Dist:
+    """Control plane for N > 1: torch.distributed (gloo) for the id broadcast, barriers and the max over ranks;
+    the data path is the library's own NCCL communicator."""
+
+    def __init__(self, world):
+        self.world = world
+        self.rank = 0
+        self.td = None
+        if world > 1:
+            import torch.distributed as td
+            self.td = td
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            td.init_process_group("gloo")
+            self.rank = td.get_rank()
+
+    def barrier(self):
+        if self.td:
+            self.td.barrier()
+
+    def bcast_bytes(self, b: bytes | None) -> bytes:
+        if not self.td:
+            return b
+        box = [b]
+        self.td.broadcast_object_list(box, src=0)
+        return box[0]
+
+    def max_float(self, v: float) -> float:
+        if not self.td:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64)
+        self.td.all_reduce(t, op=self.td.ReduceOp.MAX)
+        return float(t[0])
+
+    def close(self):
+        if self.td:
+            self.td.destroy_process_group()
+
+
+class Events:
+    def __init__(self, lib):
+        import ctypes as C
+        self.lib, self.C = lib, C
+        self.a, self.b = C.c_uint64(), C.c_uint64()
+        lib.aicf_b200_event_create(C.byref(self.a))
+        lib.aicf_b200_event_create(C.byref(self.b))
+
+    def start(self, stream):
+        self.lib.aicf_b200_event_record(self.a.value, stream)
+
+    def stop_ms(self, stream) -> float:
+        self.lib.aicf_b200_event_record(self.b.value, stream)
+        self.lib.aicf_b200_event_sync(self.b.value)
+        ms = self.C.c_float()
+        self.lib.aicf_b200_event_elapsed_ms(self.a.value, self.b.value, self.C.byref(ms))
+        return float(ms.value)
+
+
+def pinned_array(lib, shape, dtype):
+    import ctypes as C
+    n = int(np.prod(shape)) * np.dtype(dtype).itemsize
+    p = C.c_void_p()
+    rc = lib.aicf_b200_host_alloc_pinned(C.byref(p), n)
+    if rc != 0:
+        raise RuntimeError("pinned host allocation failed")
+    buf = (C.c_uint8 * n).from_address(p.value)
+    return np.frombuffer(buf, dtype=dtype).reshape(shape), p.value
+
+
+def fill_normal(dst: np.ndarray, seed: int, scale: float = 1.0, chunk: int = 1 << 24):
+    """Fills a (possibly huge) float32 array with N(0, scale) in chunks, from one PCG64 stream."""
+    rng = np.random.default_rng(seed)
+    flat = dst.reshape(-1)
+    for i in range(0, flat.size, chunk):
+        n = min(chunk, flat.size - i)
+        rng.standard_normal(n, dtype=np.float32, out=flat[i:i + n])
+        if scale != 1.0:
+            flat[i:i + n] *= np.float32(scale)
+
+
+# ------------------------------------------------------------------------------------------ MLP workload
+def mlp_flops_per_sample(dims):
+    fwd = sum(2 * a * b for a, b in zip(dims[:-1], dims[1:]))
+    dx = sum(2 * a * b for a, b in zip(dims[1:-1], dims[2:]))
+    return fwd + fwd + dx  # forward, dW, dX (no dX for the first layer)
+
+
+def build_mlp(aicf, dims, batch, global_batch, dp):
+    from aicf_cuda import Plan, build_mlp_train_step
+    vals, low = build_mlp_train_step(batch, dims, compute_dtype="bf16", global_batch=global_batch, data_parallel=dp, **ADAM)
+    return Plan("dp_mlp", vals, low), vals, low
+
+
+def init_mlp_params(aicf, plan, dims, seed):
+    """He-normal fp32 master weights (same seed on every rank => identical replicas), zero biases; bf16
+    working copies made on the device by the cast kernel."""
+    from aicf_cuda import _C
+    from aicf_cuda._C import OpKind
+    rng = np.random.default_rng(seed)
+    for i in range(len(dims) - 1):
+        w = np.empty((dims[i + 1], dims[i]), np.float32)
+        rng.standard_normal(w.size, dtype=np.float32, out=w.reshape(-1))
+        w *= np.float32(np.sqrt(2.0 / dims[i]))
+        plan.tensor(f"{2 * i}.W").copy_from_host(w)
+        _C.launch_by_id("cast_v0", OpKind.Cast, [plan.tensor(f"{2 * i}.W")], [plan.tensor(f"{2 * i}.W.lp")])
+    _C.device_sync()
+
+
+def numpy_mlp_step_time(dims, batch, global_batch, steps=1):
+    """Seconds per NumPy fp32 step of the same lowered graph at `batch` rows (timed CPU baseline)."""
+    import oracle
+    from aicf_cuda import build_mlp_train_step
+    vals, low = build_mlp_train_step(batch, dims, compute_dtype="bf16", global_batch=global_batch, **ADAM)
+    params = oracle.mlp_params(dims, seed=4)
+    x, y = oracle.mlp_batch(batch, dims[0], dims[-1], seed=4)
+    env, dtypes = {}, {}
+    for v in vals:
+        dtypes[v.vid] = v.dtype
+        if v.name == "x":
+            env[v.vid] = x
+        elif v.name == "labels":
+            env[v.vid] = y
+        elif v.name in params:
+            env[v.vid] = params[v.name]
+        elif v.name.endswith(".W.lp"):
+            env[v.vid] = oracle.cast(params[v.name[:-3]], "bf16")
+        else:
+            env[v.vid] = np.zeros(v.shape, np.int32 if v.dtype == "i32" else np.float32)
+    oracle.run_lowered(low, env, dtypes, np.float32)  # warm-up (page faults, BLAS threads)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.run_lowered(low, env, dtypes, np.float32)
+    return (time.perf_counter() - t0) / steps
+
+
+def blas_threads():
+    try:
+        from threadpoolctl import threadpool_info
+        return max([i.get("num_threads", 1) for i in threadpool_info()] or [1])
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_mlp(args, dist: Dist):
+    import ctypes as C
+    import aicf_cuda
+    lib = aicf_cuda.lib
+    rank, local_rank, world = dist.rank, dist_env()[1], dist.world
+    dims = SMALL_MLP_DIMS if args.small else MLP_DIMS
+    gbatch = SMALL_MLP_BATCH if args.small else MLP_GLOBAL_BATCH
+    batch = gbatch // world
+    aicf_cuda._lib.check(lib.aicf_b200_set_device(local_rank), "set_device")
+    if world > 1:
+        idbuf = (C.c_uint8 * 128)()
+        if rank == 0:
+            aicf_cuda._lib.check(lib.aicf_b200_dp_unique_id(idbuf), "dp_unique_id")
+        uid = dist.bcast_bytes(bytes(idbuf) if rank == 0 else None)
+        aicf_cuda._lib.check(lib.aicf_b200_dp_init(rank, world, (C.c_uint8 * 128).from_buffer_copy(uid)), "dp_init")
+
+    plan, vals, low = build_mlp(aicf_cuda, dims, batch, gbatch, dp=world > 1)
+    init_mlp_params(aicf_cuda, plan, dims, seed=4)
+
+    # host inputs in pinned memory: rank r owns rows [r*batch, (r+1)*batch) of the global batch
+    x_host, _ = pinned_array(lib, (batch, dims[0]), np.float32)
+    fill_normal(x_host, seed=4000 + rank)
+    y_host, _ = pinned_array(lib, (batch,), np.int32)
+    y_host[:] = np.random.default_rng(5000 + rank).integers(0, dims[-1], size=batch, dtype=np.int32)
+    loss_host, _ = pinned_array(lib, (1,), np.float32)
+    x_dev, y_dev, loss_dev = plan.tensor("x"), plan.tensor("labels"), plan.tensor("loss")
+    stream = plan.stream
+    lib.aicf_b200_memcpy_h2d(x_dev.ptr, x_host.ctypes.data, x_host.nbytes, stream)
+    lib.aicf_b200_memcpy_h2d(y_dev.ptr, y_host.ctypes.data, y_host.nbytes, stream)
+    plan.sync()
+
+    plan.capture()
+    ev = Events(lib)
+    # ---- device-resident timing: K graph replays --------------------------------------------------
+    plan.replay(args.warmup)
+    plan.sync()
+    dist.barrier()
+    with ClockSampler(local_rank) as clocks:
+        ev.start(stream)
+        plan.replay(args.steps)
+        ms = ev.stop_ms(stream)
+        plan.sync()
+    ms = dist.max_float(ms)
+    dist.barrier()
+    loss_after = float(loss_dev.numpy()[0])
+
+    # ---- end to end: host buffers in, loss out, every step ----------------------------------------------
+    def e2e_step():
+        lib.aicf_b200_memcpy_h2d(x_dev.ptr, x_host.ctypes.data, x_host.nbytes, stream)
+        lib.aicf_b200_memcpy_h2d(y_dev.ptr, y_host.ctypes.data, y_host.nbytes, stream)
+        plan.replay(1)
+        lib.aicf_b200_memcpy_d2h(loss_host.ctypes.data, loss_dev.ptr, 4, stream)
+        lib.aicf_b200_stream_sync(stream)  # the caller reads the loss every step
+
+    for _ in range(max(1, min(args.warmup, 2))):
+        e2e_step()
+    dist.barrier()
+    e2e_steps = max(2, min(args.steps, 10))
+    t0 = time.perf_counter()
+    ev.start(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2e_ms = ev.stop_ms(stream)
+    e2e_ms = dist.max_float(max(e2e_ms, (time.perf_counter() - t0) * 1e3))
+    dist.barrier()
+
+    # ---- per-op device times of one eager step (event pair around every op, same stream) -----------------
+    per_op = plan.profile()
+    per_op = [a if a < b else b for a, b in zip(per_op, plan.profile())]
+    kids = plan.kernel_ids()
+    gemm_ms = sum(t for t, k in zip(per_op, kids) if k.startswith("gemm"))
+    by_kid: dict[str, float] = {}
+    for t, k in zip(per_op, kids):
+        by_kid[k] = by_kid.get(k, 0.0) + t
+    gemm_flops = mlp_flops_per_sample(dims) * batch
+    peaks = measured_peaks()
+    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    status = aicf_cuda._C.gemm_status()
+
+    out = None
+    if rank == 0:
+        ms_step = ms / args.steps
+        out = {
+            "metric": "MLP train-step samples/s (captured graph replay)", "value": gbatch / (ms_step * 1e-3), "unit": "samples/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "dp_captured_mlp" + ("_small" if args.small else ""), "layers": dims, "global_batch": gbatch,
+                       "per_gpu_batch": batch, "optimizer": "adam", "loss": "softmax_ce", "parallelism": f"dp{world}",
+                       "l2": "working set (>10 GB per step) far exceeds the 126 MB L2; no flush needed"},
+            "clocks": clocks.summary(),
+            "e2e": {"value": gbatch / (e2e_ms / e2e_steps * 1e-3), "unit": "samples/s",
+                    "h2d_bytes_per_step": int(x_host.nbytes + y_host.nbytes), "d2h_bytes_per_step": 4, "steps": e2e_steps,
+                    "note": "pinned host X (fp32) and labels copied in, graph replay, loss copied out, every step"},
+            "gpu_launches": int(plan.graph_kernel_nodes) * args.steps,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None,
+                         "kernel": "gemm_tcgen05_kernel", "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
+                         "note": "algorithmic GEMM FLOPs of one step / summed GEMM op times of one eager step"},
+            "phase_ms": {k: round(v, 4) for k, v in sorted(by_kid.items(), key=lambda kv: -kv[1])},
+            "loss": loss_after, "gemm_status": status,
+        }
+        if world == 1 and not args.no_cpu:
+            sample = 128
+            sec = numpy_mlp_step_time(dims, sample, gbatch, steps=1)
+            out["cpu_baseline"] = {"value": sample / sec, "unit": "samples/s", "cores": blas_threads(), "kind": "port",
+                                   "sample": f"one NumPy fp32 train step of the same lowered graph at batch {sample} (full-size Adam)"}
+    plan.close()
+    return out
+
+
+def run_mlp_reference(args, dist: Dist):
+    """NumPy fp32 execution of the same op graph on the host cores, bounded to a few minutes."""
+    if dist.rank != 0:
+        return None
+    dims = SMALL_MLP_DIMS if args.small else MLP_DIMS
+    gbatch = SMALL_MLP_BATCH if args.small else MLP_GLOBAL_BATCH
+    sample = 128
+    budget_s = 150.0
+    one = numpy_mlp_step_time(dims, sample, gbatch, steps=1)
+    steps = int(max(1, min(args.steps, budget_s // max(one, 1e-3))))
+    sec = numpy_mlp_step_time(dims, sample, gbatch, steps=steps) if steps > 1 else one
+    value = sample / sec
+    cores = blas_threads()
+    return {"impl": "reference", "metric": "MLP train-step samples/s (captured graph replay)", "value": value, "unit": "samples/s",
+            "n_gpus": dist.world, "steps": steps, "warmup": 1, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "dp_captured_mlp" + ("_small" if args.small else ""), "layers": dims, "global_batch": gbatch,
+                       "parallelism": f"dp{dist.world}"},
+            "cpu_baseline": {"value": value, "unit": "samples/s", "cores": cores, "kind": "port",
+                             "sample": f"NumPy fp32 train steps of the same lowered graph at batch {sample} of {gbatch} "
+                                       f"({steps} timed steps; the reference project has no CPU path and lacks bf16, softmax-CE and DP)"},
+            "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+# ------------------------------------------------------------------------------------------ single-kernel workloads
+def run_kernel_workload(args):
+    """GEMM TFLOP/s and softmax / CE / reduce / Adam GB/s on BASELINE's shapes (1 GPU)."""
+    import aicf_cuda
+    import oracle
+    from aicf_cuda import _C, Tensor
+    from aicf_cuda._C import OpKind
+    lib = aicf_cuda.lib
+    peaks = measured_peaks()
+    ev = Events(lib)
+    w = args.workload
+    small = args.small
+    stream = 0
+    rng = np.random.default_rng(1)
+
+    def dev_normal(shape, dtype, scale, seed):
+        h = np.empty(shape, np.float32)
+        fill_normal(h, seed, scale)
+        return Tensor.from_numpy(h, dtype)
+
+    def time_launch(fn, flush=None):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        _C.device_sync()
+        times = []
+        with ClockSampler(0) as clocks:
+            for _ in range(args.steps):
+                if flush is not None:
+                    flush()
+                ev.start(stream)
+                fn()
+                times.append(ev.stop_ms(stream))
+        return times, clocks.summary()
+
+    cfg, launches_per_step = {}, 1
+    if w in ("gemm", "gemm_f32"):
+        n = args.size or (2048 if small else 8192 if w == "gemm" else 4096)
+        dt = "bf16" if w == "gemm" else "f32"
+        A = dev_normal((n, n), dt, 0.577, 1)  # U(-1,1) has sigma 0.577; the distribution does not affect timing
+        B = dev_normal((n, n), dt, 0.577, 2)
+        bias = dev_normal((n,), "f32", 1.0, 3)
+        Cm = Tensor.empty((n, n), dt)
+        kid = "gemm_bias_relu_bf16_tcgen05_out_bf16_v0" if w == "gemm" else "gemm_bias_relu_f32_naive_v0"
+        pay = struct.pack("<iii", 0, 1 if args.transb else 0, 1)
+        fn = lambda: _C.launch_by_id(kid, OpKind.GemmEpilogue, [A, B, bias], [Cm], 0x4750454C, pay, stream)
+        work, unit, bound = 2.0 * n ** 3, "TFLOP/s", "tensor"
+        peak = peaks["bf16_tflops"] if w == "gemm" else None
+        metric = f"GEMM+bias+ReLU {dt} TFLOP/s"
+        cfg = {"workload": f"gemm_bias_relu_{dt}", "M": n, "N": n, "K": n, "transB": bool(args.transb),
+               "l2": "operands exceed L2 at 8192; smaller sizes are L2-resident by nature"}
+    elif w == "softmax":
+        M, N = (4096, 4096) if small else (32768, 4096)
+        dt = args.dtype
+        X = dev_normal((M, N), dt, 3.0, 2)
+        Y = Tensor.empty((M, N), dt)
+        kid = f"softmax_lastdim_{dt}_v0"
+        fn = lambda: _C.launch_by_id(kid, OpKind.Softmax, [X], [Y], 0, b"", stream)
+        work, unit, bound, peak = 2.0 * M * N * X.nbytes / X.numel, "GB/s", "hbm", peaks["hbm_gbs"]
+        metric = f"row softmax {dt} HBM GB/s"
+        cfg = {"workload": f"softmax_{dt}", "rows": M, "cols": N, "l2": "read+write bytes exceed L2"}
+    elif w == "reduce":
+        M, N = (4096, 4096) if small else (32768, 4096)
+        dt = args.dtype
+        X = dev_normal((M, N), dt, 3.0, 2)
+        O = Tensor.empty((M,), "f32")
+        kid = f"reduce_{args.reduce_kind}_lastaxis_{dt}_v0"
+        kind = {"sum": OpKind.ReduceSum, "max": OpKind.ReduceMax, "mean": OpKind.ReduceMean}[args.reduce_kind]
+        sch, pay = (0x5253554D, struct.pack("<q", -1)) if args.reduce_kind == "sum" else (0, b"")
+        fn = lambda: _C.launch_by_id(kid, kind, [X], [O], sch, pay, stream)
+        work, unit, bound, peak = float(X.nbytes + 4 * M), "GB/s", "hbm", peaks["hbm_gbs"]
+        metric = f"last-axis {args.reduce_kind} {dt} HBM GB/s"
+        cfg = {"workload": f"reduce_{args.reduce_kind}_{dt}", "rows": M, "cols": N, "l2": "input exceeds L2"}
+    elif w == "ce":
+        B, Cn = (1024, 32000) if small else (8192, 32000)
+        Z = dev_normal((B, Cn), "f32", 2.0, 3)
+        L = Tensor.from_numpy(rng.integers(0, Cn, B, dtype=np.int32))
+        D, Lo, Am = Tensor.empty((B, Cn), "f32"), Tensor.empty((B,), "f32"), Tensor.empty((B,), "i32")
+        fn = lambda: _C.launch_by_id("softmax_ce_f32_i32_v0", OpKind.SoftmaxCE, [Z, L], [D, Lo, Am], 0, b"", stream)
+        work, unit, bound, peak = 2.0 * Z.nbytes + 12.0 * B, "GB/s", "hbm", peaks["hbm_gbs"]
+        metric = "softmax cross-entropy loss+grad f32 HBM GB/s"
+        cfg = {"workload": "softmax_ce_f32", "rows": B, "classes": Cn, "l2": "read+write bytes exceed L2"}
+    elif w == "adam":
+        n = (1 << 24) if small else (1 << 28)
+        P, G = dev_normal((n,), "f32", 0.02, 3), dev_normal((n,), "f32", 1e-3, 4)
+        M_, V_ = Tensor.zeros((n,)), Tensor.zeros((n,))
+        step = Tensor.from_numpy(np.array([1], np.int32))
+        pay = struct.pack("<fffffI", 3e-4, 0.9, 0.999, 1e-8, 0.01, 0)
+
+        def fn():
+            _C.launch_by_id("adam_step_f32_fused_v1", OpKind.AdamStep, [P, G, M_, V_, step], [P, M_, V_], 0x4D414441, pay, stream)
+        work, unit, bound, peak = 28.0 * n, "GB/s", "hbm", peaks["hbm_gbs"]
+        metric = "fused Adam f32 HBM GB/s"
+        cfg = {"workload": "adam_f32_wd", "elements": n, "l2": "7 streams of 1 GiB exceed L2"}
+    else:
+        raise SystemExit(f"unknown workload {w}")
+
+    _C.trace_enable(False)
+    times, clocks = time_launch(fn)
+    ms = statistics.mean(times)
+    achieved = work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
+    out = {"metric": metric, "value": achieved, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+           "ms_per_step": ms, "ms_min": min(times), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+           "dtype": cfg["workload"].split("_")[-1], "data": "synthetic", "config": cfg, "clocks": clocks,
+           "gpu_launches": args.steps * launches_per_step,
+           "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+                        "frac": (achieved / peak) if peak else None, "traffic": None, "peak_source": peaks["source"]},
+           "gemm_status": _C.gemm_status()}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="mlp")
+    ap.add_argument("--small", action="store_true", help="reduced shapes (profiler captures)")
+    ap.add_argument("--size", type=int, default=0)
+    ap.add_argument("--dtype", default="f32")
+    ap.add_argument("--reduce-kind", default="sum")
+    ap.add_argument("--transb", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the timed NumPy baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    _, _, world = dist_env()
+    if args.impl == "reference":
+        rank = dist_env()[0]
+        if rank != 0:
+            return  # only rank 0 measures the host baseline; the others have nothing to do
+        class _Solo:  # no process group is needed for a host-only measurement
+            rank, world = 0, max(world, args.gpus)
+            def barrier(self): pass
+        out = run_mlp_reference(args, _Solo())
+        print(json.dumps(out), flush=True)
+        return
+
+    if args.workload != "mlp":
+        print(json.dumps(run_kernel_workload(args)), flush=True)
+        return
+    dist = Dist(world)
+    try:
+        out = run_mlp(args, dist)
+        if out is not None:
+            print(json.dumps(out), flush=True)
+    finally:
+        dist.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -187,7 +187,11 @@ int aicf_b200_plan_replay(aicf_plan* plan, int n);           /* n graph launches
 int aicf_b200_plan_reset_graph(aicf_plan* plan);
 aicf_stream aicf_b200_plan_stream(aicf_plan* plan);
 int aicf_b200_plan_sync(aicf_plan* plan);
-int aicf_b200_plan_graph_nodes(aicf_plan* plan); /* kernel/memset/memcpy nodes in the captured graph, -1 if none */
+int aicf_b200_plan_graph_nodes(aicf_plan* plan); /* all nodes of the captured graph, -1 if none */
+int aicf_b200_plan_graph_kernel_nodes(aicf_plan* plan); /* kernel nodes only: launches per replay */
+/* Eager step with a CUDA event pair around every op on the plan's stream (all_reduce ops stay on that
+ * stream too); after a synchronise, ms_per_op[i] is the device time of op i. For measurement only. */
+int aicf_b200_plan_profile(aicf_plan* plan, float* ms_per_op, int capacity);
 
 /* ---- data-parallel gradient exchange -------------------------------------------------------------
  * No counterpart in the reference (single device, bindings.cpp:123). One process per GPU; rank 0

@@ -1,0 +1,71 @@
+"""The C-ABI library loads on a machine without a GPU and exports every symbol include/aicf_b200.h
+declares; the ctypes prototype table covers the same set."""
+import re
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parents[1]
+
+
+def declared_functions():
+    text = (REPO / "include" / "aicf_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(aicf_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_surface():
+    names = declared_functions()
+    assert len(names) >= 60
+    for must in ("aicf_b200_op_call", "aicf_b200_launch_by_id", "aicf_b200_graph_begin", "aicf_b200_plan_capture",
+                 "aicf_b200_plan_replay", "aicf_b200_dp_init"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    import aicf_cuda
+    for name in declared_functions():
+        assert hasattr(aicf_cuda.lib, name), f"{name} declared in aicf_b200.h but not exported"
+
+
+def test_ctypes_table_matches_header():
+    from aicf_cuda._lib import PROTOTYPES
+    assert sorted(PROTOTYPES) == declared_functions()
+
+
+def test_abi_version_and_status_strings():
+    import aicf_cuda
+    lib = aicf_cuda.lib
+    assert lib.aicf_b200_abi_version() == 1
+    assert [lib.aicf_b200_status_string(i).decode() for i in range(5)] == ["Ok", "InvalidArgument", "NotImplemented", "Internal", "Unknown"]
+
+
+def test_op_names_follow_the_reference_binding():
+    import aicf_cuda
+    want = ["add", "relu", "gemm", "bias_add", "reduce_sum", "mse_grad", "relu_bwd", "sgd_step", "copy", "grad_zero",
+            "adam_step", "step_inc", "bias_corr", "layernorm_fwd", "layernorm_bwd", "batchnorm_fwd", "batchnorm_bwd",
+            "gemm_epilogue", "softmax", "softmax_ce", "reduce_max", "reduce_mean", "all_reduce", "cast"]
+    got = [aicf_cuda.lib.aicf_b200_op_name(i).decode() for i in range(len(want))]
+    assert got == want
+    assert aicf_cuda.lib.aicf_b200_op_name(99).decode() == "unknown"
+
+
+def test_opkind_enum_values_are_abi():
+    from aicf_cuda._C import OpKind
+    assert [int(OpKind.EltwiseAdd), int(OpKind.Gemm), int(OpKind.AdamStep), int(OpKind.GemmEpilogue)] == [0, 2, 10, 17]
+    import aicf_cuda._C as m
+    assert m.Gemm == OpKind.Gemm  # export_values()
+    assert OpKind(17) is OpKind.GemmEpilogue
+
+
+def test_null_pointer_calls_fail_cleanly_without_a_device():
+    import aicf_cuda
+    lib = aicf_cuda.lib
+    # by-id with no id -> InvalidArgument; unknown id -> NotImplemented; both without touching the GPU
+    assert lib.aicf_b200_launch_by_id(None, 2, None, 0, None, 0, None, 0) == 1
+    assert lib.aicf_b200_launch_by_id(b"no_such_kernel_v0", 2, None, 0, None, 0, None, 0) == 2
+    assert "kernel_id=no_such_kernel_v0" in lib.aicf_b200_last_error().decode()
+    assert lib.aicf_b200_launch_by_id(b"layernorm_fwd_f32_v0", 13, None, 0, None, 0, None, 0) == 2
+    assert lib.aicf_b200_op_call(99, None, 0, None, 0, None, 0) == 1
+    assert lib.aicf_b200_graph_end() == 1
+    assert lib.aicf_b200_last_error().decode() == "graph_end called but not capturing"
+    assert lib.aicf_b200_graph_launch() == 1
+    assert lib.aicf_b200_last_error().decode() == "graph_launch called but no captured graph exists"

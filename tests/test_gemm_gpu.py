@@ -1,0 +1,138 @@
+"""GEMM / GEMM+bias+ReLU parity: tcgen05 kernel (bf16 / f16) and SIMT kernel (f32, unaligned shapes),
+all four transpose combinations, ragged edges, strided outputs. Tolerance: 16-bit inputs within 2e-2
+relative (normwise) of an fp64 host result - in practice ~4e-3, one rounding of the 16-bit output;
+fp32 within 1e-5."""
+import struct
+
+import numpy as np
+import pytest
+
+import oracle
+from aicf_cuda import _C, Tensor
+from aicf_cuda._C import OpKind
+from util import by_id, dev, host, op_call, rel_err
+
+pytestmark = pytest.mark.gpu
+
+GEMM = 0x47454D4D
+GPEL = 0x4750454C
+
+_ROUND = {"bf16": oracle.bf16_round, "f16": oracle.f16_round, "f32": lambda a: np.asarray(a, np.float32)}
+
+
+def _operands(M, N, K, ta, tb, dt, seed=1):
+    A, B, bias = oracle.gemm_inputs(M, N, K, seed)
+    A, B = _ROUND[dt](A), _ROUND[dt](B)
+    sa = np.ascontiguousarray(A.T) if ta else A   # stored [K,M] when transA
+    sb = np.ascontiguousarray(B.T) if tb else B   # stored [N,K] when transB
+    return A, B, bias, sa, sb
+
+
+GEMM_KID = {("bf16", "bf16"): "gemm_bf16_tcgen05_out_bf16_v0", ("bf16", "f32"): "gemm_bf16_tcgen05_out_f32_v0",
+            ("f16", "f16"): "gemm_f16_tcgen05_out_f16_v0", ("f16", "f32"): "gemm_f16_tcgen05_out_f32_v0",
+            ("f32", "f32"): "gemm_f32_naive_v0"}
+EPI_KID = {("bf16", "bf16"): "gemm_bias_relu_bf16_tcgen05_out_bf16_v0", ("bf16", "f32"): "gemm_bias_relu_bf16_tcgen05_out_f32_v0",
+           ("f16", "f16"): "gemm_bias_relu_f16_tcgen05_out_f16_v0", ("f32", "f32"): "gemm_bias_relu_f32_naive_v0"}
+TOL = {"bf16": 2e-2, "f16": 2e-2, "f32": 1e-5}
+
+SHAPES = [(64, 80, 48), (128, 256, 64), (256, 512, 128), (200, 304, 136), (1, 8, 8), (129, 257, 72), (384, 1000, 512),
+          (1024, 1024, 1024)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("dt,out", [("bf16", "bf16"), ("bf16", "f32"), ("f16", "f16"), ("f32", "f32")])
+def test_gemm_all_transposes(gpu, M, N, K, ta, tb, dt, out):
+    # operands whose rows are not 16-byte aligned route to the SIMT kernel inside the same variant
+    A, B, _, sa, sb = _operands(M, N, K, ta, tb, dt)
+    C = Tensor.empty((M, N), out)
+    by_id(GEMM_KID[(dt, out)], OpKind.Gemm, [dev(sa, dt), dev(sb, dt)], [C], GEMM, struct.pack("<ii", ta, tb))
+    assert _C.gemm_status() == 0
+    want = oracle.gemm(A, B)
+    assert rel_err(host(C), want) <= (TOL[dt] if out != "f32" or dt == "f32" else 1e-4), (M, N, K, ta, tb, dt, out)
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 80, 48), (256, 512, 128), (200, 304, 136), (777, 1000, 264)])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("relu", [1, 0])
+@pytest.mark.parametrize("dt,out,bias_dt", [("bf16", "bf16", "f32"), ("bf16", "bf16", "bf16"), ("f16", "f16", "f32"),
+                                            ("bf16", "f32", "f32"), ("f32", "f32", "f32")])
+def test_gemm_epilogue_bias_relu(gpu, M, N, K, ta, tb, relu, dt, out, bias_dt):
+    A, B, bias, sa, sb = _operands(M, N, K, ta, tb, dt)
+    bias = _ROUND[bias_dt](bias)
+    C = Tensor.empty((M, N), out)
+    by_id(EPI_KID[(dt, out)], OpKind.GemmEpilogue, [dev(sa, dt), dev(sb, dt), dev(bias, bias_dt)], [C], GPEL,
+          struct.pack("<iii", ta, tb, relu))
+    assert _C.gemm_status() == 0
+    want = oracle.gemm_epilogue(A, B, bias, relu=bool(relu))
+    assert rel_err(host(C), want) <= (TOL[dt] if out != "f32" or dt == "f32" else 1e-4)
+    if relu:
+        assert (host(C) >= 0).all()
+
+
+def test_reference_ids_keep_reference_contracts(gpu):
+    """gemm_f16_tc_wmma_out_f16_v0 / gemm_bias_relu_f16_tc_wmma_out_f16_v0: f16 everything (bias too),
+    packed row-major C; schema 0 means no transposes and, for the epilogue, ReLU on."""
+    M, N, K = 64, 64, 64
+    A, B, bias, sa, sb = _operands(M, N, K, 0, 0, "f16")
+    bias = oracle.f16_round(bias)
+    C = Tensor.empty((M, N), "f16")
+    by_id("gemm_f16_tc_wmma_out_f16_v0", OpKind.Gemm, [dev(sa, "f16"), dev(sb, "f16")], [C])
+    assert rel_err(host(C), oracle.gemm(A, B)) <= 2e-2
+    by_id("gemm_bias_relu_f16_tc_wmma_out_f16_v0", OpKind.GemmEpilogue, [dev(sa, "f16"), dev(sb, "f16"), dev(bias, "f16")], [C])
+    assert rel_err(host(C), oracle.gemm_epilogue(A, B, bias, relu=True)) <= 2e-2
+    # a payload under the executor's 'GEPI' tag is ignored exactly like the reference does: ta=tb=0, relu on
+    by_id("gemm_bias_relu_f16_tc_wmma_out_f16_v0", OpKind.GemmEpilogue, [dev(sa, "f16"), dev(sb, "f16"), dev(bias, "f16")],
+          [C], int.from_bytes(b"GEPI", "little"), struct.pack("<iii", 0, 1, 1))
+    assert rel_err(host(C), oracle.gemm_epilogue(A, B, bias, relu=True)) <= 2e-2
+    with pytest.raises(RuntimeError, match="InvalidArgument"):  # f32 bias is not this id's contract
+        by_id("gemm_bias_relu_f16_tc_wmma_out_f16_v0", OpKind.GemmEpilogue, [dev(sa, "f16"), dev(sb, "f16"), dev(bias)], [C])
+    with pytest.raises(RuntimeError, match="InvalidArgument"):  # wrong C shape
+        by_id("gemm_f16_tc_wmma_out_f16_v0", OpKind.Gemm, [dev(sa, "f16"), dev(sb, "f16")], [Tensor.empty((M, N + 8), "f16")])
+    op_call(OpKind.Gemm, [dev(sa, "f16"), dev(sb, "f16")], [C])  # legacy dispatch finds an f16 variant
+    assert rel_err(host(C), oracle.gemm(A, B)) <= 2e-2
+
+
+def test_f32_matches_sequential_fma_order(gpu):
+    """One FMA per k in increasing k, like the reference's fp32 kernel: compare with a float32 loop."""
+    M, N, K = 8, 16, 300
+    A, B, _ = oracle.gemm_inputs(M, N, K, seed=5)
+    C = Tensor.empty((M, N))
+    by_id("gemm_f32_naive_v0", OpKind.Gemm, [dev(A), dev(B)], [C])
+    acc = np.zeros((M, N), np.float64)
+    for k in range(K):  # float32 FMA == round(fp64 product-sum) for these magnitudes
+        acc = (acc + A[:, k:k + 1].astype(np.float64) * B[k:k + 1, :].astype(np.float64)).astype(np.float32).astype(np.float64)
+    assert np.array_equal(host(C), acc.astype(np.float32))
+
+
+@pytest.mark.parametrize("size", [4096, 8192])
+def test_large_bf16_gemm_sampled_rows(gpu, size):
+    """Full benchmark sizes: 64 sampled rows against fp64, plus linearity C(2A) == 2 C(A) on the device."""
+    M = N = K = size
+    rng = np.random.default_rng(1)
+    A = oracle.bf16_round(rng.uniform(-1, 1, (M, K)).astype(np.float32))
+    B = oracle.bf16_round(rng.uniform(-1, 1, (K, N)).astype(np.float32))
+    bias = rng.standard_normal(N).astype(np.float32)
+    dA, dB, dbias = dev(A, "bf16"), dev(B, "bf16"), dev(bias)
+    C = Tensor.empty((M, N), "bf16")
+    by_id("gemm_bias_relu_bf16_tcgen05_out_bf16_v0", OpKind.GemmEpilogue, [dA, dB, dbias], [C], GPEL, struct.pack("<iii", 0, 0, 1))
+    assert _C.gemm_status() == 0
+    got = host(C)
+    rows = rng.choice(M, 64, replace=False)
+    want = np.maximum(A[rows].astype(np.float64) @ B.astype(np.float64) + bias, 0)
+    assert rel_err(got[rows], want) <= 2e-2
+    C2 = Tensor.empty((M, N), "f32")
+    C1 = Tensor.empty((M, N), "f32")
+    by_id("gemm_bf16_tcgen05_out_f32_v0", OpKind.Gemm, [dA, dB], [C1], GEMM, struct.pack("<ii", 0, 0))
+    by_id("gemm_bf16_tcgen05_out_f32_v0", OpKind.Gemm, [dev(2 * A, "bf16"), dB], [C2], GEMM, struct.pack("<ii", 0, 0))
+    assert np.array_equal(host(C2), 2 * host(C1)), "scaling an operand by 2 is exact in bf16/fp32"
+
+
+def test_f32_4096_sampled_rows(gpu):
+    n = 4096
+    A, B, bias = oracle.gemm_inputs(n, n, n, seed=1)
+    C = Tensor.empty((n, n))
+    by_id("gemm_bias_relu_f32_naive_v0", OpKind.GemmEpilogue, [dev(A), dev(B), dev(bias)], [C], GPEL, struct.pack("<iii", 0, 0, 1))
+    rows = np.random.default_rng(0).choice(n, 32, replace=False)
+    want = np.maximum(A[rows].astype(np.float64) @ B.astype(np.float64) + bias, 0)
+    assert rel_err(host(C)[rows], want) <= 1e-5

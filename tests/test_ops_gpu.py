@@ -1,0 +1,317 @@
+"""Parity of the streaming kernels with the NumPy oracle, through the binding (launch_by_id / op_call)
+and therefore through the C ABI. Shapes follow the reference's probe scripts
+(python/cuda_binding_test/v2_*_probe.py) plus odd sizes, unaligned views and sizes past the limits the
+reference mishandles. Tolerances: fp32 elementwise / reduce / Adam 1e-5 relative; integers exact;
+16-bit outputs one rounding step of the output type."""
+import struct
+
+import numpy as np
+import pytest
+
+import oracle
+from aicf_cuda import Tensor, f32_to_bf16_bits
+from aicf_cuda._C import OpKind
+from util import assert_close_f32, by_id, dev, host, op_call
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(1024,), (64, 256), (8, 32, 128)]
+ADAM = 0x4D414441
+BCOR = 0x524F4342
+RSUM = 0x5253554D
+SMCE = 0x45434D53
+
+
+def rnd(shape, seed=0, scale=1.0):
+    return (np.random.default_rng(seed).standard_normal(shape) * scale).astype(np.float32)
+
+
+def scalar(v, dtype="f32"):
+    return Tensor.from_numpy(np.array(v, np.float32 if dtype == "f32" else np.int32))  # rank 0
+
+
+# ------------------------------------------------------------------ Adam
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("inplace", [False, True])
+def test_adam_v0_reference_contract(gpu, shape, inplace):
+    p, g, m, v = rnd(shape, 1), rnd(shape, 2, 1e-2), rnd(shape, 3, 1e-2), np.abs(rnd(shape, 4, 1e-3))
+    bc1, bc2 = 1 - 0.9 ** 3, 1 - 0.999 ** 3
+    P, G, M, V = dev(p), dev(g), dev(m), dev(v)
+    Po, Mo, Vo = (P, M, V) if inplace else (Tensor.empty(shape), Tensor.empty(shape), Tensor.empty(shape))
+    by_id("adam_step_f32_v0", OpKind.AdamStep, [P, G, M, V, scalar(bc1), scalar(bc2)], [Po, Mo, Vo], ADAM,
+          struct.pack("<ffff", 1e-3, 0.9, 0.999, 1e-8))
+    wp, wm, wv = oracle.adam_step_v0(p, g, m, v, np.float32(bc1), np.float32(bc2))
+    assert_close_f32(host(Po), wp, what="p")
+    assert_close_f32(host(Mo), wm, what="m")
+    assert_close_f32(host(Vo), wv, atol=1e-12, what="v")
+    if not inplace:
+        assert np.array_equal(host(P), p)  # inputs untouched out of place
+
+
+def test_adam_v0_rejects_what_the_reference_rejects(gpu):
+    shape = (64, 256)
+    P, G, M, V = (dev(rnd(shape, i)) for i in range(4))
+    sc = [scalar(0.5), scalar(0.5)]
+    pay = struct.pack("<ffff", 1e-3, 0.9, 0.999, 1e-8)
+    with pytest.raises(RuntimeError, match="InvalidArgument"):  # gradient aliases an output
+        by_id("adam_step_f32_v0", OpKind.AdamStep, [P, G, M, V] + sc, [G, M, V], ADAM, pay)
+    h = Tensor.from_numpy(rnd(shape).astype(np.float16))
+    with pytest.raises(RuntimeError, match="InvalidArgument"):  # f16 parameters
+        by_id("adam_step_f32_v0", OpKind.AdamStep, [h, G, M, V] + sc, [h, M, V], ADAM, pay)
+    with pytest.raises(RuntimeError, match="InvalidArgument"):  # schema 'ADAM' is mandatory
+        by_id("adam_step_f32_v0", OpKind.AdamStep, [P, G, M, V] + sc, [P, M, V], 0, b"")
+    one = Tensor.from_numpy(np.array([0.5], np.float32))        # rank-1 scalar is not rank 0
+    with pytest.raises(RuntimeError, match="InvalidArgument"):
+        by_id("adam_step_f32_v0", OpKind.AdamStep, [P, G, M, V, one, one], [P, M, V], ADAM, pay)
+
+
+@pytest.mark.parametrize("n", [1, 3, 1001, 4096, 1 << 20])
+@pytest.mark.parametrize("wd,dec", [(0.0, 0), (0.01, 0), (0.01, 1)])
+def test_adam_fused_step_counter_weight_decay_and_bf16_copy(gpu, n, wd, dec):
+    p, g = oracle.adam_inputs(n, seed=3)
+    m, v = rnd((n,), 5, 1e-3), np.abs(rnd((n,), 6, 1e-6))
+    P, G, M, V = dev(p), dev(g), dev(m), dev(v)
+    step = Tensor.from_numpy(np.array([7], np.int32))
+    lp = Tensor.empty((n,), "bf16")
+    pay = struct.pack("<fffffI", 3e-4, 0.9, 0.999, 1e-8, wd, dec)
+    by_id("adam_step_f32_fused_v1", OpKind.AdamStep, [P, G, M, V, step], [P, M, V, lp], ADAM, pay)
+    wp, wm, wv = oracle.adam_step_fused(p, g, m, v, 7, 3e-4, weight_decay=wd, decoupled=bool(dec))
+    assert_close_f32(host(P), wp, what="p")
+    assert_close_f32(host(M), wm, atol=1e-10, what="m")
+    assert_close_f32(host(V), wv, atol=1e-14, what="v")
+    assert np.array_equal(lp.numpy(), f32_to_bf16_bits(P.numpy()))  # bf16 copy is the rounded new parameter
+
+
+def test_adam_fused_unaligned_views_take_the_scalar_path(gpu):
+    n = 1000
+    base = [Tensor.zeros((n + 1,)) for _ in range(4)]
+    arrs = [rnd((n,), i, 1e-2) for i in range(4)]
+    arrs[3] = np.abs(arrs[3])
+    views = []
+    for b, a in zip(base, arrs):
+        t = Tensor((n,), "f32", ptr=b.ptr + 4)  # 4-byte offset: not 16-byte aligned
+        t.copy_from_host(a)
+        views.append(t)
+    step = Tensor.from_numpy(np.array([1], np.int32))
+    by_id("adam_step_f32_fused_v1", OpKind.AdamStep, views + [step], views[:1] + views[2:], ADAM,
+          struct.pack("<ffff", 1e-3, 0.9, 0.999, 1e-8))
+    wp, wm, wv = oracle.adam_step_fused(*arrs, 1)
+    assert_close_f32(host(views[0]), wp)
+    assert_close_f32(host(views[2]), wm, atol=1e-10)
+
+
+@pytest.mark.parametrize("t", [1, 10, 0])
+@pytest.mark.parametrize("rank0", [True, False])
+def test_bias_corr(gpu, t, rank0):
+    mk = (lambda v, dt: scalar(v, dt)) if rank0 else (lambda v, dt: Tensor.from_numpy(np.array([v], np.float32 if dt == "f32" else np.int32)))
+    S, O1, O2 = mk(t, "i32"), mk(0, "f32"), mk(0, "f32")
+    by_id("bias_corr_v0", OpKind.BiasCorr, [S], [O1, O2], BCOR, struct.pack("<ff", 0.9, 0.999))
+    w1, w2 = oracle.bias_corr(t)
+    assert host(O1).ravel()[0] == pytest.approx(w1, rel=1e-5)
+    assert host(O2).ravel()[0] == pytest.approx(w2, rel=2e-4)  # powf(0.999, t) in fp32: 1-b^t loses ~3 digits
+    with pytest.raises(RuntimeError, match="InvalidArgument"):
+        by_id("bias_corr_v0", OpKind.BiasCorr, [S], [O1, O2], 0, b"")
+    with pytest.raises(RuntimeError, match="InvalidArgument"):
+        by_id("bias_corr_v0", OpKind.BiasCorr, [O1], [O1, O2], BCOR, struct.pack("<ff", 0.9, 0.999))
+
+
+@pytest.mark.parametrize("shape", [(), (1,), (1024,), (64, 256)])
+def test_step_inc_increments_the_output_buffer(gpu, shape):
+    s = np.arange(int(np.prod(shape)) if shape else 1, dtype=np.int32).reshape(shape)
+    S = Tensor.from_numpy(s)
+    by_id("step_inc_v0", OpKind.StepInc, [S], [S])
+    assert np.array_equal(S.numpy(), s + 1)
+    SO = Tensor.from_numpy(s + 100)  # out of place: the reference never reads the input
+    by_id("step_inc_v0", OpKind.StepInc, [S], [SO])
+    assert np.array_equal(SO.numpy(), s + 101)
+
+
+# ------------------------------------------------------------------ elementwise
+def _cases():
+    for shape in SHAPES:
+        yield shape, "f32"
+    yield (7, 33, 127), "f16"
+    yield (7, 33, 127), "bf16"
+    yield (64, 256), "f16"
+    yield (64, 256), "bf16"
+
+
+def _round(a, dt):
+    return {"f32": lambda x: x, "f16": oracle.f16_round, "bf16": oracle.bf16_round}[dt](np.asarray(a, np.float32))
+
+
+def _tol(dt):
+    return {"f32": dict(rtol=1e-6, atol=1e-9), "f16": dict(rtol=1e-3, atol=1e-6), "bf16": dict(rtol=8e-3, atol=1e-6)}[dt]
+
+
+@pytest.mark.parametrize("shape,dt", list(_cases()))
+def test_elementwise_family(gpu, shape, dt):
+    x, y = _round(rnd(shape, 1), dt), _round(rnd(shape, 2), dt)
+    X, Y = dev(x, dt), dev(y, dt)
+    O = Tensor.empty(shape, dt)
+    sfx = dt
+    by_id(f"relu_{sfx}_v0", OpKind.EltwiseRelu, [X], [O])
+    assert np.array_equal(host(O), oracle.relu(x, np.float32))
+    by_id(f"relu_bwd_{sfx}_v0", OpKind.ReluBwd, [X, Y], [O])
+    assert np.array_equal(host(O), oracle.relu_bwd(x, y, np.float32))
+    by_id(f"add_{sfx}_v0", OpKind.EltwiseAdd, [X, Y], [O])
+    assert np.allclose(host(O), oracle.add(x, y), **_tol(dt))
+    by_id(f"copy_{sfx}_v0", OpKind.Copy, [X], [O])
+    assert np.array_equal(host(O), x)
+    by_id(f"mse_grad_{sfx}_v0", OpKind.MseGrad, [X, Y], [O])
+    assert np.allclose(host(O), oracle.mse_grad(x, y), **_tol(dt))
+    by_id(f"mse_grad_{sfx}_v0", OpKind.MseGrad, [X, Y], [O], 0x4745534D, struct.pack("<f", 0.25))
+    assert np.allclose(host(O), oracle.mse_grad(x, y, 0.25), **_tol(dt))
+    by_id(f"sgd_step_{sfx}_v0", OpKind.SgdStep, [X, Y], [O])
+    assert np.allclose(host(O), oracle.sgd_step(x, y), **_tol(dt))
+    by_id(f"sgd_step_{sfx}_v0", OpKind.SgdStep, [X, Y], [O], 0x53444753, struct.pack("<f", 0.01))
+    assert np.allclose(host(O), oracle.sgd_step(x, y, 0.01), **_tol(dt))
+    by_id("grad_zero_v0", OpKind.GradZero, [O], [O])
+    assert not host(O).any()
+    if len(shape) >= 2:
+        b = _round(rnd((shape[-1],), 3), dt)
+        by_id(f"bias_add_{sfx}_v0", OpKind.BiasAdd, [X, dev(b, dt)], [O])
+        assert np.allclose(host(O), oracle.bias_add(x, b), **_tol(dt))
+        by_id(f"bias_add_{sfx}_v0", OpKind.BiasAdd, [X, dev(b, dt)], [X])  # in place
+        assert np.allclose(host(X), oracle.bias_add(x, b), **_tol(dt))
+
+
+def test_reference_alias_ids_and_legacy_dispatch(gpu):
+    x = oracle.f16_round(rnd((64, 256), 1))
+    X, O = dev(x, "f16"), Tensor.empty((64, 256), "f16")
+    for kid, kind in [("relu_f16_vec2_v0", OpKind.EltwiseRelu), ("relu_f16_v0", OpKind.EltwiseRelu)]:
+        by_id(kid, kind, [X], [O])
+        assert np.array_equal(host(O), np.maximum(x, 0))
+    op_call(OpKind.EltwiseRelu, [X], [O])  # legacy path picks by priority
+    assert np.array_equal(host(O), np.maximum(x, 0))
+    with pytest.raises(RuntimeError, match="InvalidArgument"):  # dtype mismatch by id
+        by_id("relu_f32_v0", OpKind.EltwiseRelu, [X], [O])
+    with pytest.raises(RuntimeError, match="InvalidArgument"):  # shape mismatch
+        by_id("relu_f16_v0", OpKind.EltwiseRelu, [X], [Tensor.empty((64, 255), "f16")])
+    with pytest.raises(RuntimeError, match="NotImplemented"):
+        by_id("layernorm_fwd_f16_v0", OpKind.LayerNormFwd, [X], [O])
+    with pytest.raises(RuntimeError, match="InvalidArgument"):  # sgd output may not alias the gradient
+        by_id("sgd_step_f16_v0", OpKind.SgdStep, [X, O], [O])
+
+
+def test_relu_bwd_covers_sizes_the_reference_truncates(gpu):
+    n = 65535 * 256 + 12345  # the reference's grid cap leaves everything past 65535*256 unwritten
+    dout = np.ones(n, np.float32)
+    y = np.ones(n, np.float32)
+    y[::3] = -1
+    O = Tensor.from_numpy(np.full(n, 7, np.float32))
+    by_id("relu_bwd_f32_v0", OpKind.ReluBwd, [dev(dout), dev(y)], [O])
+    got = host(O)
+    assert np.array_equal(got, np.where(y > 0, 1, 0).astype(np.float32))
+
+
+@pytest.mark.parametrize("src,dst", [("f32", "bf16"), ("f32", "f16"), ("bf16", "f32"), ("f16", "bf16")])
+def test_cast_rounds_to_nearest_even(gpu, src, dst):
+    x = _round(rnd((33, 1001), 9, 3.0), src)
+    O = Tensor.empty(x.shape, dst)
+    by_id("cast_v0", OpKind.Cast, [dev(x, src)], [O])
+    assert np.array_equal(host(O), _round(x, dst))
+
+
+# ------------------------------------------------------------------ reductions
+@pytest.mark.parametrize("M,N,dt,out", [(128, 64, "f32", "f32"), (257, 64, "f16", "f32"), (257, 64, "f16", "f16"),
+                                        (1000, 130, "f32", "f32"), (4099, 1000, "bf16", "f32"), (65536, 96, "f32", "f32"),
+                                        (8192, 8192, "bf16", "f32"), (64, 10, "f32", "f32"), (3, 5, "bf16", "bf16")])
+def test_column_sum_fixed_order_and_exact_to_tolerance(gpu, M, N, dt, out):
+    x = _round(rnd((M, N), 11), dt)
+    kid = {("f32", "f32"): "reduce_sum_keep_lastdim_f32_v0", ("f16", "f32"): "reduce_sum_keep_lastdim_f16_to_f32_v0",
+           ("f16", "f16"): "reduce_sum_keep_lastdim_f16_v0", ("bf16", "f32"): "reduce_sum_keep_lastdim_bf16_to_f32_v0",
+           ("bf16", "bf16"): "reduce_sum_keep_lastdim_bf16_v0"}[(dt, out)]
+    X, O = dev(x, dt), Tensor.empty((N,), out)
+    by_id(kid, OpKind.ReduceSum, [X], [O], RSUM, struct.pack("<q", 0))
+    want = oracle.reduce_sum_columns(x)
+    got = host(O)
+    l1 = np.abs(x).astype(np.float64).sum(axis=0)
+    if out == "f32":
+        assert (np.abs(got - want) <= 1e-5 * l1 + 1e-30).all()
+    else:
+        assert np.allclose(got, want, rtol=8e-3 if out == "bf16" else 1e-3, atol=1e-2)
+    by_id(kid, OpKind.ReduceSum, [X], [O])  # no attrs: axis defaults to 0
+    assert np.array_equal(host(O), got), "two runs must agree bit for bit (fixed summation order)"
+    with pytest.raises(RuntimeError, match="InvalidArgument"):  # the column-sum ids accept axis 0 only
+        by_id(kid, OpKind.ReduceSum, [X], [O], RSUM, struct.pack("<q", 1))
+
+
+def test_column_sum_rank3_flattens_leading_dims(gpu):
+    x = rnd((8, 32, 128), 12)
+    O = Tensor.empty((128,))
+    by_id("reduce_sum_keep_lastdim_f32_v0", OpKind.ReduceSum, [dev(x)], [O])
+    assert_close_f32(host(O), oracle.reduce_sum_columns(x), rtol=1e-5, atol=1e-4)
+
+
+@pytest.mark.parametrize("M,N", [(256, 4096), (33, 1000), (1, 65536), (17, 1001), (5, 3)])
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("kind", ["sum", "max", "mean"])
+def test_last_axis_reductions(gpu, M, N, dt, kind):
+    x = _round(oracle.softmax_inputs(M, N, seed=2), dt)
+    O = Tensor.empty((M,))
+    opk = {"sum": OpKind.ReduceSum, "max": OpKind.ReduceMax, "mean": OpKind.ReduceMean}[kind]
+    sch, pay = (RSUM, struct.pack("<q", -1)) if kind == "sum" else (0, b"")
+    by_id(f"reduce_{kind}_lastaxis_{dt}_v0", opk, [dev(x, dt)], [O], sch, pay)
+    want = oracle.reduce_lastaxis(x, kind)
+    got = host(O)
+    if kind == "max":
+        assert np.array_equal(got, want.astype(np.float32))
+    else:
+        l1 = np.abs(x).astype(np.float64).sum(axis=1) / (N if kind == "mean" else 1)
+        assert (np.abs(got - want) <= 1e-5 * l1 + 1e-30).all()
+    if kind == "sum":  # legacy dispatch with axis -1 must route to the last-axis kernel, axis 0 to the column sum
+        op_call(OpKind.ReduceSum, [dev(x, dt)], [O], RSUM, struct.pack("<q", -1))
+        assert np.array_equal(host(O), got)
+
+
+# ------------------------------------------------------------------ softmax / cross-entropy
+@pytest.mark.parametrize("M,N", [(64, 4096), (33, 1000), (8, 32000), (16, 1001), (3, 50000), (128, 8), (5, 32768)])
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
+def test_softmax_rows(gpu, M, N, dt):
+    x = _round(oracle.softmax_inputs(M, N, seed=2), dt)
+    Y = Tensor.empty((M, N), dt)
+    by_id(f"softmax_lastdim_{dt}_v0", OpKind.Softmax, [dev(x, dt)], [Y])
+    want = oracle.softmax(x)
+    got = host(Y)
+    if dt == "f32":
+        assert_close_f32(got, want, rtol=1e-5, atol=1e-10)
+        assert np.allclose(got.astype(np.float64).sum(axis=1), 1, atol=1e-5)
+    else:
+        assert np.allclose(got, want, rtol=8e-3 if dt == "bf16" else 1e-3, atol=1e-7)
+    if dt == "f32":
+        assert np.array_equal(np.argmax(got, axis=1), np.argmax(x, axis=1))
+
+
+@pytest.mark.parametrize("B,Cn", [(64, 32000), (128, 1000), (32, 10), (7, 1001), (4, 40000), (256, 8)])
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
+def test_softmax_cross_entropy(gpu, B, Cn, dt):
+    z, y = oracle.ce_inputs(B, Cn, seed=2)
+    z = _round(z, dt)
+    D, L, A = Tensor.empty((B, Cn), dt), Tensor.empty((B,)), Tensor.empty((B,), "i32")
+    by_id(f"softmax_ce_{dt}_i32_v0", OpKind.SoftmaxCE, [dev(z, dt), dev(y)], [D, L, A])
+    wd, wl, wa = oracle.softmax_ce(z, y)
+    assert np.array_equal(A.numpy(), wa), "argmax must be bit-exact"
+    assert_close_f32(host(L), wl, rtol=1e-5, atol=1e-6, what="loss rows")
+    if dt == "f32":
+        assert_close_f32(host(D), wd, rtol=1e-5, atol=1e-12, what="dlogits")
+    else:
+        assert np.allclose(host(D), wd, rtol=8e-3 if dt == "bf16" else 1e-3, atol=1e-9)
+    # explicit scale, and the two-output form (no argmax)
+    D2, L2 = Tensor.empty((B, Cn), dt), Tensor.empty((B,))
+    by_id(f"softmax_ce_{dt}_i32_v0", OpKind.SoftmaxCE, [dev(z, dt), dev(y)], [D2, L2], SMCE, struct.pack("<f", 1.0 / 4096))
+    assert np.allclose(host(D2), oracle.softmax_ce(z, y, 1.0 / 4096)[0], rtol=1e-2 if dt != "f32" else 1e-5, atol=1e-12)
+    assert np.array_equal(host(L2), host(L))
+
+
+def test_softmax_ce_ties_and_out_of_range_labels(gpu):
+    z = np.zeros((4, 64), np.float32)
+    z[0, [5, 9]] = 3.0
+    z[1, 63] = 1.0
+    y = np.array([5, 64, -1, 0], np.int32)
+    D, L, A = Tensor.empty((4, 64)), Tensor.empty((4,)), Tensor.empty((4,), "i32")
+    by_id("softmax_ce_f32_i32_v0", OpKind.SoftmaxCE, [dev(z), dev(y)], [D, L, A])
+    wd, wl, wa = oracle.softmax_ce(z, y)
+    assert list(A.numpy()) == [5, 63, 0, 0] == list(wa)
+    assert_close_f32(host(L), wl, atol=1e-6)
+    assert_close_f32(host(D), wd, atol=1e-9)

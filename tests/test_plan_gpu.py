@@ -1,0 +1,144 @@
+"""The captured plan: small-MLP train steps (BASELINE config 1) against the NumPy execution of the same
+lowered-op list, eager vs captured replay, arena reuse, and the process-global graph API."""
+import struct
+
+import numpy as np
+import pytest
+
+import oracle
+from aicf_cuda import _C, Plan, Tensor, build_mlp_train_step, f32_to_bf16_bits
+from aicf_cuda._C import OpKind
+
+pytestmark = pytest.mark.gpu
+
+
+def host_bits(arr, dtype):
+    """Host array in the device's storage format (bf16 travels as uint16 bit patterns)."""
+    if dtype == "bf16":
+        return f32_to_bf16_bits(np.asarray(arr, np.float32))
+    return np.asarray(arr, {"f32": np.float32, "f16": np.float16, "i32": np.int32}[dtype])
+
+
+def make_plan(batch, dims, dtype, seed=0, **kw):
+    vals, low = build_mlp_train_step(batch, dims, compute_dtype=dtype, **kw)
+    plan = Plan(f"mlp_{dtype}", vals, low)
+    params = oracle.mlp_params(dims, seed)
+    x, y = oracle.mlp_batch(batch, dims[0], dims[-1], seed)
+    env, dtypes = {}, {}
+    for v in vals:
+        dtypes[v.vid] = v.dtype
+        if v.name == "x":
+            arr = x
+        elif v.name == "labels":
+            arr = y
+        elif v.name in params:
+            arr = params[v.name]
+        elif v.name.endswith(".W.lp"):
+            arr = oracle.cast(params[v.name[:-3]], v.dtype)
+        else:
+            arr = np.zeros(v.shape, np.int32 if v.dtype == "i32" else np.float32)
+        env[v.vid] = np.array(arr, copy=True)
+        if v.name in ("x", "labels") or v.name in params or v.name.endswith(".W.lp"):
+            plan.tensor(v.vid).copy_from_host(host_bits(arr, v.dtype))
+    return plan, vals, low, env, dtypes
+
+
+def test_small_mlp_ten_eager_steps_match_the_oracle(gpu):
+    plan, vals, low, env, dtypes = make_plan(64, [784, 256, 10], "f32", seed=0, with_argmax=True)
+    by = plan.by_name
+    for step in range(10):
+        plan.run()
+        plan.sync()
+        oracle.run_lowered(low, env, dtypes, np.float64)
+        assert plan.tensor("loss").numpy()[0] == pytest.approx(float(env[by["loss"]][0]), rel=1e-5), f"step {step}"
+        assert np.array_equal(plan.tensor("argmax").numpy(), env[by["argmax"]]), "argmax is bit-exact"
+    assert int(plan.tensor("opt.step").numpy()[0]) == 10
+    for name in ("0.W", "0.b", "2.W", "2.b"):
+        got, want = plan.tensor(name).numpy(), env[by[name]]
+        assert np.allclose(got, want, rtol=1e-4, atol=2e-6), name  # ten chained Adam steps on 1e-5-accurate grads
+    assert _C.gemm_status() == 0
+    plan.close()
+
+
+def test_capture_replay_equals_eager_bit_for_bit(gpu):
+    a, *_ = make_plan(64, [784, 256, 10], "f32", seed=0)
+    b, *_ = make_plan(64, [784, 256, 10], "f32", seed=0)
+    for _ in range(5):
+        a.run()
+    a.sync()
+    with pytest.raises(RuntimeError, match="replay called before capture"):
+        b.replay(1)
+    b.capture()
+    assert b.graph_nodes >= len(b.lowered)
+    b.replay(5)
+    b.sync()
+    for name in ("0.W", "2.W", "2.b", "opt.m.0.W", "loss"):
+        assert np.array_equal(a.tensor(name).numpy(), b.tensor(name).numpy()), name
+    assert int(b.tensor("opt.step").numpy()[0]) == 5  # the device counter advanced without host help
+    b.reset_graph()
+    with pytest.raises(RuntimeError, match="replay called before capture"):
+        b.replay(1)
+    a.close()
+    b.close()
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+def test_mixed_precision_mlp_tracks_the_oracle(gpu, dtype):
+    dims = [256, 512, 384, 64]
+    plan, vals, low, env, dtypes = make_plan(512, dims, dtype, seed=4, lr=1e-3, weight_decay=0.01)
+    by = plan.by_name
+    plan.capture()
+    for step in range(4):
+        plan.replay(1)
+        plan.sync()
+        oracle.run_lowered(low, env, dtypes, np.float64)
+        assert plan.tensor("loss").numpy()[0] == pytest.approx(float(env[by["loss"]][0]), rel=2e-2), f"step {step}"
+    # gradients of the last step: 16-bit operands, fp32 accumulation
+    for name in ("d_0.W", "d_2.W", "d_4.W", "d_4.b"):
+        got, want = plan.tensor(name).numpy(), env[by[name]]
+        assert np.max(np.abs(got - want)) <= 2e-2 * np.max(np.abs(want)) + 1e-7, name
+    lp = plan.tensor("2.W.lp").float_numpy()
+    assert np.array_equal(lp, oracle.cast(plan.tensor("2.W").numpy(), dtype)), "working copy == rounded master weight"
+    assert _C.gemm_status() == 0
+    plan.close()
+
+
+def test_arena_reuses_dead_buffers(gpu):
+    vals, low = build_mlp_train_step(1024, [512, 512, 512, 512, 64], compute_dtype="bf16")
+    plan = Plan("arena", vals, low)
+    assert 0 < plan.arena_bytes < plan.arena_bytes_no_reuse
+    plan.run()
+    plan.sync()
+    plan.close()
+
+
+def test_global_graph_api_like_the_reference_binding(gpu):
+    """graph_begin / op loop on the returned stream / graph_end / graph_launch, and the semantics the
+    reference's framework test relies on: scalars are read from device memory at replay time."""
+    n = 4096
+    p0 = np.ones(n, np.float32)
+    P, G, M, V = Tensor.from_numpy(p0), Tensor.from_numpy(np.full(n, 0.5, np.float32)), Tensor.zeros((n,)), Tensor.zeros((n,))
+    bc1, bc2 = Tensor.from_numpy(np.array(0.1, np.float32)), Tensor.from_numpy(np.array(0.001, np.float32))
+    pay = struct.pack("<ffff", 1e-2, 0.9, 0.999, 1e-8)
+    with pytest.raises(RuntimeError, match="graph_launch called but no captured graph exists"):
+        _C.graph_reset()
+        _C.graph_launch()
+    s = _C.graph_begin()
+    assert s != 0 and _C.graph_stream() == s
+    _C.launch_by_id("adam_step_f32_v0", OpKind.AdamStep, [P, G, M, V, bc1, bc2], [P, M, V], 0x4D414441, pay, s)
+    _C.graph_end()
+    assert _C.trace_get() == ["kid:adam_step_f32_v0 kind:adam_step"]  # graph_begin cleared the trace
+    assert np.array_equal(P.numpy(), p0), "capture records, it does not execute"
+    _C.graph_launch()
+    _C.device_sync()
+    d1 = p0 - P.numpy()
+    assert (d1 > 0).all()
+    before = P.numpy()
+    bc1.copy_from_host(np.array(1.0, np.float32))  # a 10x larger divisor => a visibly smaller update
+    _C.graph_launch()
+    _C.device_sync()
+    d2 = before - P.numpy()
+    assert (d2 < 0.5 * d1).all()
+    _C.graph_reset()
+    with pytest.raises(RuntimeError, match="graph_end called but not capturing"):
+        _C.graph_end()

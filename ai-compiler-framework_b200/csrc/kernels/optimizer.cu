@@ -59,7 +59,7 @@ bool adam_alias_violation(const TensorDesc& P, const TensorDesc& G, const Tensor
 //   kDivisorScalars = true : bias corrections are two device scalars used as divisors
 //                            (adam_step_f32_v0; reference kernel ops/adam_step/launcher.cu:257-293)
 //   kDivisorScalars = false: the int32 step counter is read and 1-beta^t formed in the kernel;
-//                            optional weight decay, optional bf16 copy of the new parameter.
+//                            optional weight decay, optional 16-bit copy of the new parameter.
 // ----------------------------------------------------------------------------------------------
 struct AdamArgs {
   const float* p;
@@ -69,7 +69,7 @@ struct AdamArgs {
   float* p_out;
   float* m_out;
   float* v_out;
-  __nv_bfloat16* p_bf16;  // may be null
+  void* p_lp;             // optional 16-bit working copy of the new parameter (bf16 or f16)
   const float* bc1;       // divisor scalars (v0 contract)
   const float* bc2;
   const int32_t* step;    // step counter (fused contract)
@@ -92,26 +92,42 @@ __device__ __forceinline__ void adam_one(float p, float g, float m, float v, con
   p_new = base - h.lr * (m_hat / denom);
 }
 
-__device__ __forceinline__ void store_bf16x4(__nv_bfloat16* dst, int64_t packet, const Pack16<float>& f) {
-  const __nv_bfloat162 lo = __floats2bfloat162_rn(f.v[0], f.v[1]);
-  const __nv_bfloat162 hi = __floats2bfloat162_rn(f.v[2], f.v[3]);
+// kLp: 0 = no copy, 1 = bf16, 2 = f16
+template <int kLp>
+__device__ __forceinline__ void store_lp_x4(void* dst, int64_t packet, const Pack16<float>& f) {
   uint2 w;
-  w.x = *reinterpret_cast<const uint32_t*>(&lo);
-  w.y = *reinterpret_cast<const uint32_t*>(&hi);
+  if (kLp == 1) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(f.v[0], f.v[1]);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(f.v[2], f.v[3]);
+    w.x = *reinterpret_cast<const uint32_t*>(&lo);
+    w.y = *reinterpret_cast<const uint32_t*>(&hi);
+  } else {
+    const __half2 lo = __floats2half2_rn(f.v[0], f.v[1]);
+    const __half2 hi = __floats2half2_rn(f.v[2], f.v[3]);
+    w.x = *reinterpret_cast<const uint32_t*>(&lo);
+    w.y = *reinterpret_cast<const uint32_t*>(&hi);
+  }
   reinterpret_cast<uint2*>(dst)[packet] = w;
 }
+template <int kLp>
+__device__ __forceinline__ void store_lp_x1(void* dst, int64_t k, float v) {
+  if (kLp == 1) static_cast<__nv_bfloat16*>(dst)[k] = __float2bfloat16_rn(v);
+  if (kLp == 2) static_cast<__half*>(dst)[k] = __float2half_rn(v);
+}
 
-template <bool kDivisorScalars, bool kBf16Copy>
+template <bool kDivisorScalars, int kLp>
 __global__ void __launch_bounds__(256) adam_kernel(AdamArgs a) {
   float d1, d2;
   if (kDivisorScalars) {
     d1 = a.bc1[0];
     d2 = a.bc2[0];
   } else {
+    // 1 - beta^t cancels badly in fp32 for beta close to 1; two double pow() per thread are free
+    // next to the memory traffic and give correctly rounded divisors.
     int t = a.step[0];
     if (t < 1) t = 1;
-    d1 = 1.0f - powf(a.h.beta1, static_cast<float>(t));
-    d2 = 1.0f - powf(a.h.beta2, static_cast<float>(t));
+    d1 = static_cast<float>(1.0 - pow(static_cast<double>(a.h.beta1), static_cast<double>(t)));
+    d2 = static_cast<float>(1.0 - pow(static_cast<double>(a.h.beta2), static_cast<double>(t)));
   }
   using V4 = Pack16<float>;
   const V4* P = reinterpret_cast<const V4*>(a.p);
@@ -147,7 +163,7 @@ __global__ void __launch_bounds__(256) adam_kernel(AdamArgs a) {
       st_stream(Mo + j, mo);
       st_stream(Vo + j, vo);
       st_stream(Po + j, po);
-      if (kBf16Copy) store_bf16x4(a.p_bf16, j, po);
+      if (kLp) store_lp_x4<kLp>(a.p_lp, j, po);
     }
   }
   for (; i < a.nvec; i += stride) {
@@ -159,7 +175,7 @@ __global__ void __launch_bounds__(256) adam_kernel(AdamArgs a) {
     st_stream(Mo + i, mo);
     st_stream(Vo + i, vo);
     st_stream(Po + i, po);
-    if (kBf16Copy) store_bf16x4(a.p_bf16, i, po);
+    if (kLp) store_lp_x4<kLp>(a.p_lp, i, po);
   }
   // elements not covered by packets: the n % 4 tail, or everything when a buffer is not 16-byte aligned
   for (int64_t k = (a.nvec << 2) + tid; k < a.n; k += stride) {
@@ -168,23 +184,23 @@ __global__ void __launch_bounds__(256) adam_kernel(AdamArgs a) {
     a.m_out[k] = mo;
     a.v_out[k] = vo;
     a.p_out[k] = po;
-    if (kBf16Copy) a.p_bf16[k] = __float2bfloat16_rn(po);
+    if (kLp) store_lp_x1<kLp>(a.p_lp, k, po);
   }
 }
 
-template <bool kDiv, bool kBf>
+template <bool kDiv, int kLp>
 Status launch_adam(AdamArgs a, cudaStream_t stream) {
   if (a.n <= 0) return Status::Ok;
   const void* ptrs[] = {a.p, a.g, a.m, a.v, a.p_out, a.m_out, a.v_out};
   bool vec_ok = true;
   for (const void* q : ptrs) vec_ok = vec_ok && aligned_to(q, 16);
-  if (kBf) vec_ok = vec_ok && aligned_to(a.p_bf16, 8);
+  if (kLp) vec_ok = vec_ok && aligned_to(a.p_lp, 8);
   a.nvec = vec_ok ? (a.n >> 2) : 0;
   constexpr int kThreads = 256;
   const int64_t items = vec_ok ? (a.nvec / 2 + 1) : a.n;
   const int grid = streaming_grid(items, kThreads, 4);  // 64 regs x 256 threads: 4 blocks resident per SM
   cudaGetLastError();
-  adam_kernel<kDiv, kBf><<<grid, kThreads, 0, stream>>>(a);
+  adam_kernel<kDiv, kLp><<<grid, kThreads, 0, stream>>>(a);
   return launch_status();
 }
 
@@ -220,12 +236,12 @@ Status adam_v0_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, con
   a.n = numel_raw(in[0]);
   a.h = read_adam(attr);
   a.h.weight_decay = 0.0f;  // the v0 contract has no decay term
-  return launch_adam<true, false>(a, stream);
+  return launch_adam<true, 0>(a, stream);
 }
 size_t no_workspace(const TensorDesc*, int, const void*) { return 0; }
 
 // ---------------------------------------------------------------- adam_step_f32_fused_v1
-// inputs [P,G,M,V,step(i32 scalar)] -> outputs [P,M,V] or [P,M,V,P_bf16]; textbook Adam with
+// inputs [P,G,M,V,step(i32 scalar)] -> outputs [P,M,V] or [P,M,V,P_lp (bf16|f16 copy)]; textbook Adam with
 // bias correction 1-beta^t computed from the device step counter (t clamped to >= 1).
 bool i32_scalar(const TensorDesc& d) {
   return d.dtype == DType::kI32 && (d.rank() == 0 || (d.rank() == 1 && d.shape[0] == 1));
@@ -240,7 +256,8 @@ bool adam_v1_check(const TensorDesc* in, int ni, const TensorDesc* out, int no) 
   if (!same_shape(in[0], in[1]) || !same_shape(in[0], in[2]) || !same_shape(in[0], in[3])) return false;
   if (!same_shape(in[0], out[0]) || !same_shape(in[2], out[1]) || !same_shape(in[3], out[2])) return false;
   if (no == 4) {
-    if (out[3].dtype != DType::kBF16 || !out[3].contiguous || !same_shape(in[0], out[3])) return false;
+    if ((out[3].dtype != DType::kBF16 && out[3].dtype != DType::kF16) || !out[3].contiguous || !same_shape(in[0], out[3]))
+      return false;
     for (int i = 0; i < 4; ++i)
       if (same_ptr(out[3], in[i])) return false;
   }
@@ -261,10 +278,11 @@ Status adam_v1_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, con
   a.p_out = static_cast<float*>(out[0].data);
   a.m_out = static_cast<float*>(out[1].data);
   a.v_out = static_cast<float*>(out[2].data);
-  a.p_bf16 = no == 4 ? static_cast<__nv_bfloat16*>(out[3].data) : nullptr;
+  a.p_lp = no == 4 ? out[3].data : nullptr;
   a.n = numel_raw(in[0]);
   a.h = read_adam(attr);
-  return no == 4 ? launch_adam<false, true>(a, stream) : launch_adam<false, false>(a, stream);
+  if (no != 4) return launch_adam<false, 0>(a, stream);
+  return out[3].dtype == DType::kBF16 ? launch_adam<false, 1>(a, stream) : launch_adam<false, 2>(a, stream);
 }
 
 // ---------------------------------------------------------------- step_inc

@@ -84,6 +84,10 @@ def test_capture_replay_equals_eager_bit_for_bit(gpu):
 
 @pytest.mark.parametrize("dtype", ["bf16", "f16"])
 def test_mixed_precision_mlp_tracks_the_oracle(gpu, dtype):
+    """16-bit GEMMs over fp32 master weights. Gradients are compared after the FIRST step: Adam's early
+    updates are sign-like (|update| ~ lr whatever the gradient's size), so two correct executions that
+    differ in the last bit drift apart within a few steps - the fp32 and fp64 NumPy runs of this graph
+    already differ by 10% in d_0.W after three steps. The loss, an average, stays comparable."""
     dims = [256, 512, 384, 64]
     plan, vals, low, env, dtypes = make_plan(512, dims, dtype, seed=4, lr=1e-3, weight_decay=0.01)
     by = plan.by_name
@@ -92,11 +96,14 @@ def test_mixed_precision_mlp_tracks_the_oracle(gpu, dtype):
         plan.replay(1)
         plan.sync()
         oracle.run_lowered(low, env, dtypes, np.float64)
-        assert plan.tensor("loss").numpy()[0] == pytest.approx(float(env[by["loss"]][0]), rel=2e-2), f"step {step}"
-    # gradients of the last step: 16-bit operands, fp32 accumulation
-    for name in ("d_0.W", "d_2.W", "d_4.W", "d_4.b"):
-        got, want = plan.tensor(name).numpy(), env[by[name]]
-        assert np.max(np.abs(got - want)) <= 2e-2 * np.max(np.abs(want)) + 1e-7, name
+        assert plan.tensor("loss").numpy()[0] == pytest.approx(float(env[by["loss"]][0]), rel=2e-3), f"step {step}"
+        if step == 0:
+            for name in ("d_0.W", "d_2.W", "d_4.W", "d_0.b", "d_4.b"):
+                got, want = plan.tensor(name).numpy(), env[by[name]]
+                assert np.max(np.abs(got - want)) <= 5e-3 * np.max(np.abs(want)), name
+            for name in ("0.W", "4.W", "opt.m.2.W", "opt.v.2.W"):
+                got, want = plan.tensor(name).numpy(), env[by[name]]
+                assert np.max(np.abs(got - want)) <= 5e-3 * np.max(np.abs(want)), name
     lp = plan.tensor("2.W.lp").float_numpy()
     assert np.array_equal(lp, oracle.cast(plan.tensor("2.W").numpy(), dtype)), "working copy == rounded master weight"
     assert _C.gemm_status() == 0

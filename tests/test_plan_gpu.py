@@ -98,9 +98,9 @@ def test_mixed_precision_mlp_tracks_the_oracle(gpu, dtype):
         oracle.run_lowered(low, env, dtypes, np.float64)
         assert plan.tensor("loss").numpy()[0] == pytest.approx(float(env[by["loss"]][0]), rel=2e-3), f"step {step}"
         if step == 0:
-            for name in ("d_0.W", "d_2.W", "d_4.W", "d_0.b", "d_4.b"):
+            for name in ("d_0.W", "d_2.W", "d_4.W", "d_0.b", "d_4.b"):  # 16-bit GEMM tolerance: 2e-2 normwise
                 got, want = plan.tensor(name).numpy(), env[by[name]]
-                assert np.max(np.abs(got - want)) <= 5e-3 * np.max(np.abs(want)), name
+                assert np.max(np.abs(got - want)) <= 2e-2 * np.max(np.abs(want)), name
             for name in ("0.W", "4.W", "opt.m.2.W", "opt.v.2.W"):
                 got, want = plan.tensor(name).numpy(), env[by[name]]
                 assert np.max(np.abs(got - want)) <= 5e-3 * np.max(np.abs(want)), name

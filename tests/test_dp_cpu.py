@@ -1,0 +1,109 @@
+"""Data-parallel host logic on CPU: two gloo ranks execute the data-parallel lowered graph with the NumPy
+interpreter on their shards (all_reduce = gloo sum) and must reproduce the single-process run on the whole
+batch. Checks the sharding rule, the 1/global-batch loss scale and the placement of all_reduce ops."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+REPO = Path(__file__).resolve().parents[1]
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _env_for(vals, params, x, y):
+    import oracle
+    env, dtypes = {}, {}
+    for v in vals:
+        dtypes[v.vid] = v.dtype
+        if v.name == "x":
+            env[v.vid] = x
+        elif v.name == "labels":
+            env[v.vid] = y
+        elif v.name in params:
+            env[v.vid] = params[v.name].copy()
+        else:
+            env[v.vid] = np.zeros(v.shape, np.int32 if v.dtype == "i32" else np.float32)
+    return env, dtypes
+
+
+DIMS, GLOBAL_BATCH, STEPS = [32, 48, 10], 64, 3
+
+
+def _worker(rank: int, world: int, port: int, out_dir: str):
+    for p in (REPO, REPO / "ai-compiler-framework_b200" / "python"):
+        sys.path.insert(0, str(p))
+    import torch
+    import torch.distributed as td
+    import oracle
+    from aicf_cuda import build_mlp_train_step
+    from aicf_cuda.dp import shard_rows
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    td.init_process_group("gloo", rank=rank, world_size=world)
+    lo, hi = shard_rows(GLOBAL_BATCH, rank, world)
+    vals, low = build_mlp_train_step(hi - lo, DIMS, compute_dtype="f32", global_batch=GLOBAL_BATCH, data_parallel=True)
+    x, y = oracle.mlp_batch(GLOBAL_BATCH, DIMS[0], DIMS[-1], seed=4)
+    env, dtypes = _env_for(vals, oracle.mlp_params(DIMS, seed=4), x[lo:hi], y[lo:hi])
+
+    def world_sum(vid, local):  # gloo sums in rank order for two ranks
+        t = torch.from_numpy(np.array(local, dtype=np.float64))
+        td.all_reduce(t)
+        return t.numpy()
+
+    for _ in range(STEPS):
+        oracle.run_lowered(low, env, dtypes, np.float64, world_grads=world_sum)
+    by = {v.name: v.vid for v in vals}
+    np.savez(Path(out_dir) / f"rank{rank}.npz", W0=env[by["0.W"]], W2=env[by["2.W"]], b2=env[by["2.b"]], loss=env[by["loss"]])
+    td.destroy_process_group()
+
+
+def test_two_gloo_ranks_reproduce_the_single_process_step(tmp_path):
+    import torch.multiprocessing as mp
+    import oracle
+    from aicf_cuda import build_mlp_train_step
+    port = _free_port()
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    vals, low = build_mlp_train_step(GLOBAL_BATCH, DIMS, compute_dtype="f32")
+    x, y = oracle.mlp_batch(GLOBAL_BATCH, DIMS[0], DIMS[-1], seed=4)
+    env, dtypes = _env_for(vals, oracle.mlp_params(DIMS, seed=4), x, y)
+    for _ in range(STEPS):
+        oracle.run_lowered(low, env, dtypes, np.float64)
+    by = {v.name: v.vid for v in vals}
+    r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
+    for k, name in (("W0", "0.W"), ("W2", "2.W"), ("b2", "2.b")):
+        assert np.array_equal(r0[k], r1[k]), "replicas must stay identical"
+        assert np.allclose(r0[k], env[by[name]], rtol=1e-5, atol=1e-7), name
+    # each rank reports the mean loss of its shard; their average is the global mean
+    assert (r0["loss"][0] + r1["loss"][0]) / 2 == pytest.approx(float(env[by["loss"]][0]), rel=1e-5)
+
+
+def test_sharding_rule_and_lowering_shape():
+    from aicf_cuda import build_mlp_train_step
+    from aicf_cuda.dp import loss_scale, shard_rows
+    assert [shard_rows(65536, r, 8) for r in (0, 7)] == [(0, 8192), (57344, 65536)]
+    with pytest.raises(ValueError):
+        shard_rows(10, 0, 3)
+    with pytest.raises(ValueError):
+        shard_rows(8, 2, 2)
+    assert loss_scale(65536) == 1.0 / 65536
+    vals, low = build_mlp_train_step(8192, [8192] * 5 + [1000], compute_dtype="bf16", global_batch=65536, data_parallel=True)
+    names = [it["op"] for it in low]
+    assert names.count("all_reduce") == 10 and names.count("gemm") == 9 and names.count("gemm_epilogue") == 5
+    # every all_reduce sits after the op that produces its gradient and before the Adam that consumes it
+    for i, it in enumerate(low):
+        if it["op"] == "all_reduce":
+            g = it["inputs"][0]
+            producer = max(j for j, o in enumerate(low[:i]) if g in o["outputs"] and o["op"] != "all_reduce")
+            consumer = min(j for j, o in enumerate(low) if o["op"] == "adam_step" and g in o["inputs"])
+            assert producer < i < consumer
+    ce = next(it for it in low if it["op"] == "softmax_ce")
+    assert ce["attrs"]["scale"] == 1.0 / 65536
+    params = sum(int(np.prod(v.shape)) for v in vals if v.role == 1)
+    assert params == 276_661_224

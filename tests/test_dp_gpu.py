@@ -1,0 +1,60 @@
+"""Data-parallel captured MLP on 2 GPUs (skipped with fewer): replicas stay bit-identical, the all-reduced
+gradient equals the single-device gradient of the whole batch, weights track the oracle."""
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import aicf_cuda
+import oracle
+from aicf_cuda import build_mlp_train_step
+
+pytestmark = pytest.mark.gpu
+HERE = Path(__file__).resolve().parent
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_two_rank_captured_step(gpu, tmp_path, dtype):
+    if aicf_cuda.lib.aicf_b200_device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    port = str(_free_port())
+    procs = [subprocess.Popen([sys.executable, str(HERE / "dp_worker.py"), str(r), "2", port, str(tmp_path), dtype])
+             for r in range(2)]
+    for p in procs:
+        assert p.wait(timeout=300) == 0
+    r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
+    for k in ("W0", "W4", "b4", "dW0"):
+        assert np.array_equal(r0[k], r1[k]), f"{k}: replicas diverged"
+    assert int(r0["step"][0]) == 3 and int(r0["status"][0]) == 0 and int(r1["status"][0]) == 0
+
+    dims, gbatch = [256, 512, 384, 64], 1024
+    vals, low = build_mlp_train_step(gbatch, dims, compute_dtype=dtype)
+    params = oracle.mlp_params(dims, seed=4)
+    x, y = oracle.mlp_batch(gbatch, dims[0], dims[-1], seed=4)
+    env, dtypes = {}, {}
+    for v in vals:
+        dtypes[v.vid] = v.dtype
+        arr = x if v.name == "x" else y if v.name == "labels" else params.get(v.name)
+        if arr is None and v.name.endswith(".W.lp"):
+            arr = oracle.cast(params[v.name[:-3]], v.dtype)
+        env[v.vid] = np.array(arr, copy=True) if arr is not None else np.zeros(v.shape, np.int32 if v.dtype == "i32" else np.float32)
+    by = {v.name: v.vid for v in vals}
+    oracle.run_lowered(low, env, dtypes, np.float64)
+    tol = 1e-4 if dtype == "f32" else 2e-2
+    if dtype == "f32":
+        for _ in range(2):
+            oracle.run_lowered(low, env, dtypes, np.float64)
+        for k, name in (("W0", "0.W"), ("W4", "4.W"), ("b4", "4.b")):
+            assert np.allclose(r0[k], env[by[name]], rtol=1e-4, atol=2e-6), name
+        want = env[by["d_0.W"]]
+        assert np.max(np.abs(r0["dW0"] - want)) <= tol * np.max(np.abs(want))
+    assert (r0["loss"][0] + r1["loss"][0]) / 2 == pytest.approx(float(env[by["loss"]][0]), rel=0.1 if dtype != "f32" else 1e-4)

@@ -48,13 +48,13 @@ def test_two_rank_captured_step(gpu, tmp_path, dtype):
             arr = oracle.cast(params[v.name[:-3]], v.dtype)
         env[v.vid] = np.array(arr, copy=True) if arr is not None else np.zeros(v.shape, np.int32 if v.dtype == "i32" else np.float32)
     by = {v.name: v.vid for v in vals}
-    oracle.run_lowered(low, env, dtypes, np.float64)
-    tol = 1e-4 if dtype == "f32" else 2e-2
+    for _ in range(3):
+        oracle.run_lowered(low, env, dtypes, np.float64)
     if dtype == "f32":
-        for _ in range(2):
-            oracle.run_lowered(low, env, dtypes, np.float64)
         for k, name in (("W0", "0.W"), ("W4", "4.W"), ("b4", "4.b")):
             assert np.allclose(r0[k], env[by[name]], rtol=1e-4, atol=2e-6), name
         want = env[by["d_0.W"]]
-        assert np.max(np.abs(r0["dW0"] - want)) <= tol * np.max(np.abs(want))
-    assert (r0["loss"][0] + r1["loss"][0]) / 2 == pytest.approx(float(env[by["loss"]][0]), rel=0.1 if dtype != "f32" else 1e-4)
+        assert np.max(np.abs(r0["dW0"] - want)) <= 1e-4 * np.max(np.abs(want))
+    # each rank reports the mean loss of its shard (16-bit runs: weights drift chaotically under Adam's sign-like
+    # first steps, the loss stays comparable)
+    assert (r0["loss"][0] + r1["loss"][0]) / 2 == pytest.approx(float(env[by["loss"]][0]), rel=1e-4 if dtype == "f32" else 2e-2)

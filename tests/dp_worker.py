@@ -35,12 +35,13 @@ def main():
     td.barrier()
     plan.run()          # one eager step (all_reduce on the side stream)
     plan.sync()
+    first = dict(dW0_step1=plan.tensor("d_0.W").numpy(), W0_step1=plan.tensor("0.W").numpy(), loss_step1=plan.tensor("loss").numpy())
     plan.capture()      # then captured replays with the NCCL nodes inside the graph
     plan.replay(steps - 1)
     plan.sync()
     np.savez(Path(out_dir) / f"rank{rank}.npz", W0=plan.tensor("0.W").numpy(), W4=plan.tensor("4.W").numpy(),
              b4=plan.tensor("4.b").numpy(), dW0=plan.tensor("d_0.W").numpy(), loss=plan.tensor("loss").numpy(),
-             step=plan.tensor("opt.step").numpy(), status=np.array([_C.gemm_status()]))
+             step=plan.tensor("opt.step").numpy(), status=np.array([_C.gemm_status()]), **first)
     plan.close()
     td.barrier()
     dp.finalize()

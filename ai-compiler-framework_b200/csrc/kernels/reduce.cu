@@ -7,6 +7,10 @@
 // gives a column to a whole block and reads it with stride N). Rows are split over gridDim.y so the
 // grid fills the SMs; with more than one split the per-split partial sums go to a scratch buffer
 // [splits, N] (fp32) and a second kernel adds them in split order.
+#include <mutex>
+#include <string>
+
+#include "../capi/capi_internal.hpp"
 #include "common.cuh"
 
 namespace aicf::cuda {
@@ -325,6 +329,41 @@ KernelVariant make_reduce_sum_lastdim_bf16_variant() {
               colsum_supported<DType::kBF16, DType::kBF16>, colsum_workspace<__nv_bfloat16>);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Column sum for callers that cannot allocate (aicf_b200_colsum_f32_noalloc).
+//
+// The per-split partial sums live in a fixed array in device memory that is part of the library
+// image: every GPU that loads the library carries these 512 KiB until the process exits, and no
+// allocation call is ever made on its behalf. `g_noalloc_scratch` names the array for device code;
+// on the host the same name is only a handle for the runtime, so the address kernels receive is
+// looked up once per device with cudaGetSymbolAddress while that device is current.
+// ------------------------------------------------------------------------------------------------
+constexpr size_t kNoAllocScratchBytes = size_t(512) << 10;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchBytes / sizeof(float)];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mu;
+
+// Device address of the scratch array on the current device (looked up on the first call there).
+cudaError_t noalloc_scratch_for_current_device(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (!g_noalloc_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return e;
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return cudaSuccess;
+}
+}  // namespace
+
 #define AICF_ROWREDUCE(fn, nm, DT, OP, T) \
   KernelVariant fn() { return make(nm, rowreduce_launch<DT, OP, T>, rowreduce_supported<DT, OP>, no_workspace); }
 AICF_ROWREDUCE(make_reduce_sum_lastaxis_f32_variant, "rowsum_f32_sm100", DType::kF32, RowOp::Sum, float)
@@ -338,3 +377,28 @@ AICF_ROWREDUCE(make_reduce_mean_lastaxis_bf16_variant, "rowmean_bf16_sm100", DTy
 AICF_ROWREDUCE(make_reduce_mean_lastaxis_f16_variant, "rowmean_f16_sm100", DType::kF16, RowOp::Mean, __half)
 
 }  // namespace aicf::cuda
+
+extern "C" int aicf_b200_colsum_f32_noalloc(const float* x, float* out, int64_t rows, int64_t cols, aicf_stream stream) {
+  using namespace aicf::cuda;
+  using aicf::capi::fail;
+  if (!x || !out || rows <= 0 || cols <= 0) return fail(Status::InvalidArgument, "colsum_f32_noalloc: null pointer or empty shape");
+  const size_t need = colsum_f32_scratch_bytes(x, rows, cols);
+  if (need > kNoAllocScratchBytes) {
+    return fail(Status::InvalidArgument,
+                "colsum_f32_noalloc: [" + std::to_string(rows) + "," + std::to_string(cols) + "] needs " +
+                    std::to_string(need) + " bytes of scratch, the built-in array holds " +
+                    std::to_string(kNoAllocScratchBytes) + "; use reduce_sum_keep_lastdim_f32_v0 with a workspace");
+  }
+  float* scratch = nullptr;
+  const cudaError_t e = noalloc_scratch_for_current_device(&scratch);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(Status::Internal, std::string("colsum_f32_noalloc: cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+  }
+  // Partials are fully rewritten for every (split, column) that the second pass reads, so nothing
+  // left over from an earlier call needs clearing.
+  const Status st = colsum_f32_direct(x, out, rows, cols, scratch, kNoAllocScratchBytes,
+                                      reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(stream)));
+  if (!ok(st)) return fail(st, std::string("colsum_f32_noalloc: launch failed: ") + status_to_string(st));
+  return AICF_OK;
+}

@@ -64,6 +64,7 @@ PROTOTYPES = {
     "aicf_b200_kernel_id": (_cp, [_i, _i]),
     "aicf_b200_num_op_kinds": (_i, []),
     "aicf_b200_gemm_status": (_i, [_i]),
+    "aicf_b200_colsum_f32_noalloc": (_i, [_vp, _vp, C.c_int64, C.c_int64, _u64]),
     "aicf_b200_trace_enable": (None, [_i]),
     "aicf_b200_trace_reset": (None, []),
     "aicf_b200_trace_count": (_i, []),

@@ -95,6 +95,23 @@ int aicf_b200_num_op_kinds(void);
  * device. No counterpart in the reference (its kernels have no device-side waits). */
 int aicf_b200_gemm_status(int clear);
 
+/* Column sum [rows, cols] -> [cols] (fp32, row-major, contiguous) for callers that must not allocate
+ * device memory: a host that was given a fixed memory budget up front, or code that runs where the
+ * CUDA allocator is off limits - for example a KernelVariant::launch body, which by contract may only
+ * enqueue work and which the reference's dispatcher always hands a null workspace. No counterpart in
+ * the reference.
+ * Same kernels and summation order as reduce_sum_keep_lastdim_f32_v0, but the partial sums go to a
+ * 512 KiB array built into the library's device image instead of a caller- or library-allocated
+ * workspace; cudaMalloc / cudaFree are never called. Shapes whose partial sums need more than
+ * AICF_B200_NOALLOC_SCRATCH_BYTES return InvalidArgument (the message names the need).
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+ * that first call before starting any stream capture. All calls on a device share the one array and
+ * it keeps whatever the last call left in it (each call rewrites every partial it later reads, so
+ * nothing has to be cleared); two calls that overlap on the GPU - different streams without an
+ * ordering between them - race on it. */
+#define AICF_B200_NOALLOC_SCRATCH_BYTES (512u * 1024u)
+int aicf_b200_colsum_f32_noalloc(const float* x, float* out, int64_t rows, int64_t cols, aicf_stream stream);
+
 /* ---- op trace ------------------------------------------------------------------------------
  * Replaces trace_enable / trace_reset / trace_get of the reference binding
  * (src/python_bindings/bindings.cpp:193-231,459-472). Entries are "<opname>" for op_call and

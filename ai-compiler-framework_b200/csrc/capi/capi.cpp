@@ -11,6 +11,8 @@
 
 namespace aicf::cuda {
 int gemm_tcgen05_status(bool clear);
+int row_pipeline_status(bool clear);
+int gemm_tcgen05_timeline(int enable, unsigned long long* out16);
 }
 
 static_assert(sizeof(aicf_tensor_desc) == sizeof(aicf::cuda::TensorDesc), "C and C++ tensor descriptors must match");
@@ -231,6 +233,15 @@ const char* aicf_b200_kernel_id(int op_kind, int index) {
 }
 
 int aicf_b200_gemm_status(int clear) { return aicf::cuda::gemm_tcgen05_status(clear != 0); }
+int aicf_b200_gemm_timeline(int enable, uint64_t* out16) {
+  return aicf::cuda::gemm_tcgen05_timeline(enable, reinterpret_cast<unsigned long long*>(out16)) == 0 ? AICF_OK : AICF_INTERNAL;
+}
+int aicf_b200_wait_status(int clear) {
+  const int g = aicf::cuda::gemm_tcgen05_status(clear != 0);
+  const int r = aicf::cuda::row_pipeline_status(clear != 0);
+  if (g < 0 || r < 0) return -1;
+  return (g & 0xFFFF) | (r ? 0x10000 : 0);
+}
 
 // ---- trace ------------------------------------------------------------------------------------
 void aicf_b200_trace_enable(int flag) {

@@ -40,9 +40,18 @@ constexpr int kThreads = 192;
 constexpr int kGroupM = 16;   // tile rasterisation: 16 row-tiles share their column tiles in L2
 constexpr unsigned long long kWaitBudgetNs = 1000000000ull;
 
-constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + 256 /*barriers etc.*/;
+constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + 256 /*barriers etc.*/ +
+                              4 * kTileN * sizeof(float) /*bias staging, one strip per epilogue warp*/;
 
 __device__ int g_gemm_status = 0;  // 0 ok; otherwise (role << 8) | reason of the first CTA that gave up
+
+// Optional timeline of CTA 0 (nanoseconds from %globaltimer), for tuning. Off unless the host enables it.
+//  [0] kernel start  [1] set-up done  [2] first TMA issued  [3] first stage landed  [4] first tile's MMAs issued
+//  [5] first accumulator ready  [6] first tile stored  [7] last tile stored  [8] kernel end
+//  [9] MMA wait-for-data ns  [10] MMA wait-for-accumulator ns  [11] producer wait-for-slot ns
+//  [12] epilogue wait-for-accumulator ns  [13] epilogue busy ns  [14] tiles done by CTA 0
+__device__ int g_gemm_timeline_on = 0;
+__device__ unsigned long long g_gemm_timeline[16];
 
 struct GemmParams {
   void* C;
@@ -170,6 +179,80 @@ __device__ __forceinline__ float bias_at(const GemmParams& p, int col) {
   return __half2float(static_cast<const __half*>(p.bias)[col * p.bias_stride]);
 }
 
+// Two adjacent 32-column chunks in one go: both loads are in flight together, one wait.
+__device__ __forceinline__ void tmem_ld_32x32_pair(uint32_t taddr, uint32_t (&r)[64]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]),
+        "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]),
+        "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),
+        "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]),
+        "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr)
+      : "memory");
+}
+
+// One thread's 32 consecutive output columns of one row: + bias (from shared memory), ReLU, convert, store.
+// Every array index is a compile-time constant so the values stay in registers.
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int row, int col0, const uint32_t* r,
+                                               const float* bias_s) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) + bias_s[j];
+  if (p.relu) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+  }
+  if (row >= p.M) return;
+  const int64_t off = static_cast<int64_t>(row) * p.ldc + col0;
+  const bool full_chunk = (col0 + 32 <= p.N) && p.c_vec_ok;
+  if (p.c_dtype == static_cast<int>(DType::kF32)) {
+    float* dst = static_cast<float*>(p.C) + off;
+    if (full_chunk) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        reinterpret_cast<float4*>(dst)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) dst[j] = v[j];
+    }
+    return;
+  }
+  uint32_t packed[16];
+  if (p.c_dtype == static_cast<int>(DType::kBF16)) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+      packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  }
+  uint16_t* dst = static_cast<uint16_t*>(p.C) + off;
+  if (full_chunk) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      reinterpret_cast<uint4*>(dst)[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N) dst[j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xFFFFu));
+  }
+}
+
 // ------------------------------------------------------------------ kernel
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -185,12 +268,15 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* misc = base_ptr + kStages * kStageBytes + 16 * kStages + 16 * kAccBufs;
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 4);
+  float* bias_smem = reinterpret_cast<float*>(base_ptr + kStages * kStageBytes + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + kTileN - 1) / kTileN;
   const int num_tiles = tiles_m * tiles_n;
   const int k_blocks = (p.K + kTileK - 1) / kTileK;
 
+  const bool tl = g_gemm_timeline_on != 0 && blockIdx.x == 0;
+  if (tl && threadIdx.x == 0) g_gemm_timeline[0] = global_ns();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
@@ -209,6 +295,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
+  if (tl && threadIdx.x == 0) g_gemm_timeline[1] = global_ns();
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -216,12 +303,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
+      unsigned long long waited = 0;
+      bool first = true;
       for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
         int tm, tn;
         tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
         const int m0 = tm * kTileM, n0 = tn * kTileN;
         for (int kb = 0; kb < k_blocks; ++kb) {
+          const unsigned long long w0 = tl ? global_ns() : 0;
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1)) { alive = false; break; }
+          if (tl) {
+            waited += global_ns() - w0;
+            if (first) { g_gemm_timeline[2] = global_ns(); first = false; }
+          }
           const uint32_t full = bar_full + 8 * stage;
           const uint32_t sa = base + stage * kStageBytes, sb = sa + kAStageBytes;
           const int k0 = kb * kTileK;
@@ -241,6 +335,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
+      if (tl) g_gemm_timeline[11] = waited;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -253,12 +348,21 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool alive = true;
       const uint32_t a_step = p.a_mn_major ? (2 * 1024) >> 4 : (kUmmaK * 2) >> 4;  // descriptor units of 16 B
       const uint32_t b_step = p.b_mn_major ? (2 * 1024) >> 4 : (kUmmaK * 2) >> 4;
+      unsigned long long wait_data = 0, wait_acc = 0;
+      bool first = true, first_tile = true;
       for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+        unsigned long long w0 = tl ? global_ns() : 0;
         if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, 2)) { alive = false; break; }
+        if (tl) wait_acc += global_ns() - w0;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * kTileN;
         for (int kb = 0; kb < k_blocks; ++kb) {
+          w0 = tl ? global_ns() : 0;
           if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3)) { alive = false; break; }
+          if (tl) {
+            wait_data += global_ns() - w0;
+            if (first) { g_gemm_timeline[3] = global_ns(); first = false; }
+          }
           tc_fence_after();
           const uint32_t sa = base + stage * kStageBytes, sb = sa + kAStageBytes;
           const uint64_t adesc = make_smem_desc(sa, p.a_mn_major);
@@ -271,8 +375,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         if (!alive) break;
         umma_commit(bar_acc_full + 8 * acc);   // accumulator complete
+        if (tl && first_tile) { g_gemm_timeline[4] = global_ns(); first_tile = false; }
         if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
       }
+      if (tl) { g_gemm_timeline[9] = wait_data; g_gemm_timeline[10] = wait_acc; }
     }
     __syncwarp();
   } else {
@@ -281,77 +387,59 @@ __global__ void __launch_bounds__(kThreads, 1)
     int acc = 0;
     uint32_t acc_phase = 0;
     bool alive = true;
+    const bool tle = tl && warp == 2 && lane == 0;
+    unsigned long long e_wait = 0, e_busy = 0, e_tiles = 0;
     for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
       const int row = tm * kTileM + sub * 32 + lane;
       const int n0 = tn * kTileN;
+      const unsigned long long e0 = tle ? global_ns() : 0;
       // the TMEM loads below are warp-collective: the whole warp proceeds or the whole warp leaves
       if (!__all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, 4))) { alive = false; break; }
       tc_fence_after();
+      const unsigned long long e1 = tle ? global_ns() : 0;
+      if (tle) {
+        e_wait += e1 - e0;
+        if (e_tiles == 0) g_gemm_timeline[5] = e1;
+      }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * kTileN;
+      // bias of this tile's 256 columns -> this warp's private strip of shared memory (no cross-warp barrier,
+      // so a warp that gives up on a wait can never leave another one stuck)
+      float* bs = bias_smem + (warp - 2) * kTileN;
+#pragma unroll
+      for (int h = 0; h < kTileN / 32; ++h) {
+        const int col = n0 + lane + 32 * h;
+        bs[lane + 32 * h] = (p.bias_dtype != 0 && col < p.N) ? bias_at(p, col) : 0.0f;
+      }
+      __syncwarp();
 #pragma unroll 1
-      for (int c = 0; c < kTileN / 32; ++c) {
+      for (int c = 0; c < kTileN / 32; c += 2) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;  // warp-uniform
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (p.bias_dtype != 0) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) v[j] += bias_at(p, col0 + j);
+        uint32_t r[64];
+        const bool two = col0 + 32 < p.N;  // warp-uniform
+        if (two) {
+          tmem_ld_32x32_pair(taddr + c * 32, r);
+        } else {
+          tmem_ld_32x32(taddr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
         }
-        if (p.relu) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
-        }
-        if (row < p.M) {
-          const int64_t off = static_cast<int64_t>(row) * p.ldc + col0;
-          const bool full_chunk = (col0 + 32 <= p.N) && p.c_vec_ok;
-          if (p.c_dtype == static_cast<int>(DType::kF32)) {
-            float* dst = static_cast<float*>(p.C) + off;
-            if (full_chunk) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                reinterpret_cast<float4*>(dst)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = v[j];
-            }
-          } else {
-            uint32_t packed[16];
-            if (p.c_dtype == static_cast<int>(DType::kBF16)) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                packed[j] = *reinterpret_cast<const uint32_t*>(&h);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-                packed[j] = *reinterpret_cast<const uint32_t*>(&h);
-              }
-            }
-            uint16_t* dst = static_cast<uint16_t*>(p.C) + off;
-            if (full_chunk) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q)
-                reinterpret_cast<uint4*>(dst)[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j)
-                dst[j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xFFFFu));
-            }
-          }
-        }
+        epilogue_chunk(p, row, col0, &r[0], bs + c * 32);
+        if (two) epilogue_chunk(p, row, col0 + 32, &r[32], bs + c * 32 + 32);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
       if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
+      if (tle) {
+        const unsigned long long e2 = global_ns();
+        e_busy += e2 - e1;
+        if (e_tiles == 0) g_gemm_timeline[6] = e2;
+        g_gemm_timeline[7] = e2;
+        ++e_tiles;
+      }
     }
+    if (tle) { g_gemm_timeline[12] = e_wait; g_gemm_timeline[13] = e_busy; g_gemm_timeline[14] = e_tiles; }
   }
 
   // ---------------- teardown ----------------
@@ -365,6 +453,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (tl && threadIdx.x == 0) g_gemm_timeline[8] = global_ns();
 }
 
 // ------------------------------------------------------------------ host side
@@ -492,6 +581,21 @@ int gemm_tcgen05_status(bool clear) {
     cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
   }
   return v;
+}
+
+// Tuning aid: enable / disable the CTA-0 timeline and read its 16 slots (synchronises the device).
+int gemm_tcgen05_timeline(int enable, unsigned long long* out16) {
+  if (out16) {
+    if (cudaMemcpyFromSymbol(out16, g_gemm_timeline, sizeof(unsigned long long) * 16) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+  }
+  if (cudaMemcpyToSymbol(g_gemm_timeline_on, &enable, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return 0;
 }
 
 }  // namespace aicf::cuda

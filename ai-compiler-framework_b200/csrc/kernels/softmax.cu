@@ -1,11 +1,16 @@
 // Row softmax and fused softmax cross-entropy (loss rows + gradient + argmax) over the last axis.
 //
 // Single HBM pass: a block owns one row at a time and keeps it in registers (kPackets 16-byte
-// packets per thread), so the row is read once and the result written once. Row max / sum are
-// warp-shuffle reductions joined through shared memory in a fixed order, hence deterministic.
+// packets per thread), so the row is read once and the result written once. While a row is being
+// reduced, exponentiated and stored from registers, the block's NEXT row is already on its way into
+// shared memory as one bulk asynchronous copy (cp.async.bulk + mbarrier), so every SM always has a
+// row-sized read in flight and the load / reduce / store phases of a block overlap with each other.
+// Row max / sum are warp-shuffle reductions joined through shared memory in a fixed order, hence
+// deterministic.
 // Rows wider than 32768 elements, or rows that are not 16-byte aligned, take a three-read fallback
 // kernel.
 #include "common.cuh"
+#include "sm100_async.cuh"
 
 namespace aicf::cuda {
 
@@ -54,16 +59,57 @@ __device__ __forceinline__ ArgMax block_argmax(ArgMax a, float* sv, int* si) {
   return r;
 }
 
+// ------------------------------------------------------------------ row pipeline plumbing
+constexpr unsigned long long kRowWaitBudgetNs = 1000000000ull;  // a row copy that takes 1 s is lost
+__device__ int g_row_pipeline_status = 0;                       // non-zero: a bounded wait expired
+
+// Dynamic shared memory: [row buffer: row_bytes][mbarrier: 8 B]. Thread 0 drives the copies.
+struct RowPipe {
+  uint32_t buf, bar;
+  uint32_t phase;
+  __device__ __forceinline__ void init(uint8_t* smem, uint32_t row_bytes) {
+    buf = sm100::smem_addr(smem);
+    bar = buf + row_bytes;
+    phase = 0;
+    if (threadIdx.x == 0) {
+      sm100::mbar_init(bar, 1);
+      sm100::mbar_init_fence();
+    }
+    __syncthreads();
+  }
+  __device__ __forceinline__ void fetch(const void* row, uint32_t row_bytes) {  // thread 0 only
+    sm100::mbar_expect_tx(bar, row_bytes);
+    sm100::bulk_copy_g2s(buf, row, row_bytes, bar);
+  }
+  // Block-uniform: false when any thread's wait expired (the block then stops).
+  __device__ __forceinline__ bool arrived() {
+    const bool ok = sm100::mbar_wait_bounded(bar, phase, kRowWaitBudgetNs);
+    phase ^= 1u;
+    if (__syncthreads_or(ok ? 0 : 1)) {
+      if (threadIdx.x == 0) atomicExch(&g_row_pipeline_status, 1);
+      return false;
+    }
+    return true;
+  }
+};
+
 // ------------------------------------------------------------------ softmax, row in registers
 template <typename T, int kPackets>
 __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M,
                                                            int64_t N) {
   using PK = Pack16<T>;
   constexpr int kN = PK::kN;
+  extern __shared__ __align__(16) uint8_t row_smem[];
   __shared__ float red[kMaxWarps];
   const int64_t np = N / kN;  // N % kN == 0 on this path
-  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
-    const PK* xr = reinterpret_cast<const PK*>(x + row * N);
+  const uint32_t row_bytes = static_cast<uint32_t>(N * sizeof(T));
+  RowPipe pipe;
+  pipe.init(row_smem, row_bytes);
+  int64_t row = blockIdx.x;
+  if (row < M && threadIdx.x == 0) pipe.fetch(x + row * N, row_bytes);
+  const PK* srow = reinterpret_cast<const PK*>(row_smem);
+  for (; row < M; row += gridDim.x) {
+    if (!pipe.arrived()) break;
     PK* yr = reinterpret_cast<PK*>(y + row * N);
     float f[kPackets][kN];
     float mx = -INFINITY;
@@ -71,7 +117,7 @@ __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict_
     for (int q = 0; q < kPackets; ++q) {
       const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
       if (pi < np) {
-        const PK p = ld_stream(xr + pi);
+        const PK p = srow[pi];
 #pragma unroll
         for (int e = 0; e < kN; ++e) {
           f[q][e] = Cvt<T>::to_f(p.v[e]);
@@ -82,7 +128,13 @@ __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict_
         for (int e = 0; e < kN; ++e) f[q][e] = -INFINITY;
       }
     }
+    // block_reduce starts with a barrier: after it every thread has copied its part of the row out of
+    // shared memory, so thread 0 may let the next row overwrite the buffer.
     mx = block_reduce<true>(mx, red);
+    if (threadIdx.x == 0 && row + gridDim.x < M) {
+      sm100::fence_generic_to_async_smem();
+      pipe.fetch(x + (row + gridDim.x) * N, row_bytes);
+    }
     float sum = 0.0f;
 #pragma unroll
     for (int q = 0; q < kPackets; ++q)
@@ -143,24 +195,55 @@ RowCfg pick_row_cfg(int64_t n_packets, int max_packets) {
   return c;
 }
 
+// Dynamic shared memory of the pipelined kernels: the row plus its mbarrier.
+inline size_t row_pipe_smem(int64_t row_bytes) { return static_cast<size_t>(row_bytes) + 16; }
+constexpr size_t kMaxRowPipeSmem = 200 * 1024;
+
+// Resident blocks per SM given threads and shared memory per block (227 KiB usable, ~1 KiB reserved per block).
+inline int row_pipe_blocks_per_sm(int threads, size_t smem) {
+  int by_threads = 2048 / threads;
+  int by_smem = static_cast<int>((227 * 1024) / (smem + 1024));
+  int b = by_threads < by_smem ? by_threads : by_smem;
+  return b < 1 ? 1 : (b > 16 ? 16 : b);
+}
+
+template <typename K>
+bool allow_smem(K kernel, size_t smem) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) == cudaSuccess;
+}
+
 template <typename T>
 Status softmax_run(const T* x, T* y, int64_t M, int64_t N, cudaStream_t stream) {
   constexpr int kN = Pack16<T>::kN;
   constexpr int kMaxPk = sizeof(T) == 4 ? 8 : 4;
   const bool vec = (N % kN == 0) && aligned_to(x, 16) && aligned_to(y, 16);
-  const RowCfg c = vec ? pick_row_cfg(N / kN, kMaxPk) : RowCfg{};
+  const size_t smem = row_pipe_smem(N * static_cast<int64_t>(sizeof(T)));
+  const RowCfg c = (vec && smem <= kMaxRowPipeSmem) ? pick_row_cfg(N / kN, kMaxPk) : RowCfg{};
   cudaGetLastError();
   if (c.packets == 0) {
     softmax_multipass_kernel<T><<<streaming_grid(M, 1, 8), 256, 0, stream>>>(x, y, M, N);
     return launch_status();
   }
-  const int per_sm = 2048 / c.threads;
-  const int grid = streaming_grid(M, 1, per_sm < 1 ? 1 : per_sm);
+  const int grid = streaming_grid(M, 1, row_pipe_blocks_per_sm(c.threads, smem));
+  bool ok_attr = true;
   switch (c.packets) {
-    case 1: softmax_regs_kernel<T, 1><<<grid, c.threads, 0, stream>>>(x, y, M, N); break;
-    case 2: softmax_regs_kernel<T, 2><<<grid, c.threads, 0, stream>>>(x, y, M, N); break;
-    case 4: softmax_regs_kernel<T, 4><<<grid, c.threads, 0, stream>>>(x, y, M, N); break;
-    default: softmax_regs_kernel<T, kMaxPk><<<grid, c.threads, 0, stream>>>(x, y, M, N); break;
+    case 1:
+      if ((ok_attr = allow_smem(softmax_regs_kernel<T, 1>, smem))) softmax_regs_kernel<T, 1><<<grid, c.threads, smem, stream>>>(x, y, M, N);
+      break;
+    case 2:
+      if ((ok_attr = allow_smem(softmax_regs_kernel<T, 2>, smem))) softmax_regs_kernel<T, 2><<<grid, c.threads, smem, stream>>>(x, y, M, N);
+      break;
+    case 4:
+      if ((ok_attr = allow_smem(softmax_regs_kernel<T, 4>, smem))) softmax_regs_kernel<T, 4><<<grid, c.threads, smem, stream>>>(x, y, M, N);
+      break;
+    default:
+      if ((ok_attr = allow_smem(softmax_regs_kernel<T, kMaxPk>, smem)))
+        softmax_regs_kernel<T, kMaxPk><<<grid, c.threads, smem, stream>>>(x, y, M, N);
+      break;
+  }
+  if (!ok_attr) {
+    cudaGetLastError();
+    return Status::Internal;
   }
   return launch_status();
 }
@@ -212,38 +295,50 @@ __global__ void __launch_bounds__(1024)
                            float scale) {
   using PK = Pack16<T>;
   constexpr int kN = PK::kN;
+  extern __shared__ __align__(16) uint8_t row_smem[];
   __shared__ float red[kMaxWarps];
   __shared__ int redi[kMaxWarps];
-  __shared__ float z_label;
   const int64_t np = C / kN;
-  for (int64_t row = blockIdx.x; row < B; row += gridDim.x) {
-    const PK* zr = reinterpret_cast<const PK*>(z + row * C);
+  const uint32_t row_bytes = static_cast<uint32_t>(C * sizeof(T));
+  RowPipe pipe;
+  pipe.init(row_smem, row_bytes);
+  int64_t row = blockIdx.x;
+  if (row < B && threadIdx.x == 0) pipe.fetch(z + row * C, row_bytes);
+  const PK* srow = reinterpret_cast<const PK*>(row_smem);
+  for (; row < B; row += gridDim.x) {
+    if (!pipe.arrived()) break;
     PK* dr = reinterpret_cast<PK*>(dz + row * C);
     const int label = labels[row];
+    const bool label_ok = label >= 0 && label < C;
+    float z_label = 0.0f;  // only thread 0 needs it
+    if (threadIdx.x == 0 && label_ok) z_label = Cvt<T>::to_f(reinterpret_cast<const T*>(row_smem)[label]);
     float f[kPackets][kN];
     ArgMax am{-INFINITY, 0x7fffffff};
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
       const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
       if (pi < np) {
-        const PK p = ld_stream(zr + pi);
+        const PK p = srow[pi];
 #pragma unroll
         for (int e = 0; e < kN; ++e) {
           const float v = Cvt<T>::to_f(p.v[e]);
           f[q][e] = v;
-          const int col = static_cast<int>(pi) * kN + e;
           if (v > am.v) {  // columns are visited in increasing order per thread: strict > keeps the lowest
             am.v = v;
-            am.idx = col;
+            am.idx = static_cast<int>(pi) * kN + e;
           }
-          if (col == label) z_label = v;
         }
       } else {
 #pragma unroll
         for (int e = 0; e < kN; ++e) f[q][e] = -INFINITY;
       }
     }
+    // the first barrier inside block_argmax is passed only when every thread holds its part of the row
     am = block_argmax(am, red, redi);
+    if (threadIdx.x == 0 && row + gridDim.x < B) {
+      sm100::fence_generic_to_async_smem();
+      pipe.fetch(z + (row + gridDim.x) * C, row_bytes);
+    }
     const float mx = am.v;
     float sum = 0.0f;
 #pragma unroll
@@ -253,9 +348,8 @@ __global__ void __launch_bounds__(1024)
         f[q][e] = expf(f[q][e] - mx);
         sum += f[q][e];
       }
-    sum = block_reduce<false>(sum, red);  // its barriers also publish z_label
+    sum = block_reduce<false>(sum, red);
     const float k = scale / sum;
-    const bool label_ok = label >= 0 && label < C;
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
       const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
@@ -275,7 +369,6 @@ __global__ void __launch_bounds__(1024)
       loss_row[row] = label_ok ? (logf(sum) + mx - z_label) : 0.0f;
       if (argmax_out) argmax_out[row] = am.idx;
     }
-    __syncthreads();  // z_label is rewritten by the next row
   }
 }
 
@@ -352,19 +445,28 @@ Status softmax_ce_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, 
   constexpr int kN = Pack16<T>::kN;
   constexpr int kMaxPk = sizeof(T) == 4 ? 8 : 4;
   const bool vec = (C % kN == 0) && aligned_to(z, 16) && aligned_to(dz, 16);
-  const RowCfg c = vec ? pick_row_cfg(C / kN, kMaxPk) : RowCfg{};
+  const size_t smem = row_pipe_smem(C * static_cast<int64_t>(sizeof(T)));
+  const RowCfg c = (vec && smem <= kMaxRowPipeSmem) ? pick_row_cfg(C / kN, kMaxPk) : RowCfg{};
   cudaGetLastError();
   if (c.packets == 0) {
     softmax_ce_multipass_kernel<T><<<streaming_grid(B, 1, 8), 256, 0, stream>>>(z, lab, dz, loss, am, B, C, scale);
     return launch_status();
   }
-  const int per_sm = 2048 / c.threads;
-  const int grid = streaming_grid(B, 1, per_sm < 1 ? 1 : per_sm);
+  const int grid = streaming_grid(B, 1, row_pipe_blocks_per_sm(c.threads, smem));
+  bool ok_attr = true;
+#define AICF_CE_LAUNCH(PK)                                                                            \
+  if ((ok_attr = allow_smem(softmax_ce_regs_kernel<T, PK>, smem)))                                    \
+    softmax_ce_regs_kernel<T, PK><<<grid, c.threads, smem, stream>>>(z, lab, dz, loss, am, B, C, scale)
   switch (c.packets) {
-    case 1: softmax_ce_regs_kernel<T, 1><<<grid, c.threads, 0, stream>>>(z, lab, dz, loss, am, B, C, scale); break;
-    case 2: softmax_ce_regs_kernel<T, 2><<<grid, c.threads, 0, stream>>>(z, lab, dz, loss, am, B, C, scale); break;
-    case 4: softmax_ce_regs_kernel<T, 4><<<grid, c.threads, 0, stream>>>(z, lab, dz, loss, am, B, C, scale); break;
-    default: softmax_ce_regs_kernel<T, kMaxPk><<<grid, c.threads, 0, stream>>>(z, lab, dz, loss, am, B, C, scale); break;
+    case 1: AICF_CE_LAUNCH(1); break;
+    case 2: AICF_CE_LAUNCH(2); break;
+    case 4: AICF_CE_LAUNCH(4); break;
+    default: AICF_CE_LAUNCH(kMaxPk); break;
+  }
+#undef AICF_CE_LAUNCH
+  if (!ok_attr) {
+    cudaGetLastError();
+    return Status::Internal;
   }
   return launch_status();
 }
@@ -383,6 +485,20 @@ KernelVariant make(const char* name, LaunchFn l, SupportedFn s) {
 }
 
 }  // namespace
+
+// Reads (optionally clears) the status word of the row pipeline's bounded waits. Synchronises the device.
+int row_pipeline_status(bool clear) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_row_pipeline_status, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (clear && v != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_row_pipeline_status, &zero, sizeof(int));
+  }
+  return v;
+}
 
 KernelVariant make_softmax_lastdim_f32_variant() { return make("softmax_f32_sm100", softmax_launch<DType::kF32, float>, softmax_supported<DType::kF32>); }
 KernelVariant make_softmax_lastdim_bf16_variant() { return make("softmax_bf16_sm100", softmax_launch<DType::kBF16, __nv_bfloat16>, softmax_supported<DType::kBF16>); }

@@ -507,6 +507,14 @@ int aicf_b200_plan_replay(aicf_plan* p, int n) {
   return AICF_OK;
 }
 
+int aicf_b200_plan_replay_on(aicf_plan* p, int n, aicf_stream stream) {
+  if (!p || !p->exec) return fail(Status::InvalidArgument, "[exec] replay called before capture()");
+  cudaStream_t s = stream ? as_stream(stream) : p->stream;
+  for (int i = 0; i < n; ++i)
+    if (int rc = check_cuda(cudaGraphLaunch(p->exec, s), "cudaGraphLaunch")) return rc;
+  return AICF_OK;
+}
+
 int aicf_b200_plan_reset_graph(aicf_plan* p) {
   if (!p) return fail(Status::InvalidArgument, "plan_reset_graph: null plan");
   if (p->stream) cudaStreamSynchronize(p->stream);

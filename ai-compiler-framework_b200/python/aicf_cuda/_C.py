@@ -172,5 +172,10 @@ def gemm_status(clear: bool = False) -> int:
     return int(lib.aicf_b200_gemm_status(1 if clear else 0))
 
 
+def wait_status(clear: bool = False) -> int:
+    """0 unless a bounded device-side wait expired (GEMM pipeline or softmax row prefetch); synchronises."""
+    return int(lib.aicf_b200_wait_status(1 if clear else 0))
+
+
 def device_sync() -> None:
     check(lib.aicf_b200_device_sync(), "device_sync")

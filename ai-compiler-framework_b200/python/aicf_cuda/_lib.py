@@ -64,6 +64,8 @@ PROTOTYPES = {
     "aicf_b200_kernel_id": (_cp, [_i, _i]),
     "aicf_b200_num_op_kinds": (_i, []),
     "aicf_b200_gemm_status": (_i, [_i]),
+    "aicf_b200_wait_status": (_i, [_i]),
+    "aicf_b200_gemm_timeline": (_i, [_i, _P(C.c_uint64)]),
     "aicf_b200_colsum_f32_noalloc": (_i, [_vp, _vp, C.c_int64, C.c_int64, _u64]),
     "aicf_b200_trace_enable": (None, [_i]),
     "aicf_b200_trace_reset": (None, []),
@@ -112,6 +114,7 @@ PROTOTYPES = {
     "aicf_b200_plan_run": (_i, [_vp, _u64]),
     "aicf_b200_plan_capture": (_i, [_vp]),
     "aicf_b200_plan_replay": (_i, [_vp, _i]),
+    "aicf_b200_plan_replay_on": (_i, [_vp, _i, _u64]),
     "aicf_b200_plan_reset_graph": (_i, [_vp]),
     "aicf_b200_plan_stream": (_u64, [_vp]),
     "aicf_b200_plan_sync": (_i, [_vp]),

@@ -205,12 +205,13 @@ class Plan:
         check(lib.aicf_b200_plan_capture(self._h), "plan_capture")
         self._captured = True
 
-    def replay(self, n: int = 1) -> None:
+    def replay(self, n: int = 1, stream: int = 0) -> None:
+        """n launches of the captured graph into the plan's stream (or `stream`), without synchronising."""
         if n <= 0:
             return
         if not self._captured:
             raise RuntimeError("[exec] replay called before capture()")
-        check(lib.aicf_b200_plan_replay(self._h, int(n)), "plan_replay")
+        check(lib.aicf_b200_plan_replay_on(self._h, int(n), int(stream)), "plan_replay")
 
     def reset_graph(self) -> None:
         check(lib.aicf_b200_plan_reset_graph(self._h), "plan_reset_graph")

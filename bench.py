@@ -197,9 +197,12 @@ def mlp_flops_per_sample(dims):
 
 
 def build_mlp(aicf, dims, batch, global_batch, dp):
-    from aicf_cuda import Plan, build_mlp_train_step
+    """Two plans over one set of parameters (double-buffered inputs for the end-to-end loop); the
+    device-resident timing replays the first one."""
+    from aicf_cuda import DoubleBufferedStep, build_mlp_train_step
     vals, low = build_mlp_train_step(batch, dims, compute_dtype="bf16", global_batch=global_batch, data_parallel=dp, **ADAM)
-    return Plan("dp_mlp", vals, low), vals, low
+    dbl = DoubleBufferedStep("dp_mlp", vals, low)
+    return dbl, dbl.a, vals, low
 
 
 def init_mlp_params(aicf, plan, dims, seed):
@@ -268,7 +271,7 @@ def run_mlp(args, dist: Dist):
         uid = dist.bcast_bytes(bytes(idbuf) if rank == 0 else None)
         aicf_cuda._lib.check(lib.aicf_b200_dp_init(rank, world, (C.c_uint8 * 128).from_buffer_copy(uid)), "dp_init")
 
-    plan, vals, low = build_mlp(aicf_cuda, dims, batch, gbatch, dp=world > 1)
+    dbl, plan, vals, low = build_mlp(aicf_cuda, dims, batch, gbatch, dp=world > 1)
     init_mlp_params(aicf_cuda, plan, dims, seed=4)
 
     # host inputs in pinned memory: rank r owns rows [r*batch, (r+1)*batch) of the global batch
@@ -276,14 +279,13 @@ def run_mlp(args, dist: Dist):
     fill_normal(x_host, seed=4000 + rank)
     y_host, _ = pinned_array(lib, (batch,), np.int32)
     y_host[:] = np.random.default_rng(5000 + rank).integers(0, dims[-1], size=batch, dtype=np.int32)
-    loss_host, _ = pinned_array(lib, (1,), np.float32)
     x_dev, y_dev, loss_dev = plan.tensor("x"), plan.tensor("labels"), plan.tensor("loss")
     stream = plan.stream
     lib.aicf_b200_memcpy_h2d(x_dev.ptr, x_host.ctypes.data, x_host.nbytes, stream)
     lib.aicf_b200_memcpy_h2d(y_dev.ptr, y_host.ctypes.data, y_host.nbytes, stream)
     plan.sync()
 
-    plan.capture()
+    dbl.capture()
     ev = Events(lib)
     # ---- device-resident timing: K graph replays --------------------------------------------------
     plan.replay(args.warmup)
@@ -299,22 +301,26 @@ def run_mlp(args, dist: Dist):
     loss_after = float(loss_dev.numpy()[0])
 
     # ---- end to end: host buffers in, loss out, every step ----------------------------------------------
-    def e2e_step():
-        lib.aicf_b200_memcpy_h2d(x_dev.ptr, x_host.ctypes.data, x_host.nbytes, stream)
-        lib.aicf_b200_memcpy_h2d(y_dev.ptr, y_host.ctypes.data, y_host.nbytes, stream)
-        plan.replay(1)
-        lib.aicf_b200_memcpy_d2h(loss_host.ctypes.data, loss_dev.ptr, 4, stream)
-        lib.aicf_b200_stream_sync(stream)  # the caller reads the loss every step
+    # DoubleBufferedStep.submit() = H2D of the step's pinned inputs on a copy stream, one graph replay, D2H of the
+    # loss. The loss of step t is read on the host while step t+1 is in flight (one step of pipelining).
+    def e2e_run(n):
+        prev, last_loss = None, None
+        for _ in range(n):
+            slot = dbl.submit([x_host, y_host])
+            if prev is not None:
+                last_loss = float(dbl.result(prev)[0])
+            prev = slot
+        return float(dbl.result(prev)[0])
 
-    for _ in range(max(1, min(args.warmup, 2))):
-        e2e_step()
+    e2e_run(max(2, min(args.warmup, 3)))
+    dbl.sync()
     dist.barrier()
     e2e_steps = max(2, min(args.steps, 10))
     t0 = time.perf_counter()
     ev.start(stream)
-    for _ in range(e2e_steps):
-        e2e_step()
+    e2e_run(e2e_steps)
     e2e_ms = ev.stop_ms(stream)
+    dbl.sync()
     e2e_ms = dist.max_float(max(e2e_ms, (time.perf_counter() - t0) * 1e3))
     dist.barrier()
 
@@ -329,7 +335,7 @@ def run_mlp(args, dist: Dist):
     gemm_flops = mlp_flops_per_sample(dims) * batch
     peaks = measured_peaks()
     achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
-    status = aicf_cuda._C.gemm_status()
+    status = aicf_cuda._C.wait_status()
 
     out = None
     if rank == 0:
@@ -344,7 +350,8 @@ def run_mlp(args, dist: Dist):
             "clocks": clocks.summary(),
             "e2e": {"value": gbatch / (e2e_ms / e2e_steps * 1e-3), "unit": "samples/s",
                     "h2d_bytes_per_step": int(x_host.nbytes + y_host.nbytes), "d2h_bytes_per_step": 4, "steps": e2e_steps,
-                    "note": "pinned host X (fp32) and labels copied in, graph replay, loss copied out, every step"},
+                    "note": "every step: pinned host X (fp32) + labels copied in on a copy stream (double-buffered, overlaps the "
+                            "previous replay), one graph replay, loss copied out and read by the host"},
             "gpu_launches": int(plan.graph_kernel_nodes) * args.steps,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None,
@@ -358,7 +365,7 @@ def run_mlp(args, dist: Dist):
             sec = numpy_mlp_step_time(dims, sample, gbatch, steps=1)
             out["cpu_baseline"] = {"value": sample / sec, "unit": "samples/s", "cores": blas_threads(), "kind": "port",
                                    "sample": f"one NumPy fp32 train step of the same lowered graph at batch {sample} (full-size Adam)"}
-    plan.close()
+    dbl.close()
     return out
 
 
@@ -406,19 +413,31 @@ def run_kernel_workload(args):
         fill_normal(h, seed, scale)
         return Tensor.from_numpy(h, dtype)
 
-    def time_launch(fn, flush=None):
+    def time_launch(fn):
+        """Times `reps` back-to-back launches captured in one CUDA graph (so that host launch latency does not
+        pollute short kernels); reps is chosen so a timed region lasts about 2 ms. Returns ms per launch."""
         for _ in range(max(3, args.warmup)):
-            fn()
+            fn(0)
+        _C.device_sync()
+        ev.start(0)
+        fn(0)
+        one = max(ev.stop_ms(0), 1e-3)
+        reps = int(min(200, max(1, round(2.0 / one))))
+        s = _C.graph_begin()
+        for _ in range(reps):
+            fn(s)
+        _C.graph_end()
+        for _ in range(3):
+            _C.graph_launch()
         _C.device_sync()
         times = []
         with ClockSampler(0) as clocks:
             for _ in range(args.steps):
-                if flush is not None:
-                    flush()
-                ev.start(stream)
-                fn()
-                times.append(ev.stop_ms(stream))
-        return times, clocks.summary()
+                ev.start(s)
+                _C.graph_launch()
+                times.append(ev.stop_ms(s) / reps)
+        _C.graph_reset()
+        return times, clocks.summary(), reps
 
     cfg, launches_per_step = {}, 1
     if w in ("gemm", "gemm_f32"):
@@ -430,7 +449,7 @@ def run_kernel_workload(args):
         Cm = Tensor.empty((n, n), dt)
         kid = "gemm_bias_relu_bf16_tcgen05_out_bf16_v0" if w == "gemm" else "gemm_bias_relu_f32_naive_v0"
         pay = struct.pack("<iii", 0, 1 if args.transb else 0, 1)
-        fn = lambda: _C.launch_by_id(kid, OpKind.GemmEpilogue, [A, B, bias], [Cm], 0x4750454C, pay, stream)
+        fn = lambda st: _C.launch_by_id(kid, OpKind.GemmEpilogue, [A, B, bias], [Cm], 0x4750454C, pay, st)
         work, unit, bound = 2.0 * n ** 3, "TFLOP/s", "tensor"
         peak = peaks["bf16_tflops"] if w == "gemm" else None
         metric = f"GEMM+bias+ReLU {dt} TFLOP/s"
@@ -442,7 +461,7 @@ def run_kernel_workload(args):
         X = dev_normal((M, N), dt, 3.0, 2)
         Y = Tensor.empty((M, N), dt)
         kid = f"softmax_lastdim_{dt}_v0"
-        fn = lambda: _C.launch_by_id(kid, OpKind.Softmax, [X], [Y], 0, b"", stream)
+        fn = lambda st: _C.launch_by_id(kid, OpKind.Softmax, [X], [Y], 0, b"", st)
         work, unit, bound, peak = 2.0 * M * N * X.nbytes / X.numel, "GB/s", "hbm", peaks["hbm_gbs"]
         metric = f"row softmax {dt} HBM GB/s"
         cfg = {"workload": f"softmax_{dt}", "rows": M, "cols": N, "l2": "read+write bytes exceed L2"}
@@ -454,7 +473,7 @@ def run_kernel_workload(args):
         kid = f"reduce_{args.reduce_kind}_lastaxis_{dt}_v0"
         kind = {"sum": OpKind.ReduceSum, "max": OpKind.ReduceMax, "mean": OpKind.ReduceMean}[args.reduce_kind]
         sch, pay = (0x5253554D, struct.pack("<q", -1)) if args.reduce_kind == "sum" else (0, b"")
-        fn = lambda: _C.launch_by_id(kid, kind, [X], [O], sch, pay, stream)
+        fn = lambda st: _C.launch_by_id(kid, kind, [X], [O], sch, pay, st)
         work, unit, bound, peak = float(X.nbytes + 4 * M), "GB/s", "hbm", peaks["hbm_gbs"]
         metric = f"last-axis {args.reduce_kind} {dt} HBM GB/s"
         cfg = {"workload": f"reduce_{args.reduce_kind}_{dt}", "rows": M, "cols": N, "l2": "input exceeds L2"}
@@ -463,7 +482,7 @@ def run_kernel_workload(args):
         Z = dev_normal((B, Cn), "f32", 2.0, 3)
         L = Tensor.from_numpy(rng.integers(0, Cn, B, dtype=np.int32))
         D, Lo, Am = Tensor.empty((B, Cn), "f32"), Tensor.empty((B,), "f32"), Tensor.empty((B,), "i32")
-        fn = lambda: _C.launch_by_id("softmax_ce_f32_i32_v0", OpKind.SoftmaxCE, [Z, L], [D, Lo, Am], 0, b"", stream)
+        fn = lambda st: _C.launch_by_id("softmax_ce_f32_i32_v0", OpKind.SoftmaxCE, [Z, L], [D, Lo, Am], 0, b"", st)
         work, unit, bound, peak = 2.0 * Z.nbytes + 12.0 * B, "GB/s", "hbm", peaks["hbm_gbs"]
         metric = "softmax cross-entropy loss+grad f32 HBM GB/s"
         cfg = {"workload": "softmax_ce_f32", "rows": B, "classes": Cn, "l2": "read+write bytes exceed L2"}
@@ -474,8 +493,8 @@ def run_kernel_workload(args):
         step = Tensor.from_numpy(np.array([1], np.int32))
         pay = struct.pack("<fffffI", 3e-4, 0.9, 0.999, 1e-8, 0.01, 0)
 
-        def fn():
-            _C.launch_by_id("adam_step_f32_fused_v1", OpKind.AdamStep, [P, G, M_, V_, step], [P, M_, V_], 0x4D414441, pay, stream)
+        def fn(st):
+            _C.launch_by_id("adam_step_f32_fused_v1", OpKind.AdamStep, [P, G, M_, V_, step], [P, M_, V_], 0x4D414441, pay, st)
         work, unit, bound, peak = 28.0 * n, "GB/s", "hbm", peaks["hbm_gbs"]
         metric = "fused Adam f32 HBM GB/s"
         cfg = {"workload": "adam_f32_wd", "elements": n, "l2": "7 streams of 1 GiB exceed L2"}
@@ -483,7 +502,9 @@ def run_kernel_workload(args):
         raise SystemExit(f"unknown workload {w}")
 
     _C.trace_enable(False)
-    times, clocks = time_launch(fn)
+    times, clocks, reps = time_launch(fn)
+    launches_per_step = reps
+    cfg["launches_per_timed_graph"] = reps
     ms = statistics.mean(times)
     achieved = work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
     out = {"metric": metric, "value": achieved, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
@@ -492,7 +513,7 @@ def run_kernel_workload(args):
            "gpu_launches": args.steps * launches_per_step,
            "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
                         "frac": (achieved / peak) if peak else None, "traffic": None, "peak_source": peaks["source"]},
-           "gemm_status": _C.gemm_status()}
+           "gemm_status": _C.wait_status()}
     return out
 
 

@@ -94,6 +94,15 @@ int aicf_b200_num_op_kinds(void);
 /* Status word of the tcgen05 GEMM's bounded waits: 0 = no wait ever expired. Synchronises the
  * device. No counterpart in the reference (its kernels have no device-side waits). */
 int aicf_b200_gemm_status(int clear);
+/* All device-side bounded waits of this library in one word: low 16 bits = the GEMM code above, bit 16 =
+ * a row copy of the softmax / softmax-CE prefetch pipeline did not arrive within its budget. 0 = healthy.
+ * Synchronises the device. No counterpart in the reference. */
+int aicf_b200_wait_status(int clear);
+/* Tuning aid of the tcgen05 GEMM: reads the 16-slot timeline that CTA 0 of the last GEMM wrote (globaltimer ns:
+ * start, set-up, first TMA, first stage landed, first tile issued, first accumulator ready, first / last tile stored,
+ * end, then wait and busy totals per role and the tile count), then switches recording on or off. out16 may be NULL.
+ * Synchronises the device. No counterpart in the reference. */
+int aicf_b200_gemm_timeline(int enable, uint64_t* out16);
 
 /* Column sum [rows, cols] -> [cols] (fp32, row-major, contiguous) for callers that must not allocate
  * device memory: a host that was given a fixed memory budget up front, or code that runs where the
@@ -201,6 +210,9 @@ const char* aicf_b200_plan_op_kernel_id(aicf_plan* plan, int op_index);
 int aicf_b200_plan_run(aicf_plan* plan, aicf_stream stream); /* eager: one launch per op */
 int aicf_b200_plan_capture(aicf_plan* plan);                 /* graph on the plan's own stream */
 int aicf_b200_plan_replay(aicf_plan* plan, int n);           /* n graph launches, no sync */
+/* Same, launched into `stream` instead of the plan's own stream (plans that share parameter buffers are
+ * serialised by replaying them into one stream). */
+int aicf_b200_plan_replay_on(aicf_plan* plan, int n, aicf_stream stream);
 int aicf_b200_plan_reset_graph(aicf_plan* plan);
 aicf_stream aicf_b200_plan_stream(aicf_plan* plan);
 int aicf_b200_plan_sync(aicf_plan* plan);

@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 import oracle
-from aicf_cuda import Tensor, f32_to_bf16_bits
+from aicf_cuda import _C, Tensor, f32_to_bf16_bits
 from aicf_cuda._C import OpKind
 from util import assert_close_f32, by_id, dev, host, op_call
 
@@ -274,6 +274,7 @@ def test_softmax_rows(gpu, M, N, dt):
     x = _round(oracle.softmax_inputs(M, N, seed=2), dt)
     Y = Tensor.empty((M, N), dt)
     by_id(f"softmax_lastdim_{dt}_v0", OpKind.Softmax, [dev(x, dt)], [Y])
+    assert _C.wait_status() == 0, "a bounded wait of the row prefetch pipeline expired"
     want = oracle.softmax(x)
     got = host(Y)
     if dt == "f32":
@@ -292,6 +293,7 @@ def test_softmax_cross_entropy(gpu, B, Cn, dt):
     z = _round(z, dt)
     D, L, A = Tensor.empty((B, Cn), dt), Tensor.empty((B,)), Tensor.empty((B,), "i32")
     by_id(f"softmax_ce_{dt}_i32_v0", OpKind.SoftmaxCE, [dev(z, dt), dev(y)], [D, L, A])
+    assert _C.wait_status() == 0, "a bounded wait of the row prefetch pipeline expired"
     wd, wl, wa = oracle.softmax_ce(z, y)
     assert np.array_equal(A.numpy(), wa), "argmax must be bit-exact"
     assert_close_f32(host(L), wl, rtol=1e-5, atol=1e-6, what="loss rows")

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 import oracle
-from aicf_cuda import _C, Plan, Tensor, build_mlp_train_step, f32_to_bf16_bits
+from aicf_cuda import _C, DoubleBufferedStep, Plan, Tensor, build_mlp_train_step, f32_to_bf16_bits
 from aicf_cuda._C import OpKind
 
 pytestmark = pytest.mark.gpu
@@ -112,6 +112,50 @@ def test_mixed_precision_mlp_tracks_the_oracle(gpu, dtype):
     assert np.array_equal(lp, oracle.cast(plan.tensor("2.W").numpy(), dtype)), "working copy == rounded master weight"
     assert _C.gemm_status() == 0
     plan.close()
+
+
+def test_double_buffered_pipeline_equals_sequential_steps(gpu):
+    """Two plans over shared parameters, inputs copied in on a second stream: same bits as one plan fed by hand."""
+    dims, batch = [128, 256, 32], 256
+    vals, low = build_mlp_train_step(batch, dims, compute_dtype="bf16")
+    params = oracle.mlp_params(dims, seed=1)
+    batches = [oracle.mlp_batch(batch, dims[0], dims[-1], seed=s) for s in (10, 11)]
+
+    def load(plan):
+        for name, w in params.items():
+            plan.tensor(name).copy_from_host(w)
+            if name.endswith(".W"):
+                plan.tensor(name + ".lp").copy_from_host(f32_to_bf16_bits(w))
+
+    seq = Plan("seq", vals, low)
+    load(seq)
+    seq.capture()
+    losses_seq = []
+    for t in range(6):
+        x, y = batches[t % 2]
+        seq.tensor("x").copy_from_host(x)
+        seq.tensor("labels").copy_from_host(y)
+        seq.replay(1)
+        seq.sync()
+        losses_seq.append(float(seq.tensor("loss").numpy()[0]))
+
+    dbl = DoubleBufferedStep("dbl", vals, low)
+    load(dbl.a)
+    dbl.capture()
+    losses, prev = [], None
+    for t in range(6):
+        slot = dbl.submit(list(batches[t % 2]))
+        if prev is not None:
+            losses.append(float(dbl.result(prev)[0]))
+        prev = slot
+    losses.append(float(dbl.result(prev)[0]))
+    dbl.sync()
+    assert losses == losses_seq
+    for name in ("0.W", "2.W", "2.b", "opt.m.0.W"):
+        assert np.array_equal(dbl.a.tensor(name).numpy(), seq.tensor(name).numpy()), name
+    assert dbl.b.tensor("0.W").ptr == dbl.a.tensor("0.W").ptr and dbl.b.tensor("x").ptr != dbl.a.tensor("x").ptr
+    dbl.close()
+    seq.close()
 
 
 def test_arena_reuses_dead_buffers(gpu):

@@ -1,4 +1,4 @@
-// Kernel variants of OpKind::Gemm and OpKind::GemmEpilogue.
+// Kernel variants of OpKind::Gemm, OpKind::GemmEpilogue and OpKind::GemmReluBwd.
 //
 // Each variant validates its contract and then routes to one of two sm_100a kernels:
 //   gemm_tcgen05_run  16-bit operands whose rows are 16-byte aligned (TMA + tcgen05/TMEM)
@@ -11,7 +11,7 @@ namespace aicf::cuda {
 
 namespace {
 
-enum class BiasRule { None, SameAsInput, F32OrInput };
+enum class BiasRule { None, SameAsInput, F32OrInput, ReluBwdMask };  // the last: third input is the activation Y
 
 struct GemmContract {
   DType in, out;
@@ -23,8 +23,24 @@ bool is_packed_rowmajor(const TensorDesc& t) { return t.rank() == 2 && t.stride[
 
 bool check(const GemmContract& c, const TensorDesc* in, int ni, const TensorDesc* out, int no, const void* attr,
            GemmProblem* prob) {
-  const bool with_bias = c.bias != BiasRule::None;
+  const bool with_mask = c.bias == BiasRule::ReluBwdMask;
+  const bool with_bias = c.bias != BiasRule::None && !with_mask;
   bool ta, tb, relu = false;
+  if (with_mask) {
+    // inputs [dY, W, Y] -> dX: shape rules of gemm on the first two, Y must look exactly like the output
+    if (!in || ni != 3) return false;
+    read_gemm_attr(attr, &ta, &tb);
+    GemmProblem pm;
+    if (!build_problem(in, 2, out, no, false, ta, tb, false, &pm)) return false;
+    if (in[0].dtype != c.in || in[1].dtype != c.in || out[0].dtype != c.out) return false;
+    const TensorDesc& Y = in[2];
+    if (Y.dtype != c.out || Y.rank() != 2 || Y.shape[0] != pm.M || Y.shape[1] != pm.N || Y.stride[1] != 1 || Y.stride[0] < pm.N)
+      return false;
+    pm.mask = Y.data;
+    pm.mask_ld = Y.stride[0];
+    if (prob) *prob = pm;
+    return true;
+  }
   if (with_bias) {
     read_gemm_epilogue_attr(attr, &ta, &tb, &relu);
   } else {
@@ -66,6 +82,9 @@ AICF_GEMM_CONTRACT(11, DType::kF16, DType::kF16, BiasRule::SameAsInput, true)
 AICF_GEMM_CONTRACT(12, DType::kBF16, DType::kBF16, BiasRule::F32OrInput, false)
 AICF_GEMM_CONTRACT(13, DType::kBF16, DType::kF32, BiasRule::F32OrInput, false)
 AICF_GEMM_CONTRACT(14, DType::kF16, DType::kF16, BiasRule::F32OrInput, false)
+AICF_GEMM_CONTRACT(20, DType::kBF16, DType::kBF16, BiasRule::ReluBwdMask, false)
+AICF_GEMM_CONTRACT(21, DType::kF16, DType::kF16, BiasRule::ReluBwdMask, false)
+AICF_GEMM_CONTRACT(22, DType::kF32, DType::kF32, BiasRule::ReluBwdMask, false)
 
 template <int kId>
 bool supported(const TensorDesc* in, int ni, const TensorDesc* out, int no, const void* attr) {
@@ -103,5 +122,9 @@ KernelVariant make_gemm_bias_relu_f16_tc_wmma_out_f16_variant() { return variant
 KernelVariant make_gemm_bias_relu_bf16_tcgen05_out_bf16_variant() { return variant<12>("gemm_bias_relu_bf16_tcgen05_out_bf16"); }
 KernelVariant make_gemm_bias_relu_bf16_tcgen05_out_f32_variant() { return variant<13>("gemm_bias_relu_bf16_tcgen05_out_f32"); }
 KernelVariant make_gemm_bias_relu_f16_tcgen05_out_f16_variant() { return variant<14>("gemm_bias_relu_f16_tcgen05_out_f16"); }
+
+KernelVariant make_gemm_relu_bwd_bf16_variant() { return variant<20>("gemm_relu_bwd_bf16_tcgen05"); }
+KernelVariant make_gemm_relu_bwd_f16_variant() { return variant<21>("gemm_relu_bwd_f16_tcgen05"); }
+KernelVariant make_gemm_relu_bwd_f32_variant() { return variant<22>("gemm_relu_bwd_f32_simt_sm100"); }
 
 }  // namespace aicf::cuda

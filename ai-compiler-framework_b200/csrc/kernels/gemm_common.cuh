@@ -27,6 +27,9 @@ struct GemmProblem {
   int64_t bias_stride = 1;
   DType bias_dtype = DType::kUnknown;
   bool relu = false;
+  // optional ReLU-backward mask: C[m,n] is zeroed where mask[m,n] <= 0 (same dtype as C, unit column stride)
+  const void* mask = nullptr;
+  int64_t mask_ld = 0;
   int64_t M = 0, N = 0, K = 0;
 };
 

@@ -33,8 +33,9 @@ __device__ __forceinline__ void store_elem(void* base, int64_t idx, DType dt, fl
 }
 
 struct SimtArgs {
-  const void *A, *B, *bias;
+  const void *A, *B, *bias, *mask;
   void* C;
+  int64_t mask_ld;
   int64_t Ars, Acs, Brs, Bcs, Crs, Ccs, bias_stride;
   int M, N, K;
   DType dtA, dtB, dtC, dtBias;
@@ -124,6 +125,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(SimtArgs g) {
       float v = acc[i][j];
       if (g.bias) v += load_elem(g.bias, n * g.bias_stride, g.dtBias);
       if (g.relu) v = v > 0.0f ? v : 0.0f;
+      if (g.mask && !(load_elem(g.mask, m * g.mask_ld + n, g.dtC) > 0.0f)) v = 0.0f;
       store_elem(g.C, m * g.Crs + n * g.Ccs, g.dtC, v);
     }
   }
@@ -138,6 +140,8 @@ Status gemm_simt_run(const GemmProblem& p, cudaStream_t stream) {
   g.A = p.A.data; g.B = p.B.data; g.C = const_cast<void*>(p.C.data); g.bias = p.bias;
   g.Ars = p.A.rs; g.Acs = p.A.cs; g.Brs = p.B.rs; g.Bcs = p.B.cs; g.Crs = p.C.rs; g.Ccs = p.C.cs;
   g.bias_stride = p.bias_stride;
+  g.mask = p.mask;
+  g.mask_ld = p.mask_ld;
   g.M = static_cast<int>(p.M); g.N = static_cast<int>(p.N); g.K = static_cast<int>(p.K);
   g.dtA = p.A.dtype; g.dtB = p.B.dtype; g.dtC = p.C.dtype; g.dtBias = p.bias_dtype;
   g.relu = p.relu ? 1 : 0;

@@ -19,6 +19,8 @@
 // kernel returns normally. The host reads the word through gemm_tcgen05_status().
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "gemm_common.cuh"
 
 namespace aicf::cuda {
@@ -56,6 +58,9 @@ __device__ unsigned long long g_gemm_timeline[16];
 struct GemmParams {
   void* C;
   const void* bias;
+  const void* mask;     // optional ReLU-backward mask, dtype of C, row pitch mask_ld elements
+  int64_t mask_ld;
+  int mask_vec_ok;      // mask rows allow 16-byte loads
   int64_t ldc;          // elements
   int64_t bias_stride;  // elements
   int M, N, K;
@@ -214,6 +219,55 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int row, int
   if (row >= p.M) return;
   const int64_t off = static_cast<int64_t>(row) * p.ldc + col0;
   const bool full_chunk = (col0 + 32 <= p.N) && p.c_vec_ok;
+  if (p.mask) {  // dX = (Y > 0) ? acc : 0, Y read in C's dtype
+    const int64_t moff = static_cast<int64_t>(row) * p.mask_ld + col0;
+    const bool full_mask = (col0 + 32 <= p.N) && p.mask_vec_ok;
+    if (p.c_dtype == static_cast<int>(DType::kF32)) {
+      const float* ms = static_cast<const float*>(p.mask) + moff;
+      if (full_mask) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 y = __ldcs(reinterpret_cast<const float4*>(ms) + q);
+          if (!(y.x > 0.0f)) v[4 * q] = 0.0f;
+          if (!(y.y > 0.0f)) v[4 * q + 1] = 0.0f;
+          if (!(y.z > 0.0f)) v[4 * q + 2] = 0.0f;
+          if (!(y.w > 0.0f)) v[4 * q + 3] = 0.0f;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N && !(ms[j] > 0.0f)) v[j] = 0.0f;
+      }
+    } else {
+      // "y > 0" on the raw 16-bit pattern: sign clear, magnitude non-zero and not above infinity (NaN fails, as it
+      // does in the float comparison). bf16 and f16 differ only in the bit pattern of infinity.
+      const uint32_t inf_bits = p.c_dtype == static_cast<int>(DType::kBF16) ? 0x7F80u : 0x7C00u;
+      auto not_positive = [inf_bits](uint32_t y) {
+        const uint32_t mag = y & 0x7FFFu;
+        return (y & 0x8000u) != 0u || mag == 0u || mag > inf_bits;
+      };
+      const uint16_t* ms = static_cast<const uint16_t*>(p.mask) + moff;
+      if (full_mask) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 y = __ldcs(reinterpret_cast<const uint4*>(ms) + q);
+          const uint32_t w[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t lo = w[e] & 0xFFFFu, hi = w[e] >> 16;
+            if (not_positive(lo)) v[8 * q + 2 * e] = 0.0f;
+            if (not_positive(hi)) v[8 * q + 2 * e + 1] = 0.0f;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N) {
+            if (not_positive(ms[j])) v[j] = 0.0f;
+          }
+      }
+    }
+  }
   if (p.c_dtype == static_cast<int>(DType::kF32)) {
     float* dst = static_cast<float*>(p.C) + off;
     if (full_chunk) {
@@ -456,6 +510,290 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (tl && threadIdx.x == 0) g_gemm_timeline[8] = global_ns();
 }
 
+// ================================================================== paired-CTA variant (cta_group::2)
+// Two CTAs of a cluster work on one 256x256 tile: CTA r holds rows [128r, 128r+128) of A and columns
+// [128r, 128r+128) of B in its shared memory, one tcgen05.mma.cta_group::2 issued by the leader (rank 0) reads
+// both CTAs' operands and writes 128 accumulator lanes x 256 columns in each CTA's tensor memory. Per CTA a
+// k-step moves 32 KiB instead of 48 KiB, so the same shared memory holds a 6-stage ring: less L2->SM traffic
+// and more latency cover. Loads carry no multicast: each CTA issues its own cp.async.bulk.tensor (cta_group::2
+// form, whose completion may signal the leader's mbarrier).
+constexpr int k2Stages = 6;
+constexpr int k2HalfN = kTileN / 2;                       // B columns held per CTA
+constexpr int k2AStageBytes = kTileM * kTileK * 2;        // 16 KiB
+constexpr int k2BStageBytes = k2HalfN * kTileK * 2;       // 16 KiB
+constexpr int k2StageBytes = k2AStageBytes + k2BStageBytes;
+constexpr size_t k2SmemBytes = 1024 + size_t(k2Stages) * k2StageBytes + 256 + 4 * kTileN * sizeof(float);
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_count_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `local_addr` (a shared::cta address of this CTA's window) in CTA `rank`
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar_cluster)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives (once the MMAs issued so far have completed) on the barrier at this offset in both CTAs of the pair
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const uint16_t both = 0x3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(both)
+               : "memory");
+}
+
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m2, int tiles_n, int* tm, int* tn) {
+  constexpr int kGroup = kGroupM / 2;  // 8 pair-rows = 16 row tiles of 128
+  const int per_group = kGroup * tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * kGroup;
+  const int rows = min(kGroup, tiles_m2 - first_m);
+  const int in_group = tile - group * per_group;
+  *tm = first_m + in_group % rows;
+  *tn = in_group / rows;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                             const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const uint32_t bars = base + k2Stages * k2StageBytes;
+  // barrier map (8 B each): full[0..5], empty[0..5], acc_full[0..1], acc_empty[0..1]
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * k2Stages, bar_acc_full = bars + 16 * k2Stages,
+                 bar_acc_empty = bars + 16 * k2Stages + 8 * kAccBufs;
+  uint8_t* misc = base_ptr + k2Stages * k2StageBytes + 16 * k2Stages + 16 * kAccBufs;
+  volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(misc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 4);
+  float* bias_smem = reinterpret_cast<float*>(base_ptr + k2Stages * k2StageBytes + 256);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int cluster = static_cast<int>(cluster_id_x()), num_clusters = static_cast<int>(cluster_count_x());
+  const int tiles_m2 = (p.M + 2 * kTileM - 1) / (2 * kTileM), tiles_n = (p.N + kTileN - 1) / kTileN;
+  const int num_tiles = tiles_m2 * tiles_n;
+  const int k_blocks = (p.K + kTileK - 1) / kTileK;
+
+  const bool tl = g_gemm_timeline_on != 0 && blockIdx.x == 0;
+  if (tl && threadIdx.x == 0) g_gemm_timeline[0] = global_ns();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < k2Stages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);   // the leader's arrive.expect_tx; bytes of both CTAs complete it
+      mbar_init(bar_empty + 8 * s, 1);  // one multicast commit from the leader's MMA thread
+    }
+    for (int b = 0; b < kAccBufs; ++b) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_empty + 8 * b, 8);  // four epilogue warps in each of the two CTAs
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), kTmemCols);
+  tc_fence_before();
+  cluster_sync_all();  // barriers of both CTAs are initialised before anybody signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  if (tl && threadIdx.x == 0) g_gemm_timeline[1] = global_ns();
+
+  if (warp == 0) {
+    // ---------------- TMA producer (each CTA loads its own halves; completion lands on the leader's barrier)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      unsigned long long waited = 0;
+      bool first = true;
+      for (int tile = cluster; tile < num_tiles && alive; tile += num_clusters) {
+        int tm, tn;
+        pair_tile_coords(tile, tiles_m2, tiles_n, &tm, &tn);
+        const int m0 = tm * 2 * kTileM + static_cast<int>(rank) * kTileM;
+        const int nb0 = tn * kTileN + static_cast<int>(rank) * k2HalfN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          const unsigned long long w0 = tl ? global_ns() : 0;
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1)) { alive = false; break; }
+          if (tl) {
+            waited += global_ns() - w0;
+            if (first) { g_gemm_timeline[2] = global_ns(); first = false; }
+          }
+          const uint32_t full_leader = map_to_cta(bar_full + 8 * stage, 0);
+          const uint32_t sa = base + stage * k2StageBytes, sb = sa + k2AStageBytes;
+          const int k0 = kb * kTileK;
+          if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * k2StageBytes);
+          if (p.a_mn_major) {
+            tma_load_2d_pair(sa, &tmap_a, m0, k0, full_leader);
+            tma_load_2d_pair(sa + kChunkBytes, &tmap_a, m0 + 64, k0, full_leader);
+          } else {
+            tma_load_2d_pair(sa, &tmap_a, k0, m0, full_leader);
+          }
+          if (p.b_mn_major) {
+            tma_load_2d_pair(sb, &tmap_b, nb0, k0, full_leader);
+            tma_load_2d_pair(sb + kChunkBytes, &tmap_b, nb0 + 64, k0, full_leader);
+          } else {
+            tma_load_2d_pair(sb, &tmap_b, k0, nb0, full_leader);
+          }
+          if (++stage == k2Stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (tl) g_gemm_timeline[11] = waited;
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer: the leader's elected lane drives both CTAs' tensor cores
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool alive = true;
+      const uint32_t a_step = p.a_mn_major ? (2 * 1024) >> 4 : (kUmmaK * 2) >> 4;
+      const uint32_t b_step = p.b_mn_major ? (2 * 1024) >> 4 : (kUmmaK * 2) >> 4;
+      unsigned long long wait_data = 0, wait_acc = 0;
+      bool first = true, first_tile = true;
+      for (int tile = cluster; tile < num_tiles && alive; tile += num_clusters) {
+        unsigned long long w0 = tl ? global_ns() : 0;
+        if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, 2)) { alive = false; break; }
+        if (tl) wait_acc += global_ns() - w0;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * kTileN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          w0 = tl ? global_ns() : 0;
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3)) { alive = false; break; }
+          if (tl) {
+            wait_data += global_ns() - w0;
+            if (first) { g_gemm_timeline[3] = global_ns(); first = false; }
+          }
+          tc_fence_after();
+          const uint32_t sa = base + stage * k2StageBytes, sb = sa + k2AStageBytes;
+          const uint64_t adesc = make_smem_desc(sa, p.a_mn_major);
+          const uint64_t bdesc = make_smem_desc(sb, p.b_mn_major);
+#pragma unroll
+          for (int k = 0; k < kTileK / kUmmaK; ++k)
+            umma_f16_pair(tmem_d, adesc + k * a_step, bdesc + k * b_step, p.idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(bar_empty + 8 * stage);  // frees the stage in both CTAs
+          if (++stage == k2Stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!alive) break;
+        umma_commit_pair(bar_acc_full + 8 * acc);   // accumulator halves complete in both CTAs
+        if (tl && first_tile) { g_gemm_timeline[4] = global_ns(); first_tile = false; }
+        if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (tl) { g_gemm_timeline[9] = wait_data; g_gemm_timeline[10] = wait_acc; }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue (warps 2..5 of both CTAs): this CTA's 128 rows x 256 columns
+    const int sub = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool alive = true;
+    const bool tle = tl && warp == 2 && lane == 0;
+    unsigned long long e_wait = 0, e_busy = 0, e_tiles = 0;
+    for (int tile = cluster; tile < num_tiles && alive; tile += num_clusters) {
+      int tm, tn;
+      pair_tile_coords(tile, tiles_m2, tiles_n, &tm, &tn);
+      const int row = tm * 2 * kTileM + static_cast<int>(rank) * kTileM + sub * 32 + lane;
+      const int n0 = tn * kTileN;
+      const unsigned long long e0 = tle ? global_ns() : 0;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, 4))) { alive = false; break; }
+      tc_fence_after();
+      const unsigned long long e1 = tle ? global_ns() : 0;
+      if (tle) {
+        e_wait += e1 - e0;
+        if (e_tiles == 0) g_gemm_timeline[5] = e1;
+      }
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * kTileN;
+      float* bs = bias_smem + (warp - 2) * kTileN;
+#pragma unroll
+      for (int h = 0; h < kTileN / 32; ++h) {
+        const int col = n0 + lane + 32 * h;
+        bs[lane + 32 * h] = (p.bias_dtype != 0 && col < p.N) ? bias_at(p, col) : 0.0f;
+      }
+      __syncwarp();
+#pragma unroll 1
+      for (int c = 0; c < kTileN / 32; c += 2) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;
+        uint32_t r[64];
+        const bool two = col0 + 32 < p.N;
+        if (two) {
+          tmem_ld_32x32_pair(taddr + c * 32, r);
+        } else {
+          tmem_ld_32x32(taddr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        }
+        epilogue_chunk(p, row, col0, &r[0], bs + c * 32);
+        if (two) epilogue_chunk(p, row, col0 + 32, &r[32], bs + c * 32 + 32);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(bar_acc_empty + 8 * acc, 0));  // the leader's barrier counts both CTAs
+      if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
+      if (tle) {
+        const unsigned long long e2 = global_ns();
+        e_busy += e2 - e1;
+        if (e_tiles == 0) g_gemm_timeline[6] = e2;
+        g_gemm_timeline[7] = e2;
+        ++e_tiles;
+      }
+    }
+    if (tle) { g_gemm_timeline[12] = e_wait; g_gemm_timeline[13] = e_busy; g_gemm_timeline[14] = e_tiles; }
+  }
+
+  // ---------------- teardown: neither CTA may leave while its partner can still touch its shared or tensor memory
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(16384);
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+  if (tl && threadIdx.x == 0) g_gemm_timeline[8] = global_ns();
+}
+
 // ------------------------------------------------------------------ host side
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -521,10 +859,18 @@ Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream) {
   const int a_major = operand_major(p.A.data, p.A.rs, p.A.cs, p.M, p.K);
   const int b_major = operand_major(p.B.data, p.B.cs, p.B.rs, p.N, p.K);
 
+  // One CTA per tile (128x256) or a CTA pair per 256x256 tile. The pair needs at least two row tiles to have
+  // work for both halves. AICF_GEMM_CTA_GROUP=1|2 overrides the choice (tuning and A/B tests).
+  bool pair = p.M > kTileM;
+  if (const char* e = std::getenv("AICF_GEMM_CTA_GROUP")) {
+    if (e[0] == '1') pair = false;
+    if (e[0] == '2') pair = true;
+  }
   CUtensorMap ta, tb;
+  const uint32_t b_rows = pair ? k2HalfN : kTileN;
   bool ok_maps = a_major == 0 ? encode_operand(&ta, p.A.data, p.A.dtype, p.K, p.M, p.A.rs, kTileK, kTileM)
                               : encode_operand(&ta, p.A.data, p.A.dtype, p.M, p.K, p.A.cs, 64, kTileK);
-  ok_maps = ok_maps && (b_major == 0 ? encode_operand(&tb, p.B.data, p.B.dtype, p.K, p.N, p.B.cs, kTileK, kTileN)
+  ok_maps = ok_maps && (b_major == 0 ? encode_operand(&tb, p.B.data, p.B.dtype, p.K, p.N, p.B.cs, kTileK, b_rows)
                                      : encode_operand(&tb, p.B.data, p.B.dtype, p.N, p.K, p.B.rs, 64, kTileK));
   if (!ok_maps) return Status::Internal;
 
@@ -533,6 +879,9 @@ Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream) {
   g.bias = p.bias;
   g.ldc = p.C.rs;
   g.bias_stride = p.bias_stride;
+  g.mask = p.mask;
+  g.mask_ld = p.mask_ld;
+  g.mask_vec_ok = p.mask ? (aligned_to(p.mask, 16) && ((p.mask_ld * dtype_size_bytes(p.C.dtype)) % 16 == 0)) : 0;
   g.M = static_cast<int>(p.M);
   g.N = static_cast<int>(p.N);
   g.K = static_cast<int>(p.K);
@@ -546,14 +895,52 @@ Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream) {
   // N>>3 (bits 17-22), M>>4 (bits 24-28)
   g.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(a_major) << 15) |
             (static_cast<uint32_t>(b_major) << 16) | (static_cast<uint32_t>(kTileN >> 3) << 17) |
-            (static_cast<uint32_t>(kTileM >> 4) << 24);
+            (static_cast<uint32_t>((pair ? 2 * kTileM : kTileM) >> 4) << 24);
   const int c_elem = dtype_size_bytes(p.C.dtype);
   g.c_vec_ok = aligned_to(p.C.data, 16) && ((p.C.rs * c_elem) % 16 == 0);
 
-  static bool attr_set[16] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 16 && !attr_set[dev]) {
+  if (dev < 0 || dev >= 16) dev = 0;
+  cudaGetLastError();
+  if (pair) {
+    static int max_clusters[16] = {0};
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = k2SmemBytes;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (max_clusters[dev] == 0) {
+      if (cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(k2SmemBytes)) != cudaSuccess) {
+        cudaGetLastError();
+        return Status::Internal;
+      }
+      cfg.gridDim = dim3(static_cast<unsigned>(sm_count() & ~1));
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_2cta_kernel, &cfg) != cudaSuccess || n < 1) {
+        cudaGetLastError();
+        n = sm_count() / 2;
+      }
+      max_clusters[dev] = n;
+    }
+    const int64_t pair_tiles = ((p.M + 2 * kTileM - 1) / (2 * kTileM)) * ((p.N + kTileN - 1) / kTileN);
+    const int clusters = static_cast<int>(pair_tiles < max_clusters[dev] ? pair_tiles : max_clusters[dev]);
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters));
+    if (cudaLaunchKernelEx(&cfg, gemm_tcgen05_2cta_kernel, ta, tb, g) != cudaSuccess) {
+      cudaGetLastError();
+      return Status::Internal;
+    }
+    return launch_status();
+  }
+  static bool attr_set[16] = {false};
+  if (!attr_set[dev]) {
     if (cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(kSmemBytes)) != cudaSuccess) {
       cudaGetLastError();
@@ -563,7 +950,6 @@ Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream) {
   }
   const int64_t tiles = ((p.M + kTileM - 1) / kTileM) * ((p.N + kTileN - 1) / kTileN);
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-  cudaGetLastError();
   gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, g);
   return launch_status();
 }

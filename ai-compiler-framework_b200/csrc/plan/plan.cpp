@@ -43,7 +43,7 @@ bool kind_of(const std::string& name, OpKind* k) {
       {"batchnorm_fwd", OpKind::BatchNormFwd}, {"batchnorm_bwd", OpKind::BatchNormBwd},
       {"gemm_epilogue", OpKind::GemmEpilogue}, {"softmax", OpKind::Softmax}, {"softmax_ce", OpKind::SoftmaxCE},
       {"reduce_max", OpKind::ReduceMax},  {"reduce_mean", OpKind::ReduceMean}, {"all_reduce", OpKind::AllReduce},
-      {"cast", OpKind::Cast},
+      {"cast", OpKind::Cast},             {"gemm_relu_bwd", OpKind::GemmReluBwd},
   };
   auto it = kMap.find(name);
   if (it == kMap.end()) return false;

@@ -78,6 +78,9 @@ KernelVariant make_gemm_bias_relu_f16_tc_wmma_out_f16_variant();
 KernelVariant make_gemm_bias_relu_bf16_tcgen05_out_bf16_variant();
 KernelVariant make_gemm_bias_relu_bf16_tcgen05_out_f32_variant();
 KernelVariant make_gemm_bias_relu_f16_tcgen05_out_f16_variant();
+KernelVariant make_gemm_relu_bwd_bf16_variant();
+KernelVariant make_gemm_relu_bwd_f16_variant();
+KernelVariant make_gemm_relu_bwd_f32_variant();
 // allreduce.cpp
 KernelVariant make_all_reduce_nccl_f32_variant();
 }  // namespace aicf::cuda
@@ -164,6 +167,9 @@ extern "C" void aicf_cuda_register_all_kernels() {
       {K::SoftmaxCE, make_softmax_ce_bf16_variant, 0, "softmax_ce_bf16_i32_v0"},
       {K::SoftmaxCE, make_softmax_ce_f16_variant, 0, "softmax_ce_f16_i32_v0"},
       {K::Cast, make_cast_variant, 0, "cast_v0"},
+      {K::GemmReluBwd, make_gemm_relu_bwd_bf16_variant, 20, "gemm_relu_bwd_bf16_tcgen05_out_bf16_v0"},
+      {K::GemmReluBwd, make_gemm_relu_bwd_f16_variant, 10, "gemm_relu_bwd_f16_tcgen05_out_f16_v0"},
+      {K::GemmReluBwd, make_gemm_relu_bwd_f32_variant, 0, "gemm_relu_bwd_f32_v0"},
       {K::AllReduce, make_all_reduce_nccl_f32_variant, 0, "all_reduce_nccl_f32_v0"},
   };
 

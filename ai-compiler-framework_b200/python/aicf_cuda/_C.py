@@ -43,6 +43,7 @@ class OpKind(enum.IntEnum):
     ReduceMean = 21
     AllReduce = 22
     Cast = 23
+    GemmReluBwd = 24
 
 
 # pybind's export_values(): enumerators are also module attributes

@@ -9,7 +9,9 @@ working copies of fp32 master weights, and all_reduce for data parallelism.
 Differences from what the reference's lowering would emit, all of them removing work:
   * the activation saved for relu_bwd is the gemm_epilogue output itself (no copy_saved op),
   * no dX for the first layer,
-  * the last Linear is a gemm_epilogue with relu off instead of gemm + bias_add.
+  * the last Linear is a gemm_epilogue with relu off instead of gemm + bias_add,
+  * gemm(dY, W) followed by relu_bwd is one gemm_relu_bwd op: the mask is applied in the GEMM epilogue, which
+    saves one read and one write of the activation gradient per hidden layer.
 """
 from __future__ import annotations
 
@@ -21,7 +23,7 @@ from .plan import ROLE_INPUT, ROLE_PARAM, ROLE_STATIC, ValueSpec
 def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str = "bf16", global_batch: int | None = None,
                          lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
                          weight_decay: float = 0.0, data_parallel: bool = False, with_argmax: bool = False,
-                         input_f32: bool = True) -> Tuple[List[ValueSpec], List[Dict[str, Any]]]:
+                         input_f32: bool = True, fuse_relu_bwd: bool = True) -> Tuple[List[ValueSpec], List[Dict[str, Any]]]:
     """dims = [in, hidden..., out]. Every Linear but the last is followed by ReLU.
 
     compute_dtype 'f32': GEMMs run on fp32 parameters directly.
@@ -58,6 +60,8 @@ def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str 
     colsum_kid = {"f32": "reduce_sum_keep_lastdim_f32_v0", "bf16": "reduce_sum_keep_lastdim_bf16_to_f32_v0",
                   "f16": "reduce_sum_keep_lastdim_f16_to_f32_v0"}[cd]
     relu_bwd_kid = {"f32": "relu_bwd_f32_v0", "bf16": "relu_bwd_bf16_v0", "f16": "relu_bwd_f16_v0"}[cd]
+    fused_kid = {"f32": "gemm_relu_bwd_f32_v0", "bf16": "gemm_relu_bwd_bf16_tcgen05_out_bf16_v0",
+                 "f16": "gemm_relu_bwd_f16_tcgen05_out_f16_v0"}[cd]
     ce_kid = {"f32": "softmax_ce_f32_i32_v0", "bf16": "softmax_ce_bf16_i32_v0", "f16": "softmax_ce_f16_i32_v0"}[cd]
 
     # ---- inputs -------------------------------------------------------------------------------
@@ -117,8 +121,11 @@ def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str 
             op("all_reduce", [db[i]], [db[i]], {"bucket": 2 * i + 1}, "all_reduce_nccl_f32_v0")
         if i > 0:
             dX = val(f"d_relu{i - 1}_out", (batch, dims[i]), cd)
-            op("gemm", [dY, Wlp[i]], [dX], {"transA": False, "transB": False}, gemm_kid)
-            op("relu_bwd", [dX, acts[i]], [dX], None, relu_bwd_kid)  # in place: dX becomes d(pre-activation)
+            if fuse_relu_bwd:
+                op("gemm_relu_bwd", [dY, Wlp[i], acts[i]], [dX], {"transA": False, "transB": False}, fused_kid)
+            else:
+                op("gemm", [dY, Wlp[i]], [dX], {"transA": False, "transB": False}, gemm_kid)
+                op("relu_bwd", [dX, acts[i]], [dX], None, relu_bwd_kid)  # in place: dX becomes d(pre-activation)
             dY = dX
 
     # ---- optimizer ---------------------------------------------------------------------------------

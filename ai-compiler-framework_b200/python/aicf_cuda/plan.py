@@ -50,7 +50,7 @@ def pack_attrs(op: str, attrs: Optional[Dict[str, Any]]) -> Tuple[int, bytes]:
     op = str(op).strip().lower()
     a = dict(attrs or {})
     ta, tb = int(bool(a.get("transA", False))), int(bool(a.get("transB", False)))
-    if op == "gemm":
+    if op in ("gemm", "gemm_relu_bwd"):
         return SCHEMA_GEMM, struct.pack("<ii", ta, tb)
     if op == "gemm_epilogue":
         return SCHEMA_GEMM_EPILOGUE, struct.pack("<iii", ta, tb, _relu_flag(a))

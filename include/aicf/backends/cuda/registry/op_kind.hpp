@@ -32,8 +32,9 @@ enum class OpKind : int {
   ReduceMean = 21,  // last-axis mean
   AllReduce = 22,   // in-place sum over data-parallel ranks
   Cast = 23,        // dtype conversion (f32 <-> bf16/f16)
+  GemmReluBwd = 24, // dX = (Y > 0) ? dY * op(W) : 0  (the ReLU backward mask applied in the GEMM epilogue)
 
-  _Count = 24,
+  _Count = 25,
   // Number of kinds the reference defines; ids below this resolve exactly as there.
   _ReferenceCount = 18
 };
@@ -66,6 +67,7 @@ inline const char* op_kind_name(OpKind k) {
     case OpKind::ReduceMean: return "reduce_mean";
     case OpKind::AllReduce: return "all_reduce";
     case OpKind::Cast: return "cast";
+    case OpKind::GemmReluBwd: return "gemm_relu_bwd";
     default: return "unknown";
   }
 }

@@ -45,6 +45,8 @@ def run_lowered(lowered: Sequence[Dict[str, Any]], env: Dict[int, np.ndarray], d
             store(o[0], O.gemm(i[0], i[1], a.get("transA", False), a.get("transB", False), dt))
         elif op == "gemm_epilogue":
             store(o[0], O.gemm_epilogue(i[0], i[1], i[2], a.get("transA", False), a.get("transB", False), _relu_flag(a), dt))
+        elif op == "gemm_relu_bwd":
+            store(o[0], O.gemm_relu_bwd(i[0], i[1], i[2], a.get("transA", False), a.get("transB", False), dt))
         elif op == "bias_add":
             store(o[0], O.bias_add(i[0], i[1], dt))
         elif op == "relu":

@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import numpy as np
 
-__all__ = ["bf16_round", "f16_round", "gemm", "gemm_epilogue", "bias_add", "relu", "relu_bwd", "copy", "grad_zero",
+__all__ = ["bf16_round", "f16_round", "gemm", "gemm_epilogue", "gemm_relu_bwd", "bias_add", "relu", "relu_bwd", "copy", "grad_zero",
            "mse_grad", "reduce_sum_columns", "reduce_lastaxis", "adam_step_v0", "adam_step_fused", "step_inc",
            "bias_corr", "sgd_step", "add", "softmax", "softmax_ce", "cast"]
 
@@ -35,6 +35,12 @@ def gemm_epilogue(A, B, bias, transA=False, transB=False, relu=True, dt=np.float
     to on when no attrs are given, :57-60)."""
     c = gemm(A, B, transA, transB, dt) + np.asarray(bias, dt)[None, :]
     return np.maximum(c, 0) if relu else c
+
+
+def gemm_relu_bwd(dY, W, Y, transA=False, transB=False, dt=np.float64):
+    """dX = (Y > 0) ? op(dY) @ op(W) : 0 - the reference's gemm followed by its relu_bwd
+    (python/aicf_fw/core_v2/lower.py:88-111 emits them as two ops; ops/relu_bwd/launcher.cu:37-44)."""
+    return relu_bwd(gemm(dY, W, transA, transB, dt), Y, dt)
 
 
 def bias_add(Y, bias, dt=np.float64):

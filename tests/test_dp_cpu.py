@@ -95,7 +95,8 @@ def test_sharding_rule_and_lowering_shape():
     assert loss_scale(65536) == 1.0 / 65536
     vals, low = build_mlp_train_step(8192, [8192] * 5 + [1000], compute_dtype="bf16", global_batch=65536, data_parallel=True)
     names = [it["op"] for it in low]
-    assert names.count("all_reduce") == 10 and names.count("gemm") == 9 and names.count("gemm_epilogue") == 5
+    assert names.count("all_reduce") == 10 and names.count("gemm") == 5 and names.count("gemm_relu_bwd") == 4
+    assert names.count("gemm_epilogue") == 5 and "relu_bwd" not in names
     # every all_reduce sits after the op that produces its gradient and before the Adam that consumes it
     for i, it in enumerate(low):
         if it["op"] == "all_reduce":

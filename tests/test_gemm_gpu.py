@@ -35,6 +35,13 @@ EPI_KID = {("bf16", "bf16"): "gemm_bias_relu_bf16_tcgen05_out_bf16_v0", ("bf16",
            ("f16", "f16"): "gemm_bias_relu_f16_tcgen05_out_f16_v0", ("f32", "f32"): "gemm_bias_relu_f32_naive_v0"}
 TOL = {"bf16": 2e-2, "f16": 2e-2, "f32": 1e-5}
 
+@pytest.fixture(params=["1", "2"], ids=["cta1", "cta2"])
+def cta_group(request, monkeypatch):
+    """Runs a test once with one CTA per tile and once with CTA pairs (tcgen05 cta_group::2)."""
+    monkeypatch.setenv("AICF_GEMM_CTA_GROUP", request.param)
+    return request.param
+
+
 SHAPES = [(64, 80, 48), (128, 256, 64), (256, 512, 128), (200, 304, 136), (1, 8, 8), (129, 257, 72), (384, 1000, 512),
           (1024, 1024, 1024)]
 
@@ -42,7 +49,7 @@ SHAPES = [(64, 80, 48), (128, 256, 64), (256, 512, 128), (200, 304, 136), (1, 8,
 @pytest.mark.parametrize("M,N,K", SHAPES)
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
 @pytest.mark.parametrize("dt,out", [("bf16", "bf16"), ("bf16", "f32"), ("f16", "f16"), ("f32", "f32")])
-def test_gemm_all_transposes(gpu, M, N, K, ta, tb, dt, out):
+def test_gemm_all_transposes(gpu, cta_group, M, N, K, ta, tb, dt, out):
     # operands whose rows are not 16-byte aligned route to the SIMT kernel inside the same variant
     A, B, _, sa, sb = _operands(M, N, K, ta, tb, dt)
     C = Tensor.empty((M, N), out)
@@ -57,7 +64,7 @@ def test_gemm_all_transposes(gpu, M, N, K, ta, tb, dt, out):
 @pytest.mark.parametrize("relu", [1, 0])
 @pytest.mark.parametrize("dt,out,bias_dt", [("bf16", "bf16", "f32"), ("bf16", "bf16", "bf16"), ("f16", "f16", "f32"),
                                             ("bf16", "f32", "f32"), ("f32", "f32", "f32")])
-def test_gemm_epilogue_bias_relu(gpu, M, N, K, ta, tb, relu, dt, out, bias_dt):
+def test_gemm_epilogue_bias_relu(gpu, cta_group, M, N, K, ta, tb, relu, dt, out, bias_dt):
     A, B, bias, sa, sb = _operands(M, N, K, ta, tb, dt)
     bias = _ROUND[bias_dt](bias)
     C = Tensor.empty((M, N), out)
@@ -68,6 +75,27 @@ def test_gemm_epilogue_bias_relu(gpu, M, N, K, ta, tb, relu, dt, out, bias_dt):
     assert rel_err(host(C), want) <= (TOL[dt] if out != "f32" or dt == "f32" else 1e-4)
     if relu:
         assert (host(C) >= 0).all()
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 80, 48), (256, 512, 128), (200, 304, 136), (129, 257, 72), (512, 1024, 1000)])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1)])
+@pytest.mark.parametrize("dt", ["bf16", "f16", "f32"])
+def test_gemm_with_relu_backward_mask(gpu, cta_group, M, N, K, ta, tb, dt):
+    """dX = (Y > 0) ? dY*op(W) : 0 in one kernel == the reference's gemm followed by relu_bwd."""
+    A, B, _, sa, sb = _operands(M, N, K, ta, tb, dt)
+    y = _ROUND[dt](np.random.default_rng(7).standard_normal((M, N)).astype(np.float32))
+    y[::3, ::5] = 0.0
+    y[1, 1] = np.nan
+    kid = {"bf16": "gemm_relu_bwd_bf16_tcgen05_out_bf16_v0", "f16": "gemm_relu_bwd_f16_tcgen05_out_f16_v0", "f32": "gemm_relu_bwd_f32_v0"}[dt]
+    C = Tensor.empty((M, N), dt)
+    by_id(kid, OpKind.GemmReluBwd, [dev(sa, dt), dev(sb, dt), dev(y, dt)], [C], GEMM, struct.pack("<ii", ta, tb))
+    assert _C.gemm_status() == 0
+    got = host(C)
+    want = oracle.gemm_relu_bwd(A, B, np.nan_to_num(y, nan=-1.0))  # NaN > 0 is false: masked
+    assert rel_err(got, want) <= TOL[dt]
+    assert not got[~(y > 0)].any(), "every element whose activation is not positive must be exactly zero"
+    with pytest.raises(RuntimeError, match="InvalidArgument"):  # the mask must have the output's shape
+        by_id(kid, OpKind.GemmReluBwd, [dev(sa, dt), dev(sb, dt), dev(y[:, :-8].copy(), dt)], [C], GEMM, struct.pack("<ii", ta, tb))
 
 
 def test_reference_ids_keep_reference_contracts(gpu):
@@ -106,7 +134,7 @@ def test_f32_matches_sequential_fma_order(gpu):
 
 
 @pytest.mark.parametrize("size", [4096, 8192])
-def test_large_bf16_gemm_sampled_rows(gpu, size):
+def test_large_bf16_gemm_sampled_rows(gpu, cta_group, size):
     """Full benchmark sizes: 64 sampled rows against fp64, plus linearity C(2A) == 2 C(A) on the device."""
     M = N = K = size
     rng = np.random.default_rng(1)

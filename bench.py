@@ -265,11 +265,18 @@ def run_mlp(args, dist: Dist):
     batch = gbatch // world
     aicf_cuda._lib.check(lib.aicf_b200_set_device(local_rank), "set_device")
     if world > 1:
-        idbuf = (C.c_uint8 * 128)()
-        if rank == 0:
-            aicf_cuda._lib.check(lib.aicf_b200_dp_unique_id(idbuf), "dp_unique_id")
-        uid = dist.bcast_bytes(bytes(idbuf) if rank == 0 else None)
-        aicf_cuda._lib.check(lib.aicf_b200_dp_init(rank, world, (C.c_uint8 * 128).from_buffer_copy(uid)), "dp_init")
+        from aicf_cuda import dp
+        # NCCL prints its version banner on stdout at communicator creation; stdout carries the one JSON line only,
+        # so file descriptor 1 points at stderr while the communicator comes up.
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dp.init_communicator(rank, world, dist.bcast_bytes)
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
 
     dbl, plan, vals, low = build_mlp(aicf_cuda, dims, batch, gbatch, dp=world > 1)
     init_mlp_params(aicf_cuda, plan, dims, seed=4)

@@ -13,6 +13,7 @@ namespace aicf::cuda {
 int gemm_tcgen05_status(bool clear);
 int row_pipeline_status(bool clear);
 int gemm_tcgen05_timeline(int enable, unsigned long long* out16);
+int dp_wait_status(bool clear);
 }
 
 static_assert(sizeof(aicf_tensor_desc) == sizeof(aicf::cuda::TensorDesc), "C and C++ tensor descriptors must match");
@@ -239,8 +240,9 @@ int aicf_b200_gemm_timeline(int enable, uint64_t* out16) {
 int aicf_b200_wait_status(int clear) {
   const int g = aicf::cuda::gemm_tcgen05_status(clear != 0);
   const int r = aicf::cuda::row_pipeline_status(clear != 0);
-  if (g < 0 || r < 0) return -1;
-  return (g & 0xFFFF) | (r ? 0x10000 : 0);
+  const int d = aicf::cuda::dp_wait_status(clear != 0);
+  if (g < 0 || r < 0 || d < 0) return -1;
+  return (g & 0xFFFF) | (r ? 0x10000 : 0) | ((d & 3) << 17);
 }
 
 // ---- trace ------------------------------------------------------------------------------------

@@ -26,6 +26,12 @@ using aicf::cuda::Status;
 using aicf::cuda::TensorDesc;
 using namespace aicf::capi;
 
+namespace aicf::cuda {
+size_t dp_control_bytes();
+bool dp_register_pool(void* mine, size_t bytes, void* const* peers, int rank, int world);
+void dp_unregister_pool(void* mine);
+}  // namespace aicf::cuda
+
 namespace {
 
 constexpr size_t kAlign = 256;
@@ -44,6 +50,7 @@ bool kind_of(const std::string& name, OpKind* k) {
       {"gemm_epilogue", OpKind::GemmEpilogue}, {"softmax", OpKind::Softmax}, {"softmax_ce", OpKind::SoftmaxCE},
       {"reduce_max", OpKind::ReduceMax},  {"reduce_mean", OpKind::ReduceMean}, {"all_reduce", OpKind::AllReduce},
       {"cast", OpKind::Cast},             {"gemm_relu_bwd", OpKind::GemmReluBwd},
+      {"dp_adam_step", OpKind::DpAdamStep},
   };
   auto it = kMap.find(name);
   if (it == kMap.end()) return false;
@@ -63,6 +70,7 @@ struct Value {
   int alias_of = -1;
   void* ptr = nullptr;
   bool bound = false;   // caller-owned memory
+  bool peer_visible = false;  // lives in the pool that other ranks map (gradients, broadcast working copies)
   size_t bytes = 0;
   int first = -1, last = -1;  // live range in op indices
 };
@@ -93,6 +101,11 @@ struct aicf_plan {
   void* ws = nullptr;
   size_t ws_bytes = 0;
   std::vector<void*> owned;
+  void* peer_pool = nullptr;       // one allocation: control block + every peer-visible value
+  size_t peer_pool_bytes = 0;
+  std::vector<void*> peer_mapped;  // other ranks' pools opened through IPC handles
+  bool peers_open = false;
+  int peer_world = 1;
   cudaStream_t stream = nullptr, comm_stream = nullptr;
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
@@ -193,7 +206,7 @@ size_t assign_arena(std::vector<Value*>& vals, int num_ops, std::map<int, size_t
 int enqueue_all(aicf_plan* p, cudaStream_t main, std::vector<cudaEvent_t>* marks = nullptr) {
   // vid -> event a later op on `main` must wait for (pending all_reduce on the comm stream)
   std::map<int, cudaEvent_t> pending;
-  const bool overlap = aicf_b200_dp_world_size() > 1 && !marks;
+  const bool overlap = (aicf_b200_dp_world_size() > 1 || p->peer_world > 1) && !marks;
   for (size_t i = 0; i < p->ops.size(); ++i) {
     Op& op = p->ops[i];
     if (marks)
@@ -213,7 +226,7 @@ int enqueue_all(aicf_plan* p, cudaStream_t main, std::vector<cudaEvent_t>* marks
       if (int rc = wait_for(vid)) return rc;
 
     cudaStream_t s = main;
-    const bool on_comm = overlap && op.kind == OpKind::AllReduce && op.ev_ready && op.ev_done;
+    const bool on_comm = overlap && (op.kind == OpKind::AllReduce || op.kind == OpKind::DpAdamStep) && op.ev_ready && op.ev_done;
     if (on_comm) {
       if (int rc = check_cuda(cudaEventRecord(op.ev_ready, main), "cudaEventRecord(fork)")) return rc;
       if (int rc = check_cuda(cudaStreamWaitEvent(p->comm_stream, op.ev_ready, 0), "cudaStreamWaitEvent(fork)")) return rc;
@@ -262,6 +275,12 @@ void aicf_b200_plan_destroy(aicf_plan* p) {
     if (op.ev_done) cudaEventDestroy(op.ev_done);
   }
   for (void* q : p->owned) cudaFree(q);
+  if (p->peer_pool) {
+    aicf::cuda::dp_unregister_pool(p->peer_pool);
+    for (void* q : p->peer_mapped)
+      if (q) cudaIpcCloseMemHandle(q);
+    cudaFree(p->peer_pool);
+  }
   if (p->arena) cudaFree(p->arena);
   if (p->ws) cudaFree(p->ws);
   if (p->stream) cudaStreamDestroy(p->stream);
@@ -340,6 +359,54 @@ int aicf_b200_plan_bind(aicf_plan* p, int vid, void* device_ptr) {
   return AICF_OK;
 }
 
+int aicf_b200_plan_set_peer_visible(aicf_plan* p, int vid) {
+  if (!p || p->finalized) return fail(Status::InvalidArgument, "plan_set_peer_visible: plan missing or finalized");
+  Value* v = p->find(vid);
+  if (!v) return fail(Status::InvalidArgument, "plan_set_peer_visible: unknown value id");
+  v->peer_visible = true;
+  v->persistent = true;
+  return AICF_OK;
+}
+
+int aicf_b200_plan_peer_handle(aicf_plan* p, void* handle64, size_t* pool_bytes) {
+  if (!p || !p->finalized || !handle64) return fail(Status::InvalidArgument, "plan_peer_handle: plan not finalized or null output");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size is part of the ABI");
+  if (pool_bytes) *pool_bytes = p->peer_pool_bytes;
+  std::memset(handle64, 0, 64);
+  if (!p->peer_pool) return AICF_OK;  // nothing to share
+  cudaIpcMemHandle_t h;
+  if (int rc = check_cuda(cudaIpcGetMemHandle(&h, p->peer_pool), "cudaIpcGetMemHandle")) return rc;
+  std::memcpy(handle64, &h, 64);
+  return AICF_OK;
+}
+
+int aicf_b200_plan_open_peers(aicf_plan* p, int rank, int world, const void* handles) {
+  if (!p || !p->finalized) return fail(Status::InvalidArgument, "plan_open_peers: plan not finalized");
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(Status::InvalidArgument, "plan_open_peers: bad rank/world");
+  if (!p->peer_pool) return AICF_OK;
+  if (p->peers_open) return fail(Status::InvalidArgument, "plan_open_peers: already open");
+  if (world > 1 && !handles) return fail(Status::InvalidArgument, "plan_open_peers: null handles");
+  std::vector<void*> bases(static_cast<size_t>(world), nullptr);
+  p->peer_mapped.assign(static_cast<size_t>(world), nullptr);
+  for (int k = 0; k < world; ++k) {
+    if (k == rank) {
+      bases[static_cast<size_t>(k)] = p->peer_pool;
+      continue;
+    }
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, static_cast<const uint8_t*>(handles) + 64 * static_cast<size_t>(k), 64);
+    void* q = nullptr;
+    if (int rc = check_cuda(cudaIpcOpenMemHandle(&q, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle")) return rc;
+    p->peer_mapped[static_cast<size_t>(k)] = q;
+    bases[static_cast<size_t>(k)] = q;
+  }
+  if (!aicf::cuda::dp_register_pool(p->peer_pool, p->peer_pool_bytes, bases.data(), rank, world))
+    return fail(Status::Internal, "plan_open_peers: pool registration failed");
+  p->peers_open = true;
+  p->peer_world = world;
+  return AICF_OK;
+}
+
 int aicf_b200_plan_finalize(aicf_plan* p) {
   if (!p || p->finalized) return fail(Status::InvalidArgument, "plan_finalize: plan missing or already finalized");
   KernelRegistry::ensure_registered();
@@ -363,11 +430,39 @@ int aicf_b200_plan_finalize(aicf_plan* p) {
       if (t) t->persistent = true;
     }
 
+  // peer-visible values: one pool that starts with the exchange's control block
+  {
+    size_t pool = aicf::cuda::dp_control_bytes();
+    bool any = false;
+    for (auto& kv : p->values) {
+      Value& v = kv.second;
+      if (v.alias_of >= 0 || v.bound || !v.peer_visible) continue;
+      any = true;
+      pool += round_up(v.bytes, kAlign);
+    }
+    if (any) {
+      if (int rc = check_cuda(cudaMalloc(&p->peer_pool, pool), "cudaMalloc(peer pool)")) return rc;
+      if (int rc = check_cuda(cudaMemset(p->peer_pool, 0, pool), "cudaMemset(peer pool)")) return rc;
+      p->peer_pool_bytes = pool;
+      size_t off = aicf::cuda::dp_control_bytes();
+      for (auto& kv : p->values) {
+        Value& v = kv.second;
+        if (v.alias_of >= 0 || v.bound || !v.peer_visible) continue;
+        v.ptr = static_cast<uint8_t*>(p->peer_pool) + off;
+        off += round_up(v.bytes, kAlign);
+      }
+    }
+  }
+
   std::vector<Value*> arena_vals;
   p->no_reuse_bytes = 0;
   for (auto& kv : p->values) {
     Value& v = kv.second;
     if (v.alias_of >= 0 || v.bound) continue;
+    if (v.peer_visible && v.ptr) {
+      if (v.role == AICF_ROLE_STATIC) p->no_reuse_bytes += round_up(v.bytes, kAlign);
+      continue;
+    }
     if (v.role == AICF_ROLE_STATIC) p->no_reuse_bytes += round_up(v.bytes, kAlign);
     if (v.role == AICF_ROLE_STATIC && !v.persistent && !v.zero_init && v.first >= 0) {
       arena_vals.push_back(&v);
@@ -438,7 +533,7 @@ int aicf_b200_plan_finalize(aicf_plan* p) {
     }
     if (op.variant->query_workspace) op.ws_bytes = op.variant->query_workspace(op.in_desc.data(), ni, &op.blob);
     ws_need = std::max(ws_need, op.ws_bytes);
-    if (op.kind == OpKind::AllReduce) any_allreduce = true;
+    if (op.kind == OpKind::AllReduce || op.kind == OpKind::DpAdamStep) any_allreduce = true;
   }
   if (ws_need) {
     p->ws_bytes = round_up(ws_need, kAlign);
@@ -448,7 +543,7 @@ int aicf_b200_plan_finalize(aicf_plan* p) {
   if (any_allreduce) {
     if (int rc = check_cuda(cudaStreamCreateWithFlags(&p->comm_stream, cudaStreamNonBlocking), "cudaStreamCreateWithFlags")) return rc;
     for (Op& op : p->ops)
-      if (op.kind == OpKind::AllReduce) {
+      if (op.kind == OpKind::AllReduce || op.kind == OpKind::DpAdamStep) {
         if (int rc = check_cuda(cudaEventCreateWithFlags(&op.ev_ready, cudaEventDisableTiming), "cudaEventCreate")) return rc;
         if (int rc = check_cuda(cudaEventCreateWithFlags(&op.ev_done, cudaEventDisableTiming), "cudaEventCreate")) return rc;
       }

@@ -83,6 +83,8 @@ KernelVariant make_gemm_relu_bwd_f16_variant();
 KernelVariant make_gemm_relu_bwd_f32_variant();
 // allreduce.cpp
 KernelVariant make_all_reduce_nccl_f32_variant();
+// dp_adam.cu
+KernelVariant make_dp_adam_step_variant();
 }  // namespace aicf::cuda
 
 namespace {
@@ -171,6 +173,7 @@ extern "C" void aicf_cuda_register_all_kernels() {
       {K::GemmReluBwd, make_gemm_relu_bwd_f16_variant, 10, "gemm_relu_bwd_f16_tcgen05_out_f16_v0"},
       {K::GemmReluBwd, make_gemm_relu_bwd_f32_variant, 0, "gemm_relu_bwd_f32_v0"},
       {K::AllReduce, make_all_reduce_nccl_f32_variant, 0, "all_reduce_nccl_f32_v0"},
+      {K::DpAdamStep, make_dp_adam_step_variant, 0, "dp_adam_step_f32_p2p_v0"},
   };
 
   KernelRegistry& reg = KernelRegistry::instance();

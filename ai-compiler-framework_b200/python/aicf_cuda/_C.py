@@ -44,6 +44,7 @@ class OpKind(enum.IntEnum):
     AllReduce = 22
     Cast = 23
     GemmReluBwd = 24
+    DpAdamStep = 25
 
 
 # pybind's export_values(): enumerators are also module attributes

@@ -104,6 +104,9 @@ PROTOTYPES = {
     "aicf_b200_plan_add_op": (_i, [_vp, _cp, _cp, _P(_i), _i, _P(_i), _i, C.c_uint32, _vp, C.c_uint32]),
     "aicf_b200_plan_alias": (_i, [_vp, _i, _i]),
     "aicf_b200_plan_bind": (_i, [_vp, _i, _vp]),
+    "aicf_b200_plan_set_peer_visible": (_i, [_vp, _i]),
+    "aicf_b200_plan_peer_handle": (_i, [_vp, _vp, _P(_sz)]),
+    "aicf_b200_plan_open_peers": (_i, [_vp, _i, _i, _vp]),
     "aicf_b200_plan_finalize": (_i, [_vp]),
     "aicf_b200_plan_value_ptr": (_vp, [_vp, _i]),
     "aicf_b200_plan_value_bytes": (_sz, [_vp, _i]),

@@ -57,5 +57,26 @@ def init_from_torch_distributed() -> Tuple[int, int]:
     return rank, world
 
 
+def connect_plans(plans, rank: int, world: int, allgather) -> None:
+    """Lets every plan's dp_adam_step ops reach the other ranks' gradient and weight buffers.
+    `allgather(obj)` must return the list of every rank's `obj` in rank order (for instance
+    torch.distributed.all_gather_object). All ranks must pass their plans in the same order."""
+    for plan in plans:
+        handles = allgather(plan.peer_handle())
+        plan.open_peers(rank, world, handles)
+
+
+def connect_plans_torch(plans) -> None:
+    import torch.distributed as td
+    rank, world = td.get_rank(), td.get_world_size()
+
+    def gather(obj):
+        out = [None] * world
+        td.all_gather_object(out, obj)
+        return out
+
+    connect_plans(plans, rank, world, gather)
+
+
 def finalize() -> None:
     check(lib.aicf_b200_dp_finalize(), "dp_finalize")

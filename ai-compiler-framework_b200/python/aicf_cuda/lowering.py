@@ -22,7 +22,7 @@ from .plan import ROLE_INPUT, ROLE_PARAM, ROLE_STATIC, ValueSpec
 
 def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str = "bf16", global_batch: int | None = None,
                          lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
-                         weight_decay: float = 0.0, data_parallel: bool = False, with_argmax: bool = False,
+                         weight_decay: float = 0.0, data_parallel=False, with_argmax: bool = False,
                          input_f32: bool = True, fuse_relu_bwd: bool = True) -> Tuple[List[ValueSpec], List[Dict[str, Any]]]:
     """dims = [in, hidden..., out]. Every Linear but the last is followed by ReLU.
 
@@ -31,9 +31,16 @@ def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str 
     working copies ('<i>.W.lp') which the fused Adam rewrites every step; activations are 16-bit.
     The loss gradient is scaled by 1/global_batch so that summed shard gradients equal the
     single-device gradient.
+
+    data_parallel: False - single device; True / "nccl" - an all_reduce op per gradient tensor, then the
+    ordinary fused Adam; "fused" - one dp_adam_step op per parameter that exchanges the gradient over peer
+    memory, updates the owning rank's shard and broadcasts the new weights (master weights and moments of
+    matrices are then sharded over the ranks).
     """
     L = len(dims) - 1
     assert L >= 1
+    dp_mode = {False: None, None: None, True: "nccl", "nccl": "nccl", "fused": "fused"}[data_parallel]
+    fused_dp = dp_mode == "fused"
     cd = compute_dtype
     mixed = cd != "f32"
     gb = int(global_batch or batch)
@@ -41,9 +48,9 @@ def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str 
     ops: List[Dict[str, Any]] = []
     ids: Dict[str, int] = {}
 
-    def val(name, shape, dtype, role=None, persistent=False, zero=None) -> int:
+    def val(name, shape, dtype, role=None, persistent=False, zero=None, peer=False) -> int:
         vid = len(vals)
-        vals.append(ValueSpec(vid, name, tuple(shape), dtype, role, persistent, zero))
+        vals.append(ValueSpec(vid, name, tuple(shape), dtype, role, persistent, zero, None, peer))
         ids[name] = vid
         return vid
 
@@ -77,14 +84,22 @@ def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str 
     W, b, Wlp, mW, vW, mb, vb = [], [], [], [], [], [], []
     for i in range(L):
         li = 2 * i  # reference naming: Sequential index of the Linear ("0.W", "2.W", ...)
-        W.append(val(f"{li}.W", (dims[i + 1], dims[i]), "f32", ROLE_PARAM))
-        b.append(val(f"{li}.b", (dims[i + 1],), "f32", ROLE_PARAM))
-        Wlp.append(val(f"{li}.W.lp", (dims[i + 1], dims[i]), cd, ROLE_STATIC, persistent=True) if mixed else W[-1])
+        # with the fused exchange, whatever the owning rank broadcasts must be mapped by the peers: the working
+        # copy of a matrix (or the matrix itself in fp32 mode) and the bias
+        W.append(val(f"{li}.W", (dims[i + 1], dims[i]), "f32", ROLE_PARAM, peer=fused_dp and not mixed))
+        b.append(val(f"{li}.b", (dims[i + 1],), "f32", ROLE_PARAM, peer=fused_dp))
+        Wlp.append(val(f"{li}.W.lp", (dims[i + 1], dims[i]), cd, ROLE_STATIC, persistent=True, peer=fused_dp) if mixed else W[-1])
         mW.append(val(f"opt.m.{li}.W", (dims[i + 1], dims[i]), "f32", persistent=True))
         vW.append(val(f"opt.v.{li}.W", (dims[i + 1], dims[i]), "f32", persistent=True))
         mb.append(val(f"opt.m.{li}.b", (dims[i + 1],), "f32", persistent=True))
         vb.append(val(f"opt.v.{li}.b", (dims[i + 1],), "f32", persistent=True))
     step = val("opt.step", (1,), "i32", persistent=True)
+
+    hyper = {"lr": lr, "beta1": beta1, "beta2": beta2, "eps": eps}
+    if weight_decay:
+        hyper["weight_decay"] = weight_decay
+    if fused_dp:  # the optimizer ops are interleaved with the backward pass, so the counter moves first
+        op("step_inc", [step], [step], None, "step_inc_v0")
 
     # ---- forward ---------------------------------------------------------------------------------
     acts = [x]
@@ -112,11 +127,11 @@ def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str 
     dY = dlogits
     for i in reversed(range(L)):
         li = 2 * i
-        dW[i] = val(f"d_{li}.W", (dims[i + 1], dims[i]), "f32")
-        db[i] = val(f"d_{li}.b", (dims[i + 1],), "f32")
+        dW[i] = val(f"d_{li}.W", (dims[i + 1], dims[i]), "f32", peer=fused_dp)
+        db[i] = val(f"d_{li}.b", (dims[i + 1],), "f32", peer=fused_dp)
         op("gemm", [dY, acts[i]], [dW[i]], {"transA": True, "transB": False}, gemm_f32out_kid)
         op("reduce_sum", [dY], [db[i]], {"axis": 0, "keepdim": False}, colsum_kid)
-        if data_parallel:
+        if dp_mode == "nccl":
             op("all_reduce", [dW[i]], [dW[i]], {"bucket": 2 * i}, "all_reduce_nccl_f32_v0")
             op("all_reduce", [db[i]], [db[i]], {"bucket": 2 * i + 1}, "all_reduce_nccl_f32_v0")
         if i > 0:
@@ -127,12 +142,17 @@ def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str 
                 op("gemm", [dY, Wlp[i]], [dX], {"transA": False, "transB": False}, gemm_kid)
                 op("relu_bwd", [dX, acts[i]], [dX], None, relu_bwd_kid)  # in place: dX becomes d(pre-activation)
             dY = dX
+        if fused_dp:
+            # after dX: from here on this rank no longer reads layer i's weights, so peers may overwrite them
+            outs = [W[i], mW[i], vW[i]] + ([Wlp[i]] if mixed else [])
+            op("dp_adam_step", [W[i], dW[i], mW[i], vW[i], step], outs, dict(hyper, slot=2 * i), "dp_adam_step_f32_p2p_v0")
+            op("dp_adam_step", [b[i], db[i], mb[i], vb[i], step], [b[i], mb[i], vb[i]], dict(hyper, slot=2 * i + 1),
+               "dp_adam_step_f32_p2p_v0")
+    if fused_dp:
+        return vals, ops
 
     # ---- optimizer ---------------------------------------------------------------------------------
     op("step_inc", [step], [step], None, "step_inc_v0")
-    hyper = {"lr": lr, "beta1": beta1, "beta2": beta2, "eps": eps}
-    if weight_decay:
-        hyper["weight_decay"] = weight_decay
     for i in range(L):
         outs = [W[i], mW[i], vW[i]] + ([Wlp[i]] if mixed else [])
         op("adam_step", [W[i], dW[i], mW[i], vW[i], step], outs, hyper, "adam_step_f32_fused_v1")

@@ -59,6 +59,11 @@ class DoubleBufferedStep:
         buf = (C.c_uint8 * (2 * nb)).from_address(p.value)
         self._result_host = np.frombuffer(buf, dtype=np.float32).reshape(2, -1)
 
+    def connect(self, rank: int, world: int, allgather) -> None:
+        """Data-parallel runs with dp_adam_step ops: maps the peers' pools for both plans (see dp.connect_plans)."""
+        from .dp import connect_plans
+        connect_plans(self.plans, rank, world, allgather)
+
     def capture(self) -> None:
         for p in self.plans:
             p.capture()

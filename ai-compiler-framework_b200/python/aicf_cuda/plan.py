@@ -29,6 +29,7 @@ SCHEMA_BIAS_ADD = 0x44444142
 SCHEMA_MSE_GRAD = 0x4745534D
 SCHEMA_SOFTMAX_CE = 0x45434D53
 SCHEMA_ALL_REDUCE = 0x44455241
+SCHEMA_DP_ADAM = 0x44415044
 # What the reference's Python executor sends for gemm_epilogue (exec.py:215-217); the reference's C++
 # does not know this tag and silently applies its defaults.
 SCHEMA_GEPI_AS_SENT_BY_REFERENCE_EXECUTOR = int.from_bytes(b"GEPI", "little")
@@ -62,6 +63,11 @@ def pack_attrs(op: str, attrs: Optional[Dict[str, Any]]) -> Tuple[int, bytes]:
         if "weight_decay" in a or "decoupled" in a:
             payload += struct.pack("<fI", float(a.get("weight_decay", 0.0)), 1 if a.get("decoupled", False) else 0)
         return SCHEMA_ADAM, payload
+    if op == "dp_adam_step":
+        return SCHEMA_DP_ADAM, struct.pack("<fffffIi", float(a.get("lr", 1e-3)), float(a.get("beta1", 0.9)),
+                                           float(a.get("beta2", 0.999)), float(a.get("eps", 1e-8)),
+                                           float(a.get("weight_decay", 0.0)), 1 if a.get("decoupled", False) else 0,
+                                           int(a["slot"]))
     if op == "bias_corr":
         return SCHEMA_BIAS_CORR, struct.pack("<ff", float(a.get("beta1", 0.9)), float(a.get("beta2", 0.999)))
     if op == "sgd_step" and "lr" in a:
@@ -124,6 +130,7 @@ class ValueSpec:
     persistent: bool = False          # keep out of arena reuse (read after the step)
     zero_init: Optional[bool] = None  # None -> needs_zero_init(name)
     alias_of: Optional[int] = None
+    peer_visible: bool = False        # mapped by the other data-parallel ranks (gradients, broadcast copies)
 
 
 class Plan:
@@ -150,6 +157,8 @@ class Plan:
         for v in self.values.values():
             if v.alias_of is not None:
                 check(lib.aicf_b200_plan_alias(self._h, v.vid, v.alias_of), "plan_alias")
+            if v.peer_visible:
+                check(lib.aicf_b200_plan_set_peer_visible(self._h, v.vid), "plan_set_peer_visible")
         for vid, t in (bind or {}).items():
             check(lib.aicf_b200_plan_bind(self._h, int(vid), int(t.data_ptr())), "plan_bind")
             self._keep.append(t)
@@ -195,6 +204,22 @@ class Plan:
 
     def kernel_ids(self) -> List[str]:
         return [lib.aicf_b200_plan_op_kernel_id(self._h, i).decode() for i in range(lib.aicf_b200_plan_num_ops(self._h))]
+
+    # ---- data-parallel peer memory ---------------------------------------------------------------------
+    def peer_handle(self) -> bytes:
+        """64-byte IPC handle of this plan's peer-visible pool (all zero when there is none)."""
+        buf = (C.c_uint8 * 64)()
+        n = C.c_size_t(0)
+        check(lib.aicf_b200_plan_peer_handle(self._h, buf, C.byref(n)), "plan_peer_handle")
+        return bytes(buf)
+
+    def open_peers(self, rank: int, world: int, handles: Sequence[bytes]) -> None:
+        """Maps the other ranks' pools; `handles[k]` is rank k's peer_handle()."""
+        blob = b"".join(bytes(h) for h in handles)
+        if len(blob) != 64 * world:
+            raise ValueError("need one 64-byte handle per rank")
+        buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        check(lib.aicf_b200_plan_open_peers(self._h, int(rank), int(world), buf), "plan_open_peers")
 
     # ---- execution (names follow PlannedExecutor) --------------------------------------------------
     def run(self, stream: int = 0) -> None:

@@ -135,6 +135,13 @@ class Dist:
         self.td.broadcast_object_list(box, src=0)
         return box[0]
 
+    def allgather(self, obj):
+        if not self.td:
+            return [obj]
+        out = [None] * self.world
+        self.td.all_gather_object(out, obj)
+        return out
+
     def max_float(self, v: float) -> float:
         if not self.td:
             return v
@@ -264,7 +271,7 @@ def run_mlp(args, dist: Dist):
     gbatch = SMALL_MLP_BATCH if args.small else MLP_GLOBAL_BATCH
     batch = gbatch // world
     aicf_cuda._lib.check(lib.aicf_b200_set_device(local_rank), "set_device")
-    if world > 1:
+    if world > 1 and args.dp_mode == "nccl":
         from aicf_cuda import dp
         # NCCL prints its version banner on stdout at communicator creation; stdout carries the one JSON line only,
         # so file descriptor 1 points at stderr while the communicator comes up.
@@ -278,7 +285,9 @@ def run_mlp(args, dist: Dist):
             os.dup2(saved, 1)
             os.close(saved)
 
-    dbl, plan, vals, low = build_mlp(aicf_cuda, dims, batch, gbatch, dp=world > 1)
+    dbl, plan, vals, low = build_mlp(aicf_cuda, dims, batch, gbatch, dp=(args.dp_mode if world > 1 else False))
+    if world > 1 and args.dp_mode == "fused":
+        dbl.connect(rank, world, dist.allgather)
     init_mlp_params(aicf_cuda, plan, dims, seed=4)
 
     # host inputs in pinned memory: rank r owns rows [r*batch, (r+1)*batch) of the global batch
@@ -353,6 +362,8 @@ def run_mlp(args, dist: Dist):
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "dp_captured_mlp" + ("_small" if args.small else ""), "layers": dims, "global_batch": gbatch,
                        "per_gpu_batch": batch, "optimizer": "adam", "loss": "softmax_ce", "parallelism": f"dp{world}",
+                       "gradient_exchange": ("none" if world == 1 else "dp_adam_step over NVLink peer memory" if args.dp_mode == "fused"
+                                             else "NCCL all-reduce"),
                        "l2": "working set (>10 GB per step) far exceeds the 126 MB L2; no flush needed"},
             "clocks": clocks.summary(),
             "e2e": {"value": gbatch / (e2e_ms / e2e_steps * 1e-3), "unit": "samples/s",
@@ -537,6 +548,8 @@ def main():
     ap.add_argument("--reduce-kind", default="sum")
     ap.add_argument("--transb", action="store_true")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed NumPy baseline")
+    ap.add_argument("--dp-mode", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: gradient exchange fused with Adam over peer memory, or NCCL all-reduce + Adam")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 

@@ -34,7 +34,9 @@ enum class OpKind : int {
   Cast = 23,        // dtype conversion (f32 <-> bf16/f16)
   GemmReluBwd = 24, // dX = (Y > 0) ? dY * op(W) : 0  (the ReLU backward mask applied in the GEMM epilogue)
 
-  _Count = 25,
+  DpAdamStep = 25,  // data-parallel Adam fused with its gradient exchange over peer memory
+
+  _Count = 26,
   // Number of kinds the reference defines; ids below this resolve exactly as there.
   _ReferenceCount = 18
 };
@@ -68,6 +70,7 @@ inline const char* op_kind_name(OpKind k) {
     case OpKind::AllReduce: return "all_reduce";
     case OpKind::Cast: return "cast";
     case OpKind::GemmReluBwd: return "gemm_relu_bwd";
+    case OpKind::DpAdamStep: return "dp_adam_step";
     default: return "unknown";
   }
 }

@@ -95,7 +95,8 @@ int aicf_b200_num_op_kinds(void);
  * device. No counterpart in the reference (its kernels have no device-side waits). */
 int aicf_b200_gemm_status(int clear);
 /* All device-side bounded waits of this library in one word: low 16 bits = the GEMM code above, bit 16 =
- * a row copy of the softmax / softmax-CE prefetch pipeline did not arrive within its budget. 0 = healthy.
+ * a row copy of the softmax / softmax-CE prefetch pipeline did not arrive within its budget, bits 17-18 = a
+ * cross-GPU wait of dp_adam_step expired (1 waiting for gradients, 2 waiting for completion). 0 = healthy.
  * Synchronises the device. No counterpart in the reference. */
 int aicf_b200_wait_status(int clear);
 /* Tuning aid of the tcgen05 GEMM: reads the 16-slot timeline that CTA 0 of the last GEMM wrote (globaltimer ns:
@@ -199,6 +200,14 @@ int aicf_b200_plan_add_op(aicf_plan* plan, const char* op_name, const char* kern
 int aicf_b200_plan_alias(aicf_plan* plan, int vid, int target_vid);
 /* Binds a value to caller-owned device memory (must outlive the plan and stay at that address). */
 int aicf_b200_plan_bind(aicf_plan* plan, int vid, void* device_ptr);
+/* Data-parallel exchange over peer memory (dp_adam_step ops; no counterpart in the reference). Values marked
+ * peer-visible before finalize (gradients, broadcast working copies, biases) are placed in one pool allocation
+ * per plan. After finalize every rank exports its pool as a 64-byte IPC handle (all zero when the plan has no
+ * pool), the handles are exchanged by the caller, and open_peers maps the other ranks' pools
+ * (handles = world x 64 bytes in rank order; the own entry is ignored). One process per GPU. */
+int aicf_b200_plan_set_peer_visible(aicf_plan* plan, int vid);
+int aicf_b200_plan_peer_handle(aicf_plan* plan, void* handle64, size_t* pool_bytes);
+int aicf_b200_plan_open_peers(aicf_plan* plan, int rank, int world, const void* handles);
 /* Allocates the arena and every unbound value, resolves variants. No ops may be added afterwards. */
 int aicf_b200_plan_finalize(aicf_plan* plan);
 void* aicf_b200_plan_value_ptr(aicf_plan* plan, int vid);

@@ -97,6 +97,16 @@ def run_lowered(lowered: Sequence[Dict[str, Any]], env: Dict[int, np.ndarray], d
             store(o[2], v)
             if len(o) > 3:
                 store(o[3], p)  # low-precision working copy of the new parameter
+        elif op == "dp_adam_step":  # gradient summed over the ranks, then Adam; every rank ends with the same result
+            g = world_grads(it["inputs"][1], i[1]) if world_grads else i[1]
+            p, m, v = O.adam_step_fused(i[0], g, i[2], i[3], int(np.ravel(i[4])[0]), lr=a.get("lr", 1e-3),
+                                        beta1=a.get("beta1", 0.9), beta2=a.get("beta2", 0.999), eps=a.get("eps", 1e-8),
+                                        weight_decay=a.get("weight_decay", 0.0), decoupled=a.get("decoupled", False), dt=dt)
+            store(o[0], p)
+            store(o[1], m)
+            store(o[2], v)
+            if len(o) > 3:
+                store(o[3], p)
         elif op == "all_reduce":
             store(o[0], world_grads(it["inputs"][0], i[0]) if world_grads else i[0])
         else:

@@ -11,7 +11,7 @@ for p in (REPO, REPO / "ai-compiler-framework_b200" / "python"):
 
 
 def main():
-    rank, world, port, out_dir, dtype = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4], sys.argv[5]
+    rank, world, port, out_dir, dtype, mode = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4], sys.argv[5], sys.argv[6]
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=port, RANK=str(rank), WORLD_SIZE=str(world))
     import torch.distributed as td
     import aicf_cuda
@@ -20,10 +20,13 @@ def main():
     dims, gbatch, steps = [256, 512, 384, 64], 1024, 3
     td.init_process_group("gloo", rank=rank, world_size=world)
     aicf_cuda._lib.check(aicf_cuda.lib.aicf_b200_set_device(rank), "set_device")
-    dp.init_from_torch_distributed()
+    if mode != "fused":
+        dp.init_from_torch_distributed()
     lo, hi = dp.shard_rows(gbatch, rank, world)
-    vals, low = build_mlp_train_step(hi - lo, dims, compute_dtype=dtype, global_batch=gbatch, data_parallel=True)
+    vals, low = build_mlp_train_step(hi - lo, dims, compute_dtype=dtype, global_batch=gbatch, data_parallel=mode)
     plan = Plan(f"dp_rank{rank}", vals, low)
+    if mode == "fused":
+        dp.connect_plans_torch([plan])
     params = oracle.mlp_params(dims, seed=4)
     x, y = oracle.mlp_batch(gbatch, dims[0], dims[-1], seed=4)
     for v in vals:
@@ -41,7 +44,7 @@ def main():
     plan.sync()
     np.savez(Path(out_dir) / f"rank{rank}.npz", W0=plan.tensor("0.W").numpy(), W4=plan.tensor("4.W").numpy(),
              b4=plan.tensor("4.b").numpy(), dW0=plan.tensor("d_0.W").numpy(), loss=plan.tensor("loss").numpy(),
-             step=plan.tensor("opt.step").numpy(), status=np.array([_C.gemm_status()]), **first)
+             step=plan.tensor("opt.step").numpy(), status=np.array([_C.wait_status()]), **first)
     plan.close()
     td.barrier()
     dp.finalize()

@@ -42,7 +42,7 @@ def test_op_names_follow_the_reference_binding():
     import aicf_cuda
     want = ["add", "relu", "gemm", "bias_add", "reduce_sum", "mse_grad", "relu_bwd", "sgd_step", "copy", "grad_zero",
             "adam_step", "step_inc", "bias_corr", "layernorm_fwd", "layernorm_bwd", "batchnorm_fwd", "batchnorm_bwd",
-            "gemm_epilogue", "softmax", "softmax_ce", "reduce_max", "reduce_mean", "all_reduce", "cast", "gemm_relu_bwd"]
+            "gemm_epilogue", "softmax", "softmax_ce", "reduce_max", "reduce_mean", "all_reduce", "cast", "gemm_relu_bwd", "dp_adam_step"]
     got = [aicf_cuda.lib.aicf_b200_op_name(i).decode() for i in range(len(want))]
     assert got == want
     assert aicf_cuda.lib.aicf_b200_op_name(99).decode() == "unknown"

@@ -37,7 +37,7 @@ def _env_for(vals, params, x, y):
 DIMS, GLOBAL_BATCH, STEPS = [32, 48, 10], 64, 3
 
 
-def _worker(rank: int, world: int, port: int, out_dir: str):
+def _worker(rank: int, world: int, port: int, out_dir: str, mode):
     for p in (REPO, REPO / "ai-compiler-framework_b200" / "python"):
         sys.path.insert(0, str(p))
     import torch
@@ -48,7 +48,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     td.init_process_group("gloo", rank=rank, world_size=world)
     lo, hi = shard_rows(GLOBAL_BATCH, rank, world)
-    vals, low = build_mlp_train_step(hi - lo, DIMS, compute_dtype="f32", global_batch=GLOBAL_BATCH, data_parallel=True)
+    vals, low = build_mlp_train_step(hi - lo, DIMS, compute_dtype="f32", global_batch=GLOBAL_BATCH, data_parallel=mode)
     x, y = oracle.mlp_batch(GLOBAL_BATCH, DIMS[0], DIMS[-1], seed=4)
     env, dtypes = _env_for(vals, oracle.mlp_params(DIMS, seed=4), x[lo:hi], y[lo:hi])
 
@@ -64,12 +64,13 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
     td.destroy_process_group()
 
 
-def test_two_gloo_ranks_reproduce_the_single_process_step(tmp_path):
+@pytest.mark.parametrize("mode", ["nccl", "fused"])
+def test_two_gloo_ranks_reproduce_the_single_process_step(tmp_path, mode):
     import torch.multiprocessing as mp
     import oracle
     from aicf_cuda import build_mlp_train_step
     port = _free_port()
-    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, str(tmp_path), mode), nprocs=2, join=True)
     vals, low = build_mlp_train_step(GLOBAL_BATCH, DIMS, compute_dtype="f32")
     x, y = oracle.mlp_batch(GLOBAL_BATCH, DIMS[0], DIMS[-1], seed=4)
     env, dtypes = _env_for(vals, oracle.mlp_params(DIMS, seed=4), x, y)
@@ -104,6 +105,18 @@ def test_sharding_rule_and_lowering_shape():
             producer = max(j for j, o in enumerate(low[:i]) if g in o["outputs"] and o["op"] != "all_reduce")
             consumer = min(j for j, o in enumerate(low) if o["op"] == "adam_step" and g in o["inputs"])
             assert producer < i < consumer
+    fv, fl = build_mlp_train_step(8192, [8192] * 5 + [1000], compute_dtype="bf16", global_batch=65536, data_parallel="fused")
+    fnames = [it["op"] for it in fl]
+    assert fnames.count("dp_adam_step") == 10 and "all_reduce" not in fnames and "adam_step" not in fnames
+    assert fnames.index("step_inc") < fnames.index("gemm_epilogue"), "the step counter moves before the interleaved updates"
+    for i, it in enumerate(fl):  # a layer's exchange starts only after that layer's dX: peers may then overwrite its weights
+        if it["op"] == "dp_adam_step" and len(it["outputs"]) == 4:
+            lp = it["outputs"][3]
+            readers = [j for j, o in enumerate(fl) if lp in o["inputs"] and o["op"] != "dp_adam_step"]
+            assert max(readers) < i
+    assert sorted(it["attrs"]["slot"] for it in fl if it["op"] == "dp_adam_step") == list(range(10))
+    peer = {v.name for v in fv if v.peer_visible}
+    assert {"0.W.lp", "0.b", "d_0.W", "d_0.b"} <= peer and "0.W" not in peer and "x" not in peer
     ce = next(it for it in low if it["op"] == "softmax_ce")
     assert ce["attrs"]["scale"] == 1.0 / 65536
     params = sum(int(np.prod(v.shape)) for v in vals if v.role == 1)

@@ -22,16 +22,40 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
+def shard_bounds(n, rank, world):
+    """Element range of a flat tensor owned by `rank` in the fused exchange (4-element packets, contiguous)."""
+    packets = (n + 3) // 4
+    return min(n, (packets * rank // world) * 4), min(n, (packets * (rank + 1) // world) * 4)
+
+
+def assemble(parts):
+    """Master tensor from the per-rank copies of the fused mode: every rank contributes its own shard."""
+    out = np.empty_like(parts[0]).reshape(-1)
+    for r, a in enumerate(parts):
+        lo, hi = shard_bounds(out.size, r, len(parts))
+        out[lo:hi] = a.reshape(-1)[lo:hi]
+    return out.reshape(parts[0].shape)
+
+
+@pytest.mark.parametrize("mode", ["nccl", "fused"])
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
-def test_two_rank_captured_step(gpu, tmp_path, dtype):
+def test_two_rank_captured_step(gpu, tmp_path, dtype, mode):
     if aicf_cuda.lib.aicf_b200_device_count() < 2:
         pytest.skip("needs 2 GPUs")
     port = str(_free_port())
-    procs = [subprocess.Popen([sys.executable, str(HERE / "dp_worker.py"), str(r), "2", port, str(tmp_path), dtype])
+    procs = [subprocess.Popen([sys.executable, str(HERE / "dp_worker.py"), str(r), "2", port, str(tmp_path), dtype, mode])
              for r in range(2)]
     for p in procs:
         assert p.wait(timeout=300) == 0
-    r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
+    r0, r1 = dict(np.load(tmp_path / "rank0.npz")), dict(np.load(tmp_path / "rank1.npz"))
+    if mode == "fused":
+        # biases are replicated; matrix masters are sharded (each rank is current inside its own shard); the
+        # gradient buffers hold each rank's LOCAL gradient, the oracle's is their sum
+        assert np.array_equal(r0["b4"], r1["b4"]), "b4: replicas diverged"
+        for k in ("W0", "W4", "W0_step1"):
+            r0[k] = r1[k] = assemble([r0[k], r1[k]])
+        for k in ("dW0", "dW0_step1"):
+            r0[k] = r1[k] = r0[k] + r1[k]
     for k in ("W0", "W4", "b4", "dW0"):
         assert np.array_equal(r0[k], r1[k]), f"{k}: replicas diverged"
     assert int(r0["step"][0]) == 3 and int(r0["status"][0]) == 0 and int(r1["status"][0]) == 0

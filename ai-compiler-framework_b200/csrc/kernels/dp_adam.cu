@@ -153,14 +153,20 @@ __global__ void __launch_bounds__(256) dp_adam_kernel(const DpAdamArgs a) {
     // shard bounds are multiples of 4 except possibly the very end of the tensor
     const int64_t p_begin = a.begin >> 2, p_end = a.end >> 2;
     for (int64_t i = p_begin + tid; i < p_end; i += stride) {
-      float4 acc = __ldcg(reinterpret_cast<const float4*>(a.g_of[0]) + i);
-      for (int k = 1; k < a.world; ++k) {  // fixed rank order: the same bits whoever owns the shard
-        const float4 gk = __ldcg(reinterpret_cast<const float4*>(a.g_of[k]) + i);
-        acc.x += gk.x;
-        acc.y += gk.y;
-        acc.z += gk.z;
-        acc.w += gk.w;
-      }
+      // all ranks' packets are requested before any is used: up to 8 independent NVLink loads in flight per thread
+      float4 gk[kMaxRanks];
+#pragma unroll
+      for (int k = 0; k < kMaxRanks; ++k)
+        if (k < a.world) gk[k] = __ldcg(reinterpret_cast<const float4*>(a.g_of[k]) + i);
+      float4 acc = gk[0];
+#pragma unroll
+      for (int k = 1; k < kMaxRanks; ++k)  // fixed rank order: the same bits whoever owns the shard
+        if (k < a.world) {
+          acc.x += gk[k].x;
+          acc.y += gk[k].y;
+          acc.z += gk[k].z;
+          acc.w += gk[k].w;
+        }
       const V4 p = ld_stream(reinterpret_cast<const V4*>(a.p) + i);
       const V4 m = ld_stream(reinterpret_cast<const V4*>(a.m) + i);
       const V4 v = ld_stream(reinterpret_cast<const V4*>(a.v) + i);
@@ -285,7 +291,19 @@ Status dp_adam_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, con
   const int64_t packets = (n + 3) / 4;
   a.begin = std::min<int64_t>(n, (packets * a.rank / a.world) * 4);
   a.end = std::min<int64_t>(n, (packets * (a.rank + 1) / a.world) * 4);
-  const int grid = streaming_grid((a.end - a.begin) / 4 + 1, 256, 2);
+  // One CTA per SM at most: 256 threads x 80 registers fit beside a persistent GEMM CTA (192 x 136), two would not,
+  // and a GEMM launched while this kernel is resident must still find room on every SM.
+  const int grid = streaming_grid((a.end - a.begin) / 4 + 1, 256, 1);
+  // The SM's L1/shared split is one setting for all resident CTAs. The GEMMs run with the largest shared-memory
+  // split; asking for the same split here lets these CTAs and GEMM CTAs join each other's SMs in either order
+  // (with the default split, a GEMM CTA would have to wait for the SM to drain first).
+  static bool carveout_set = false;
+  if (!carveout_set) {
+    cudaFuncSetAttribute(dp_adam_kernel<1>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(dp_adam_kernel<2>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(dp_adam_kernel<3>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    carveout_set = true;
+  }
   cudaGetLastError();
   switch (bcast_kind) {
     case 1: dp_adam_kernel<1><<<grid, 256, 0, stream>>>(a); break;

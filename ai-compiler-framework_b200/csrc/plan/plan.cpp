@@ -10,6 +10,7 @@
 // first later op touching that gradient waits for them, so the exchange overlaps the rest of the
 // backward pass both in eager runs and inside the captured graph.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <string>
@@ -206,7 +207,9 @@ size_t assign_arena(std::vector<Value*>& vals, int num_ops, std::map<int, size_t
 int enqueue_all(aicf_plan* p, cudaStream_t main, std::vector<cudaEvent_t>* marks = nullptr) {
   // vid -> event a later op on `main` must wait for (pending all_reduce on the comm stream)
   std::map<int, cudaEvent_t> pending;
-  const bool overlap = (aicf_b200_dp_world_size() > 1 || p->peer_world > 1) && !marks;
+  // AICF_PLAN_NO_OVERLAP=1 keeps the exchange on the main stream (to measure what the side stream buys)
+  static const bool no_overlap = std::getenv("AICF_PLAN_NO_OVERLAP") != nullptr;
+  const bool overlap = (aicf_b200_dp_world_size() > 1 || p->peer_world > 1) && !marks && !no_overlap;
   for (size_t i = 0; i < p->ops.size(); ++i) {
     Op& op = p->ops[i];
     if (marks)

@@ -312,6 +312,7 @@ def run_mlp(args, dist: Dist):
         plan.replay(args.steps)
         ms = ev.stop_ms(stream)
         plan.sync()
+    ms_fastest = -dist.max_float(-ms)
     ms = dist.max_float(ms)
     dist.barrier()
     loss_after = float(loss_dev.numpy()[0])
@@ -376,7 +377,7 @@ def run_mlp(args, dist: Dist):
                          "kernel": "gemm_tcgen05_kernel", "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
                          "note": "algorithmic GEMM FLOPs of one step / summed GEMM op times of one eager step"},
             "phase_ms": {k: round(v, 4) for k, v in sorted(by_kid.items(), key=lambda kv: -kv[1])},
-            "loss": loss_after, "gemm_status": status,
+            "loss": loss_after, "gemm_status": status, "ms_per_step_fastest_rank": ms_fastest / args.steps,
         }
         if world == 1 and not args.no_cpu:
             sample = 128

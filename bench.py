@@ -559,10 +559,9 @@ def main():
         rank = dist_env()[0]
         if rank != 0:
             return  # only rank 0 measures the host baseline; the others have nothing to do
-        class _Solo:  # no process group is needed for a host-only measurement
-            rank, world = 0, max(world, args.gpus)
-            def barrier(self): pass
-        out = run_mlp_reference(args, _Solo())
+        import types  # no process group is needed for a host-only measurement
+        solo = types.SimpleNamespace(rank=0, world=max(world, args.gpus), barrier=lambda: None)
+        out = run_mlp_reference(args, solo)
         print(json.dumps(out), flush=True)
         return
 

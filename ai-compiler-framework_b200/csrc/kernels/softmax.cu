@@ -18,17 +18,23 @@ namespace {
 
 constexpr int kMaxWarps = 32;
 
-// Block-wide max / sum. Every thread returns the same value; partials are folded in warp order.
+// Block-wide max / sum. Every thread returns the same value. Warp partials go through shared memory and are
+// folded by the first warp with a fixed shuffle tree (a 1024-thread block would otherwise spend more time on
+// every thread re-reading 32 partials than on the row itself).
 template <bool kIsMax>
-__device__ __forceinline__ float block_reduce(float v, float* smem /*[kMaxWarps]*/) {
+__device__ __forceinline__ float block_reduce(float v, float* smem /*[kMaxWarps + 1]*/) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   v = kIsMax ? warp_max(v) : warp_sum(v);
   __syncthreads();  // smem may still be read by the previous reduction
   if (lane == 0) smem[warp] = v;
   __syncthreads();
-  float r = smem[0];
-  for (int w = 1; w < nwarps; ++w) r = kIsMax ? fmaxf(r, smem[w]) : r + smem[w];
-  return r;
+  if (warp == 0) {
+    float r = lane < nwarps ? smem[lane] : (kIsMax ? -INFINITY : 0.0f);
+    r = kIsMax ? warp_max(r) : warp_sum(r);
+    if (lane == 0) smem[kMaxWarps] = r;
+  }
+  __syncthreads();
+  return smem[kMaxWarps];
 }
 
 // exp for arguments <= 0: one multiply and one MUFU.EX2. Relative error <= |x| * 2^-24 + 2^-22, i.e. below
@@ -44,8 +50,7 @@ __device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {  // larger value 
   if (b.v > a.v || (b.v == a.v && b.idx < a.idx)) return b;
   return a;
 }
-__device__ __forceinline__ ArgMax block_argmax(ArgMax a, float* sv, int* si) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+__device__ __forceinline__ ArgMax warp_argmax(ArgMax a) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     ArgMax b;
@@ -53,15 +58,27 @@ __device__ __forceinline__ ArgMax block_argmax(ArgMax a, float* sv, int* si) {
     b.idx = __shfl_xor_sync(0xffffffffu, a.idx, o);
     a = better(a, b);
   }
+  return a;
+}
+__device__ __forceinline__ ArgMax block_argmax(ArgMax a, float* sv /*[kMaxWarps + 1]*/, int* si /*[kMaxWarps + 1]*/) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  a = warp_argmax(a);
   __syncthreads();
   if (lane == 0) {
     sv[warp] = a.v;
     si[warp] = a.idx;
   }
   __syncthreads();
-  ArgMax r{sv[0], si[0]};
-  for (int w = 1; w < nwarps; ++w) r = better(r, ArgMax{sv[w], si[w]});
-  return r;
+  if (warp == 0) {
+    ArgMax r{lane < nwarps ? sv[lane] : -INFINITY, lane < nwarps ? si[lane] : 0x7fffffff};
+    r = warp_argmax(r);
+    if (lane == 0) {
+      sv[kMaxWarps] = r.v;
+      si[kMaxWarps] = r.idx;
+    }
+  }
+  __syncthreads();
+  return ArgMax{sv[kMaxWarps], si[kMaxWarps]};
 }
 
 // ------------------------------------------------------------------ row pipeline plumbing
@@ -105,7 +122,7 @@ __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict_
   using PK = Pack16<T>;
   constexpr int kN = PK::kN;
   extern __shared__ __align__(16) uint8_t row_smem[];
-  __shared__ float red[kMaxWarps];
+  __shared__ float red[kMaxWarps + 1];
   const int64_t np = N / kN;  // N % kN == 0 on this path
   const uint32_t row_bytes = static_cast<uint32_t>(N * sizeof(T));
   RowPipe pipe;
@@ -167,7 +184,7 @@ __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict_
 template <typename T>
 __global__ void __launch_bounds__(256) softmax_multipass_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M,
                                                                int64_t N) {
-  __shared__ float red[kMaxWarps];
+  __shared__ float red[kMaxWarps + 1];
   for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
     const T* xr = x + row * N;
     T* yr = y + row * N;
@@ -301,8 +318,8 @@ __global__ void __launch_bounds__(1024)
   using PK = Pack16<T>;
   constexpr int kN = PK::kN;
   extern __shared__ __align__(16) uint8_t row_smem[];
-  __shared__ float red[kMaxWarps];
-  __shared__ int redi[kMaxWarps];
+  __shared__ float red[kMaxWarps + 1];
+  __shared__ int redi[kMaxWarps + 1];
   const int64_t np = C / kN;
   const uint32_t row_bytes = static_cast<uint32_t>(C * sizeof(T));
   RowPipe pipe;
@@ -382,8 +399,8 @@ __global__ void __launch_bounds__(256)
     softmax_ce_multipass_kernel(const T* __restrict__ z, const int32_t* __restrict__ labels, T* __restrict__ dz,
                                 float* __restrict__ loss_row, int32_t* __restrict__ argmax_out, int64_t B, int64_t C,
                                 float scale) {
-  __shared__ float red[kMaxWarps];
-  __shared__ int redi[kMaxWarps];
+  __shared__ float red[kMaxWarps + 1];
+  __shared__ int redi[kMaxWarps + 1];
   for (int64_t row = blockIdx.x; row < B; row += gridDim.x) {
     const T* zr = z + row * C;
     T* dr = dz + row * C;

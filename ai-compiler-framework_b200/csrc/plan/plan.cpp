@@ -410,6 +410,22 @@ int aicf_b200_plan_open_peers(aicf_plan* p, int rank, int world, const void* han
   return AICF_OK;
 }
 
+int aicf_b200_plan_open_peers_raw(aicf_plan* p, int rank, int world, void* const* bases) {
+  if (!p || !p->finalized) return fail(Status::InvalidArgument, "plan_open_peers_raw: plan not finalized");
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || !bases) return fail(Status::InvalidArgument, "plan_open_peers_raw: bad arguments");
+  if (!p->peer_pool) return AICF_OK;
+  if (p->peers_open) return fail(Status::InvalidArgument, "plan_open_peers_raw: already open");
+  std::vector<void*> b(bases, bases + world);
+  b[static_cast<size_t>(rank)] = p->peer_pool;
+  for (void* q : b)
+    if (!q) return fail(Status::InvalidArgument, "plan_open_peers_raw: null pool address");
+  if (!aicf::cuda::dp_register_pool(p->peer_pool, p->peer_pool_bytes, b.data(), rank, world))
+    return fail(Status::Internal, "plan_open_peers_raw: pool registration failed");
+  p->peers_open = true;
+  p->peer_world = world;
+  return AICF_OK;
+}
+
 int aicf_b200_plan_finalize(aicf_plan* p) {
   if (!p || p->finalized) return fail(Status::InvalidArgument, "plan_finalize: plan missing or already finalized");
   KernelRegistry::ensure_registered();
@@ -564,6 +580,7 @@ size_t aicf_b200_plan_value_bytes(aicf_plan* p, int vid) {
   Value* v = p ? p->find(vid) : nullptr;
   return v ? v->bytes : 0;
 }
+size_t aicf_b200_plan_peer_pool_bytes(aicf_plan* p) { return p ? p->peer_pool_bytes : 0; }
 size_t aicf_b200_plan_arena_bytes(aicf_plan* p) { return p ? p->arena_bytes : 0; }
 size_t aicf_b200_plan_arena_bytes_no_reuse(aicf_plan* p) { return p ? p->no_reuse_bytes : 0; }
 int aicf_b200_plan_num_ops(aicf_plan* p) { return p ? static_cast<int>(p->ops.size()) : 0; }

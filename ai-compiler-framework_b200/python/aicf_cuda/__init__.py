@@ -8,9 +8,9 @@ from ._lib import LIB_PATH, lib
 from .lowering import build_mlp_train_step
 from .pipeline import DoubleBufferedStep
 from .plan import (ROLE_INPUT, ROLE_PARAM, ROLE_STATIC, Plan, ValueSpec, classify_role, needs_zero_init, pack_attrs,
-                   pack_attrs_like_reference_executor)
+                   pack_attrs_like_reference_executor, plan_from_json, plan_to_json)
 from .tensor import Tensor, bf16_bits_to_f32, f32_to_bf16_bits
 
 __all__ = ["_C", "lib", "LIB_PATH", "Plan", "ValueSpec", "Tensor", "DoubleBufferedStep", "build_mlp_train_step", "pack_attrs",
-           "pack_attrs_like_reference_executor", "classify_role", "needs_zero_init", "f32_to_bf16_bits",
+           "pack_attrs_like_reference_executor", "plan_to_json", "plan_from_json", "classify_role", "needs_zero_init", "f32_to_bf16_bits",
            "bf16_bits_to_f32", "ROLE_INPUT", "ROLE_PARAM", "ROLE_STATIC"]

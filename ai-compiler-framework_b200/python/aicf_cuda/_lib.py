@@ -107,6 +107,8 @@ PROTOTYPES = {
     "aicf_b200_plan_set_peer_visible": (_i, [_vp, _i]),
     "aicf_b200_plan_peer_handle": (_i, [_vp, _vp, _P(_sz)]),
     "aicf_b200_plan_open_peers": (_i, [_vp, _i, _i, _vp]),
+    "aicf_b200_plan_open_peers_raw": (_i, [_vp, _i, _i, _P(_vp)]),
+    "aicf_b200_plan_peer_pool_bytes": (_sz, [_vp]),
     "aicf_b200_plan_finalize": (_i, [_vp]),
     "aicf_b200_plan_value_ptr": (_vp, [_vp, _i]),
     "aicf_b200_plan_value_bytes": (_sz, [_vp, _i]),

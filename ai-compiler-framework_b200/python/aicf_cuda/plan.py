@@ -133,6 +133,33 @@ class ValueSpec:
     peer_visible: bool = False        # mapped by the other data-parallel ranks (gradients, broadcast copies)
 
 
+def plan_to_json(name: str, values: Iterable[ValueSpec], lowered: Sequence[Dict[str, Any]]) -> str:
+    """On-disk form of a compiled plan: the lowered-op list plus the value table, as JSON.
+
+    The lowered part is the reference's own contract ({"op","inputs","outputs","attrs","kernel_id"},
+    python/aicf_fw/core_v2/lower.py:9-21); the value table carries what its text dump prints per value
+    (core_v2/printer.py:115-147: id, name, role, shape, dtype) plus this backend's placement flags."""
+    import json
+    vals = [{"vid": v.vid, "name": v.name, "shape": list(v.shape), "dtype": v.dtype,
+             "role": classify_role(v.name) if v.role is None else v.role, "persistent": bool(v.persistent),
+             "zero_init": needs_zero_init(v.name) if v.zero_init is None else bool(v.zero_init),
+             "alias_of": v.alias_of, "peer_visible": bool(v.peer_visible)} for v in values]
+    ops = [{"op": it["op"], "inputs": list(it.get("inputs", [])), "outputs": list(it.get("outputs", [])),
+            "attrs": dict(it.get("attrs") or {}), **({"kernel_id": it["kernel_id"]} if it.get("kernel_id") else {})}
+           for it in lowered]
+    return json.dumps({"format": "aicf_b200.plan/1", "name": name, "values": vals, "lowered": ops}, indent=1)
+
+
+def plan_from_json(text: str) -> Tuple[str, List[ValueSpec], List[Dict[str, Any]]]:
+    import json
+    d = json.loads(text)
+    if d.get("format") != "aicf_b200.plan/1":
+        raise ValueError(f"not a plan file: format={d.get('format')!r}")
+    vals = [ValueSpec(v["vid"], v["name"], tuple(v["shape"]), v["dtype"], v["role"], v["persistent"], v["zero_init"],
+                      v.get("alias_of"), v.get("peer_visible", False)) for v in d["values"]]
+    return d["name"], vals, d["lowered"]
+
+
 class Plan:
     """A finalized execution plan. Buffers are pointer-stable for the plan's lifetime."""
 
@@ -190,6 +217,25 @@ class Plan:
         t._base = self
         return t
 
+    def state_names(self) -> List[str]:
+        """Values that carry training state across steps: parameters, optimizer state, working copies."""
+        out = []
+        for v in self.values.values():
+            role = classify_role(v.name) if v.role is None else v.role
+            if v.alias_of is None and (role == ROLE_PARAM or v.name.startswith("opt.") or v.name.endswith(".lp")):
+                out.append(v.name)
+        return out
+
+    def state_dict(self) -> Dict[str, Any]:
+        """Host copies of the training state (numpy arrays; bf16 as uint16 bit patterns), e.g. for np.savez."""
+        return {n: self.tensor(n).numpy() for n in self.state_names()}
+
+    def load_state_dict(self, state: Dict[str, Any]) -> None:
+        for n in self.state_names():
+            if n not in state:
+                raise KeyError(f"state is missing {n!r}")
+            self.tensor(n).copy_from_host(state[n])
+
     @property
     def arena_bytes(self) -> int:
         return int(lib.aicf_b200_plan_arena_bytes(self._h))
@@ -220,6 +266,15 @@ class Plan:
             raise ValueError("need one 64-byte handle per rank")
         buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
         check(lib.aicf_b200_plan_open_peers(self._h, int(rank), int(world), buf), "plan_open_peers")
+
+    @property
+    def peer_pool_bytes(self) -> int:
+        return int(lib.aicf_b200_plan_peer_pool_bytes(self._h))
+
+    def open_peers_raw(self, rank: int, world: int, bases: Sequence[int]) -> None:
+        """Like open_peers, from device addresses of the other ranks' pools (bases[rank] is ignored)."""
+        arr = (C.c_void_p * world)(*[C.c_void_p(int(b)) for b in bases])
+        check(lib.aicf_b200_plan_open_peers_raw(self._h, int(rank), int(world), arr), "plan_open_peers_raw")
 
     # ---- execution (names follow PlannedExecutor) --------------------------------------------------
     def run(self, stream: int = 0) -> None:

@@ -208,6 +208,11 @@ int aicf_b200_plan_bind(aicf_plan* plan, int vid, void* device_ptr);
 int aicf_b200_plan_set_peer_visible(aicf_plan* plan, int vid);
 int aicf_b200_plan_peer_handle(aicf_plan* plan, void* handle64, size_t* pool_bytes);
 int aicf_b200_plan_open_peers(aicf_plan* plan, int rank, int world, const void* handles);
+/* Same, for callers that already hold device addresses of the other ranks' pools (one process driving several
+ * GPUs with peer access enabled, or a test that stands a silent buffer in for a rank that never arrives).
+ * bases[k] = address of rank k's pool as seen from this device; bases[rank] is ignored. */
+int aicf_b200_plan_open_peers_raw(aicf_plan* plan, int rank, int world, void* const* bases);
+size_t aicf_b200_plan_peer_pool_bytes(aicf_plan* plan);
 /* Allocates the arena and every unbound value, resolves variants. No ops may be added afterwards. */
 int aicf_b200_plan_finalize(aicf_plan* plan);
 void* aicf_b200_plan_value_ptr(aicf_plan* plan, int vid);

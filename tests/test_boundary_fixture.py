@@ -80,6 +80,23 @@ def test_attr_packing_matches_both_contracts():
     assert pack_attrs_like_reference_executor("sgd_step", {"lr": 0.01}) == (0, b"")
 
 
+def test_plan_json_round_trip_keeps_the_lowered_contract():
+    from aicf_cuda import build_mlp_train_step, plan_from_json, plan_to_json
+    vals, low = build_mlp_train_step(64, [784, 256, 10], compute_dtype="bf16", data_parallel="fused", weight_decay=0.01)
+    text = plan_to_json("mlp", vals, low)
+    name, vals2, low2 = plan_from_json(text)
+    assert name == "mlp" and plan_to_json(name, vals2, low2) == text
+    assert [(v.vid, v.name, v.shape, v.dtype, v.peer_visible) for v in vals2] == [(v.vid, v.name, v.shape, v.dtype, v.peer_visible) for v in vals]
+    assert [it["op"] for it in low2] == [it["op"] for it in low] and low2[2]["kernel_id"] == low[2]["kernel_id"]
+    assert [pack_attrs(it["op"], it["attrs"]) for it in low2] == [pack_attrs(it["op"], it["attrs"]) for it in low]
+    # the reference's own lowered list (fixture) survives the same trip
+    fvals = [ValueSpec(v["vid"], v["name"], tuple(v["shape"]), _TORCH_DT[v["dtype"]]) for v in FIX["values"]]
+    _, _, flow = plan_from_json(plan_to_json("fixture", fvals, FIX["lowered"]))
+    assert flow == FIX["lowered"]
+    with pytest.raises(ValueError):
+        plan_from_json('{"format": "something else"}')
+
+
 _TORCH_DT = {"float16": "f16", "float32": "f32", "int32": "i32"}
 
 

@@ -158,6 +158,33 @@ def test_double_buffered_pipeline_equals_sequential_steps(gpu):
     seq.close()
 
 
+def test_state_dict_resumes_training_bit_for_bit(gpu, tmp_path):
+    """Checkpoint after 3 steps, restore into a fresh plan built from the JSON form, continue: same bits as 6 straight steps."""
+    from aicf_cuda import plan_from_json, plan_to_json
+    a, vals, low, *_ = make_plan(64, [784, 256, 10], "bf16", seed=0)
+    a.capture()
+    a.replay(3)
+    a.sync()
+    np.savez(tmp_path / "ckpt.npz", **a.state_dict())
+    (tmp_path / "plan.json").write_text(plan_to_json("mlp", vals, low))
+    a.replay(3)
+    a.sync()
+    name, vals2, low2 = plan_from_json((tmp_path / "plan.json").read_text())
+    b = Plan(name, vals2, low2)
+    b.load_state_dict(dict(np.load(tmp_path / "ckpt.npz")))
+    x, y = oracle.mlp_batch(64, 784, 10, 0)
+    b.tensor("x").copy_from_host(x)
+    b.tensor("labels").copy_from_host(y)
+    b.capture()
+    b.replay(3)
+    b.sync()
+    assert sorted(a.state_names()) == sorted(b.state_names()) and "opt.step" in a.state_names()
+    for n in a.state_names():
+        assert np.array_equal(a.tensor(n).numpy(), b.tensor(n).numpy()), n
+    a.close()
+    b.close()
+
+
 def test_arena_reuses_dead_buffers(gpu):
     vals, low = build_mlp_train_step(1024, [512, 512, 512, 512, 64], compute_dtype="bf16")
     plan = Plan("arena", vals, low)

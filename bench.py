@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the op backend + captured-plan hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload mlp|gemm|gemm_f32|softmax|ce|reduce|adam]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload mlp|mlp_c1|gemm|gemm_f32|softmax|ce|reduce|adam]
                     [--impl reference] [--small]
 
 Default workload `mlp`: the data-parallel captured MLP train step (4x Linear(8192->8192)+ReLU ->
@@ -412,6 +412,59 @@ def run_mlp_reference(args, dist: Dist):
             "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
+def run_mlp_c1(args):
+    """BASELINE config 1: fp32 MLP 784->256->10, batch 64, captured replay (launch/latency-bound; reports us/step)."""
+    import aicf_cuda
+    import oracle
+    from aicf_cuda import Plan, _C, build_mlp_train_step
+    dims, batch = [784, 256, 10], 64
+    vals, low = build_mlp_train_step(batch, dims, compute_dtype="f32", **ADAM)
+    plan = Plan("mlp_c1", vals, low)
+    for name, w in oracle.mlp_params(dims, seed=0).items():
+        plan.tensor(name).copy_from_host(w)
+    x, y = oracle.mlp_batch(batch, dims[0], dims[-1], seed=0)
+    plan.tensor("x").copy_from_host(x)
+    plan.tensor("labels").copy_from_host(y)
+    plan.capture()
+    ev = Events(aicf_cuda.lib)
+    reps = 200
+    plan.replay(max(3, args.warmup) * 10)
+    plan.sync()
+    times = []
+    with ClockSampler(0) as clocks:
+        for _ in range(args.steps):
+            ev.start(plan.stream)
+            plan.replay(reps)
+            times.append(ev.stop_ms(plan.stream) / reps)
+    ms = statistics.mean(times)
+    t0 = time.perf_counter()
+    env, dtypes = {}, {}
+    params = oracle.mlp_params(dims, seed=0)
+    for v in vals:
+        dtypes[v.vid] = v.dtype
+        env[v.vid] = x if v.name == "x" else y if v.name == "labels" else params[v.name].copy() if v.name in params else \
+            np.zeros(v.shape, np.int32 if v.dtype == "i32" else np.float32)
+    cpu_steps = 50
+    t0 = time.perf_counter()
+    for _ in range(cpu_steps):
+        oracle.run_lowered(low, env, dtypes, np.float32)
+    cpu_s = (time.perf_counter() - t0) / cpu_steps
+    flops = mlp_flops_per_sample(dims) * batch
+    out = {"metric": "small MLP train-step samples/s (captured graph replay)", "value": batch / (ms * 1e-3), "unit": "samples/s",
+           "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "us_per_step": ms * 1e3,
+           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+           "config": {"workload": "mlp_784_256_10_batch64", "kernels_per_step": plan.graph_kernel_nodes,
+                      "l2": "3.3 MB working set: L2-resident by nature (latency-bound configuration)"},
+           "clocks": clocks.summary(), "gpu_launches": plan.graph_kernel_nodes * reps * args.steps,
+           "roofline": {"bound": "latency", "achieved": flops / (ms * 1e-3) / 1e12, "peak": None, "unit": "TFLOP/s", "frac": None,
+                        "traffic": None, "note": f"{plan.graph_kernel_nodes} dependent kernels per step; time is launch + drain latency"},
+           "cpu_baseline": {"value": batch / cpu_s, "unit": "samples/s", "cores": blas_threads(), "kind": "port",
+                            "sample": f"{cpu_steps} NumPy fp32 steps of the same lowered graph (full configuration)"},
+           "loss": float(plan.tensor("loss").numpy()[0]), "gemm_status": _C.wait_status()}
+    plan.close()
+    return out
+
+
 # ------------------------------------------------------------------------------------------ single-kernel workloads
 def run_kernel_workload(args):
     """GEMM TFLOP/s and softmax / CE / reduce / Adam GB/s on BASELINE's shapes (1 GPU)."""
@@ -565,6 +618,9 @@ def main():
         print(json.dumps(out), flush=True)
         return
 
+    if args.workload == "mlp_c1":
+        print(json.dumps(run_mlp_c1(args)), flush=True)
+        return
     if args.workload != "mlp":
         print(json.dumps(run_kernel_workload(args)), flush=True)
         return

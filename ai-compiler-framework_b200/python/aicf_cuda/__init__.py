@@ -1,9 +1,10 @@
 """aicf_cuda: B200 (sm_100a) op backend and captured-plan hot path behind the reference's interfaces.
 
 `aicf_cuda._C` is the drop-in binding module; `aicf_cuda.Plan` is the C++ captured plan;
-`aicf_cuda.Tensor` is a NumPy-only device buffer for callers that do not use torch.
+`aicf_cuda.Tensor` is a NumPy-only device buffer for callers that do not use torch;
+`aicf_cuda.core_v2` is the tracing front end with the reference's names (also importable as `aicf_fw.core_v2`).
 """
-from . import _C
+from . import _C, core_v2
 from ._lib import LIB_PATH, lib
 from .lowering import build_mlp_train_step
 from .pipeline import DoubleBufferedStep
@@ -11,6 +12,6 @@ from .plan import (ROLE_INPUT, ROLE_PARAM, ROLE_STATIC, Plan, ValueSpec, classif
                    pack_attrs_like_reference_executor, plan_from_json, plan_to_json)
 from .tensor import Tensor, bf16_bits_to_f32, f32_to_bf16_bits
 
-__all__ = ["_C", "lib", "LIB_PATH", "Plan", "ValueSpec", "Tensor", "DoubleBufferedStep", "build_mlp_train_step", "pack_attrs",
+__all__ = ["_C", "core_v2", "lib", "LIB_PATH", "Plan", "ValueSpec", "Tensor", "DoubleBufferedStep", "build_mlp_train_step", "pack_attrs",
            "pack_attrs_like_reference_executor", "plan_to_json", "plan_from_json", "classify_role", "needs_zero_init", "f32_to_bf16_bits",
            "bf16_bits_to_f32", "ROLE_INPUT", "ROLE_PARAM", "ROLE_STATIC"]

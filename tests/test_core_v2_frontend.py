@@ -299,3 +299,66 @@ def test_reference_import_paths_resolve_to_this_front_end():
     assert set(pkg.__all__) >= {"trace_ir", "dump_ir", "dump_lowered", "dump_plan", "lower_to_backend_ops", "build_binding_plan",
                                 "BindingPlan", "PlanOptions", "SymTensor", "sym_tensor", "linear", "relu", "mse_grad",
                                 "PlannedExecutor", "ExecOptions"}
+
+
+# ---- compile_train_step -----------------------------------------------------------------------------------
+def test_compile_train_step_graph_shape():
+    """Host-side part: the traced and lowered step (no device needed until the first run)."""
+    from aicf_cuda.train_step import same_name_is_same_storage
+    ir = cv.IRGraph("alias")
+    a = ir.new_value(name="opt.step", shape=(), dtype="i32")
+    b = ir.new_value(name="opt.step", shape=(), dtype="i32")
+    c = ir.new_value(name="x", shape=(2,), dtype="f32")
+    d = ir.new_value(name="x", shape=(2,), dtype="f32")
+    low = [{"op": "step_inc", "inputs": [a.id], "outputs": [b.id], "attrs": {}},
+           {"op": "copy", "inputs": [c.id], "outputs": [d.id], "attrs": {}}]
+    out = same_name_is_same_storage(ir, low)
+    assert out[0]["inputs"] == out[0]["outputs"] == [a.id]               # optimizer state: one buffer per name
+    assert out[1]["inputs"] == [c.id] and out[1]["outputs"] == [d.id]     # other names are left alone
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("optimizer,dtype", [("adam", "f32"), ("sgd", "f16"), ("sgd", "f32")])
+def test_compile_train_step_matches_the_oracle_eager_and_replayed(gpu, optimizer, dtype):
+    import oracle
+    from aicf_cuda.train_step import compile_train_step
+    dims, Bn, steps = [24, 32, 16, 8], 48, 4
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((Bn, dims[0])).astype(np.float32)
+    t = rng.standard_normal((Bn, dims[-1])).astype(np.float32)
+    init = {}
+    for i in range(len(dims) - 1):
+        init[f"{2 * i}.W"] = (rng.standard_normal((dims[i + 1], dims[i])) * 0.2).astype(np.float32)
+        init[f"{2 * i}.b"] = (rng.standard_normal((dims[i + 1],)) * 0.1).astype(np.float32)
+    kw = dict(B=Bn, dtype=dtype, optimizer=optimizer, lr=0.01, loss_scale=2.0 / (Bn * dims[-1]), params=init)
+
+    eager = compile_train_step(dims, **kw)
+    for _ in range(steps):
+        eager.train_step({"x": x, "t": t})
+    eager.sync()
+    graphed = compile_train_step(dims, **kw)
+    graphed.capture({"x": x, "t": t})
+    graphed.replay(steps, sync=True)
+    graphed.sync()
+
+    # oracle: the same lowered list interpreted on the host
+    ir, lowered = eager.ir, eager.lowered
+    rnd = (lambda a: a.astype(np.float16).astype(np.float32)) if dtype == "f16" else (lambda a: a)
+    dts = {vid: cv.short_dtype(v.dtype) for vid, v in ir.values.items()}
+    env = {vid: np.zeros(v.shape, np.int32 if dts[vid] == "i32" else np.float32) for vid, v in ir.values.items()}
+    by_name = {v.name: vid for vid, v in sorted(ir.values.items(), reverse=True)}
+    for nm, a in {**init, "x": x, "t": t}.items():
+        env[by_name[nm]] = rnd(a.copy())
+    f32 = lambda it: dict(it, attrs={k: (float(np.float32(v)) if isinstance(v, float) else v) for k, v in it["attrs"].items()})
+    for _ in range(steps):
+        oracle.run_lowered([f32(it) for it in lowered], env, dts, np.float64)
+    tol = dict(rtol=2e-2, atol=2e-3) if dtype == "f16" else dict(rtol=2e-4, atol=2e-5)
+    for nm in init:
+        want = env[by_name[nm]]
+        bad = ~np.isclose(eager.params[nm].float_numpy(), want, **tol)
+        # Adam divides by sqrt(v): where a gradient is within rounding of zero the fp32 and fp64 updates differ by up
+        # to lr, so a small fraction of elements may sit outside the tolerance; SGD must match everywhere.
+        assert bad.mean() <= (0.01 if optimizer == "adam" else 0.0), f"eager {nm}: {bad.sum()} of {bad.size} differ"
+        np.testing.assert_array_equal(graphed.params[nm].numpy(), eager.params[nm].numpy(), err_msg=f"replay {nm}")
+    if optimizer == "adam":
+        assert int(eager.value("opt.step").numpy()) == steps == int(graphed.value("opt.step").numpy())

@@ -12,6 +12,7 @@
 namespace aicf::cuda {
 int gemm_tcgen05_status(bool clear);
 int row_pipeline_status(bool clear);
+int layernorm_pipeline_status(bool clear);
 int gemm_tcgen05_timeline(int enable, unsigned long long* out16);
 int dp_wait_status(bool clear);
 }
@@ -239,9 +240,11 @@ int aicf_b200_gemm_timeline(int enable, uint64_t* out16) {
 }
 int aicf_b200_wait_status(int clear) {
   const int g = aicf::cuda::gemm_tcgen05_status(clear != 0);
-  const int r = aicf::cuda::row_pipeline_status(clear != 0);
+  const int rs = aicf::cuda::row_pipeline_status(clear != 0);
+  const int rl = aicf::cuda::layernorm_pipeline_status(clear != 0);
   const int d = aicf::cuda::dp_wait_status(clear != 0);
-  if (g < 0 || r < 0 || d < 0) return -1;
+  if (g < 0 || rs < 0 || rl < 0 || d < 0) return -1;
+  const int r = rs | rl;
   return (g & 0xFFFF) | (r ? 0x10000 : 0) | ((d & 3) << 17);
 }
 

@@ -3,8 +3,8 @@
 // The 30 kernel ids of the reference's MLP path (register_all.cpp:105-263 there) resolve to sm_100a
 // kernels with the same contracts and the same relative priorities, so lowered plans pinned to
 // those ids run unchanged. The *_vec2 / *_half2 ids are aliases of the one vectorised kernel per
-// dtype (it picks 16-byte or scalar accesses itself). layernorm / batchnorm ids are not registered:
-// by-id dispatch answers NotImplemented for them.
+// dtype (it picks 16-byte or scalar accesses itself). batchnorm ids are not registered: by-id dispatch
+// answers NotImplemented for them.
 #include "aicf/backends/cuda/registry/register_all.hpp"
 
 #include <cstdio>
@@ -60,6 +60,12 @@ KernelVariant make_reduce_mean_lastaxis_f32_variant();
 KernelVariant make_reduce_mean_lastaxis_bf16_variant();
 KernelVariant make_reduce_mean_lastaxis_f16_variant();
 // softmax.cu
+KernelVariant make_layernorm_fwd_f32_variant();
+KernelVariant make_layernorm_fwd_f16_variant();
+KernelVariant make_layernorm_fwd_bf16_variant();
+KernelVariant make_layernorm_bwd_f32_variant();
+KernelVariant make_layernorm_bwd_f16_variant();
+KernelVariant make_layernorm_bwd_bf16_variant();
 KernelVariant make_softmax_lastdim_f32_variant();
 KernelVariant make_softmax_lastdim_bf16_variant();
 KernelVariant make_softmax_lastdim_f16_variant();
@@ -133,6 +139,10 @@ extern "C" void aicf_cuda_register_all_kernels() {
       {K::AdamStep, make_adam_step_f32_variant, 0, "adam_step_f32_v0"},
       {K::StepInc, make_step_inc_variant, 0, "step_inc_v0"},
       {K::BiasCorr, make_biascorr_variant, 0, "bias_corr_v0"},
+      {K::LayerNormFwd, make_layernorm_fwd_f16_variant, 10, "layernorm_fwd_f16_v0"},
+      {K::LayerNormFwd, make_layernorm_fwd_f32_variant, 0, "layernorm_fwd_f32_v0"},
+      {K::LayerNormBwd, make_layernorm_bwd_f16_variant, 10, "layernorm_bwd_f16_v0"},
+      {K::LayerNormBwd, make_layernorm_bwd_f32_variant, 0, "layernorm_bwd_f32_v0"},
 
       // ---- additions: bf16 everywhere, fp32-output contractions, new ops ----
       {K::ReduceSum, make_reduce_sum_lastdim_bf16_variant, 95, "reduce_sum_keep_lastdim_bf16_v0"},
@@ -159,6 +169,8 @@ extern "C" void aicf_cuda_register_all_kernels() {
       {K::MseGrad, make_mse_grad_bf16_variant, 15, "mse_grad_bf16_v0"},
       {K::ReluBwd, make_relu_bwd_bf16_variant, 25, "relu_bwd_bf16_v0"},
       {K::SgdStep, make_sgd_step_bf16_variant, 25, "sgd_step_bf16_v0"},
+      {K::LayerNormFwd, make_layernorm_fwd_bf16_variant, 15, "layernorm_fwd_bf16_v0"},
+      {K::LayerNormBwd, make_layernorm_bwd_bf16_variant, 15, "layernorm_bwd_bf16_v0"},
       {K::Copy, make_copy_bf16_variant, 15, "copy_bf16_v0"},
       {K::Copy, make_copy_i32_variant, 10, "copy_i32_v0"},
       {K::AdamStep, make_adam_step_f32_fused_variant, -10, "adam_step_f32_fused_v1"},

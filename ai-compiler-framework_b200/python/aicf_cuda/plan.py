@@ -28,6 +28,8 @@ SCHEMA_SGD = 0x53444753
 SCHEMA_BIAS_ADD = 0x44444142
 SCHEMA_MSE_GRAD = 0x4745534D
 SCHEMA_SOFTMAX_CE = 0x45434D53
+SCHEMA_LAYERNORM = 0x50454E4C  # 'LNEP'
+
 SCHEMA_ALL_REDUCE = 0x44455241
 SCHEMA_DP_ADAM = 0x44415044
 # What the reference's Python executor sends for gemm_epilogue (exec.py:215-217); the reference's C++
@@ -78,6 +80,8 @@ def pack_attrs(op: str, attrs: Optional[Dict[str, Any]]) -> Tuple[int, bytes]:
         return SCHEMA_BIAS_ADD, struct.pack("<q", int(a["axis"]))
     if op == "softmax_ce" and "scale" in a:
         return SCHEMA_SOFTMAX_CE, struct.pack("<f", float(a["scale"]))
+    if op == "layernorm_fwd" and "eps" in a:
+        return SCHEMA_LAYERNORM, struct.pack("<f", float(a["eps"]))
     if op == "all_reduce":
         return SCHEMA_ALL_REDUCE, struct.pack("<i", int(a.get("bucket", 0)))
     return 0, b""

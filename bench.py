@@ -537,6 +537,27 @@ def run_kernel_workload(args):
         work, unit, bound, peak = 2.0 * M * N * X.nbytes / X.numel, "GB/s", "hbm", peaks["hbm_gbs"]
         metric = f"row softmax {dt} HBM GB/s"
         cfg = {"workload": f"softmax_{dt}", "rows": M, "cols": N, "l2": "read+write bytes exceed L2"}
+    elif w in ("ln_fwd", "ln_bwd"):
+        M, N = (4096, 4096) if small else (32768, 4096)
+        dt = args.dtype
+        esz = 4 if dt == "f32" else 2
+        X = dev_normal((M, N), dt, 2.0, 2)
+        Gm, Bt = dev_normal((N,), dt, 1.0, 3), dev_normal((N,), dt, 0.1, 4)
+        Y, Mu, Rs = Tensor.empty((M, N), dt), Tensor.empty((M,), "f32"), Tensor.empty((M,), "f32")
+        fwd = lambda st: _C.launch_by_id(f"layernorm_fwd_{dt}_v0", OpKind.LayerNormFwd, [X, Gm, Bt], [Y, Mu, Rs], 0, b"", st)
+        if w == "ln_fwd":
+            fn = fwd
+            work = 2.0 * M * N * esz + 8.0 * M + 2.0 * N * esz
+        else:
+            fwd(0)
+            _C.device_sync()
+            dY = dev_normal((M, N), dt, 1.0, 5)
+            dX, dG, dB = Tensor.empty((M, N), dt), Tensor.empty((N,), "f32"), Tensor.empty((N,), "f32")
+            fn = lambda st: _C.launch_by_id(f"layernorm_bwd_{dt}_v0", OpKind.LayerNormBwd, [X, dY, Gm, Mu, Rs], [dX, dG, dB], 0, b"", st)
+            work = 3.0 * M * N * esz + 8.0 * M + N * esz + 8.0 * N
+        unit, bound, peak = "GB/s", "hbm", peaks["hbm_gbs"]
+        metric = f"layer norm {'forward' if w == 'ln_fwd' else 'backward (dx, dgamma, dbeta)'} {dt} HBM GB/s"
+        cfg = {"workload": f"layernorm_{w[3:]}_{dt}", "rows": M, "cols": N, "l2": "read+write bytes exceed L2"}
     elif w == "reduce":
         M, N = (4096, 4096) if small else (32768, 4096)
         dt = args.dtype

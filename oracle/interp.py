@@ -75,6 +75,15 @@ def run_lowered(lowered: Sequence[Dict[str, Any]], env: Dict[int, np.ndarray], d
             store(o[1], loss)
             if len(o) > 2:
                 store(o[2], am)
+        elif op == "layernorm_fwd":
+            y, mu, rs = O.layernorm_fwd(i[0], i[1] if len(i) == 3 else None, i[2] if len(i) == 3 else None, a.get("eps", 1e-5), dt)
+            store(o[0], y), store(o[1], mu), store(o[2], rs)
+        elif op == "layernorm_bwd":
+            aff = len(i) == 5
+            dx, dg, db = O.layernorm_bwd(i[0], i[1], i[2] if aff else None, i[3 if aff else 2], i[4 if aff else 3], dt)
+            store(o[0], dx)
+            if aff:
+                store(o[1], dg), store(o[2], db)
         elif op == "step_inc":
             store(o[0], O.step_inc(env[o[0]]))
         elif op == "bias_corr":

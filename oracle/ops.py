@@ -7,7 +7,7 @@ import numpy as np
 
 __all__ = ["bf16_round", "f16_round", "gemm", "gemm_epilogue", "gemm_relu_bwd", "bias_add", "relu", "relu_bwd", "copy", "grad_zero",
            "mse_grad", "reduce_sum_columns", "reduce_lastaxis", "adam_step_v0", "adam_step_fused", "step_inc",
-           "bias_corr", "sgd_step", "add", "softmax", "softmax_ce", "cast"]
+           "bias_corr", "sgd_step", "add", "softmax", "softmax_ce", "cast", "layernorm_fwd", "layernorm_bwd"]
 
 
 def bf16_round(x: np.ndarray) -> np.ndarray:
@@ -175,3 +175,37 @@ def softmax_ce(logits, labels, scale=None, dt=np.float64):
     rows = np.nonzero(ok)[0]
     d[rows, lab[rows]] -= s
     return d, loss, z.argmax(axis=1).astype(np.int32)
+
+
+def layernorm_fwd(X, gamma=None, beta=None, eps=1e-5, dt=np.float64):
+    """(y, mean, rstd) over the last axis of X[M, N]: mean = sum(x)/N, var = max(sum(x^2)/N - mean^2, 0),
+    rstd = 1/sqrt(var + eps), y = (x - mean) * rstd [* gamma + beta]; eps defaults to 1e-5
+    (ops/layernorm/launcher.cu:128-170 forward kernel, :49-56 and :456 eps)."""
+    x = np.asarray(X, dt)
+    n = x.shape[-1]
+    mu = x.sum(axis=-1) / dt(n)
+    var = np.maximum((x * x).sum(axis=-1) / dt(n) - mu * mu, dt(0))
+    rs = dt(1) / np.sqrt(var + dt(eps))
+    y = (x - mu[..., None]) * rs[..., None]
+    if gamma is not None:
+        y = y * np.asarray(gamma, dt) + np.asarray(beta, dt)
+    return y, mu, rs
+
+
+def layernorm_bwd(X, dY, gamma, mean, rstd, dt=np.float64):
+    """(dx, dgamma, dbeta); gamma=None is the non-affine form and returns (dx, None, None).
+    xhat = (x - mean) * rstd, g = dy [* gamma], dx = (N*g - sum(g) - xhat * sum(g * xhat)) * rstd / N
+    (ops/layernorm/launcher.cu:221-262); dgamma = sum over rows of dy * xhat, dbeta = sum over rows of dy
+    (:309-340)."""
+    x, dy = np.asarray(X, dt), np.asarray(dY, dt)
+    n = x.shape[-1]
+    mu, rs = np.asarray(mean, dt)[..., None], np.asarray(rstd, dt)[..., None]
+    xhat = (x - mu) * rs
+    g = dy if gamma is None else dy * np.asarray(gamma, dt)
+    s1 = g.sum(axis=-1, keepdims=True)
+    s2 = (g * xhat).sum(axis=-1, keepdims=True)
+    dx = (dt(n) * g - s1 - xhat * s2) * (rs / dt(n))
+    if gamma is None:
+        return dx, None, None
+    lead = tuple(range(x.ndim - 1))
+    return dx, (dy * xhat).sum(axis=lead), dy.sum(axis=lead)

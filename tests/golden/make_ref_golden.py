@@ -82,6 +82,30 @@ def main(out_path: Path) -> None:
         o = run("bias_corr_v0", OpKind.BiasCorr, [Tensor.from_numpy(np.array(t, np.int32))], (), 0x524F4342,
                 struct.pack("<ff", 0.9, 0.999), n_out=2)
         g[f"bias_corr_{t}"] = np.array([o[0].ravel()[0], o[1].ravel()[0]], np.float32)
+    # layer norm (drawn after everything above so that the earlier inputs keep their values)
+    def run_multi(kid, kind, ins, out_specs, schema=0, payload=b""):
+        outs = [Tensor.zeros(s, d) for s, d in out_specs]
+        st = ref_by_id(ref, kid, kind, ins, outs, schema, payload)
+        assert st == 0, (kid, st)
+        return [o.numpy() for o in outs]
+
+    LM, LN = 37, 96
+    lx = (rng.standard_normal((LM, LN)) * 2.0 + 0.5).astype(np.float32)
+    ldy = rng.standard_normal((LM, LN)).astype(np.float32)
+    lg = (1.0 + 0.1 * rng.standard_normal(LN)).astype(np.float32)
+    lb = (0.1 * rng.standard_normal(LN)).astype(np.float32)
+    g.update(ln_x=lx, ln_dy=ldy, ln_gamma=lg, ln_beta=lb)
+    LX, LDY, LG, LB = (Tensor.from_numpy(a) for a in (lx, ldy, lg, lb))
+    fwd_specs = [((LM, LN), "f32"), ((LM,), "f32"), ((LM,), "f32")]
+    lnep = struct.pack("<f", 1e-5)
+    y, mu, rs = run_multi("layernorm_fwd_f32_v0", OpKind.LayerNormFwd, [LX, LG, LB], fwd_specs, 0x50454E4C, lnep)
+    g.update(ln_y_affine=y, ln_mean=mu, ln_rstd=rs)
+    g["ln_y_plain"] = run_multi("layernorm_fwd_f32_v0", OpKind.LayerNormFwd, [LX], fwd_specs, 0x50454E4C, lnep)[0]
+    MU, RS = Tensor.from_numpy(mu), Tensor.from_numpy(rs)
+    dx, dg, db = run_multi("layernorm_bwd_f32_v0", OpKind.LayerNormBwd, [LX, LDY, LG, MU, RS],
+                           [((LM, LN), "f32"), ((LN,), "f32"), ((LN,), "f32")])
+    g.update(ln_dx_affine=dx, ln_dgamma=dg, ln_dbeta=db)
+    g["ln_dx_plain"] = run_multi("layernorm_bwd_f32_v0", OpKind.LayerNormBwd, [LX, LDY, MU, RS], [((LM, LN), "f32")])[0]
     out_path.parent.mkdir(parents=True, exist_ok=True)
     np.savez_compressed(out_path, **g)
     print(f"wrote {out_path} ({out_path.stat().st_size >> 10} KiB, {len(g)} arrays)")

@@ -63,7 +63,7 @@ def test_null_pointer_calls_fail_cleanly_without_a_device():
     assert lib.aicf_b200_launch_by_id(None, 2, None, 0, None, 0, None, 0) == 1
     assert lib.aicf_b200_launch_by_id(b"no_such_kernel_v0", 2, None, 0, None, 0, None, 0) == 2
     assert "kernel_id=no_such_kernel_v0" in lib.aicf_b200_last_error().decode()
-    assert lib.aicf_b200_launch_by_id(b"layernorm_fwd_f32_v0", 13, None, 0, None, 0, None, 0) == 2
+    assert lib.aicf_b200_launch_by_id(b"batchnorm_fwd_f16_v0", 15, None, 0, None, 0, None, 0) == 2   # not registered
     assert lib.aicf_b200_op_call(99, None, 0, None, 0, None, 0) == 1
     assert lib.aicf_b200_graph_end() == 1
     assert lib.aicf_b200_last_error().decode() == "graph_end called but not capturing"

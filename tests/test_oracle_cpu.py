@@ -191,3 +191,14 @@ def test_oracle_against_reference_cuda_golden_vectors():
     for t in (1, 10):
         b1, b2 = oracle.bias_corr(t, f(0.9), f(0.999))
         assert np.allclose([b1, b2], g[f"bias_corr_{t}"], rtol=1e-4)  # the reference's fp32 powf: 1-0.999^t cancels
+    # layer norm (mean offset 0.5, std 2: the reference's one-pass variance loses ~1e-7 relative here)
+    assert "ln_x" in g.files, "regenerate tests/golden/ref_cuda_golden.npz with tests/golden/make_ref_golden.py"
+    lx, ldy, lg, lb = g["ln_x"], g["ln_dy"], g["ln_gamma"], g["ln_beta"]
+    yy, mu, rs = oracle.layernorm_fwd(lx, lg, lb, f(1e-5))
+    assert np.allclose(mu, g["ln_mean"], rtol=1e-5, atol=1e-6) and np.allclose(rs, g["ln_rstd"], rtol=1e-5)
+    assert np.allclose(yy, g["ln_y_affine"], rtol=1e-5, atol=1e-5)
+    assert np.allclose(oracle.layernorm_fwd(lx, None, None, f(1e-5))[0], g["ln_y_plain"], rtol=1e-5, atol=1e-5)
+    dx, dg, db = oracle.layernorm_bwd(lx, ldy, lg, g["ln_mean"], g["ln_rstd"])
+    assert np.allclose(dx, g["ln_dx_affine"], rtol=1e-5, atol=1e-5)
+    assert np.allclose(dg, g["ln_dgamma"], rtol=1e-5, atol=1e-5) and np.allclose(db, g["ln_dbeta"], rtol=1e-5, atol=1e-5)
+    assert np.allclose(oracle.layernorm_bwd(lx, ldy, None, g["ln_mean"], g["ln_rstd"])[0], g["ln_dx_plain"], rtol=1e-5, atol=1e-5)

@@ -74,17 +74,18 @@ __global__ void __launch_bounds__(1024)
   using PK = Pack16<T>;
   constexpr int kN = PK::kN;
   extern __shared__ __align__(16) uint8_t row_smem[];
-  __shared__ float red[kMaxWarps + 1];
+  __shared__ float red[2][kMaxWarps + 1];
+  __shared__ int wait_failed;
   const int64_t np = N / kN;
   const uint32_t row_bytes = static_cast<uint32_t>(N * sizeof(T));
   const float inv_n = 1.0f / static_cast<float>(N);
   RowPipe pipe;
-  pipe.init(row_smem, row_bytes);
+  pipe.init(row_smem, row_bytes, &wait_failed);
   int64_t row = blockIdx.x;
   if (row < M && threadIdx.x == 0) pipe.fetch(x + row * N, row_bytes);
   const PK* srow = reinterpret_cast<const PK*>(row_smem);
   for (; row < M; row += gridDim.x) {
-    if (!pipe.arrived(&g_ln_pipeline_status)) break;
+    pipe.wait_row(&wait_failed);
     float f[kPackets][kN];
     float s = 0.0f;
 #pragma unroll
@@ -102,8 +103,13 @@ __global__ void __launch_bounds__(1024)
         for (int e = 0; e < kN; ++e) f[q][e] = 0.0f;
       }
     }
-    // The reduction starts with a barrier: after it the whole row is in registers and the buffer is free.
-    s = block_reduce<false>(s, red);
+    // Past the reduction's barriers the whole row is in registers everywhere and the buffer is free; a wait that
+    // ran out is seen by all threads here.
+    s = block_reduce_2b<false>(s, red[0]);
+    if (wait_failed) {
+      if (threadIdx.x == 0) atomicExch(&g_ln_pipeline_status, 1);
+      break;
+    }
     if (threadIdx.x == 0 && row + gridDim.x < M) {
       sm100::fence_generic_to_async_smem();
       pipe.fetch(x + (row + gridDim.x) * N, row_bytes);
@@ -121,7 +127,7 @@ __global__ void __launch_bounds__(1024)
         }
       }
     }
-    d2 = block_reduce<false>(d2, red);
+    d2 = block_reduce_2b<false>(d2, red[1]);
     const float rs = rsqrtf(d2 * inv_n + eps);
     if (threadIdx.x == 0) {
       mean[row] = mu;

@@ -27,6 +27,25 @@ __device__ __forceinline__ float block_reduce(float v, float* smem /*[kMaxWarps 
   return smem[kMaxWarps];
 }
 
+// The same reduction with two barriers instead of three: nothing guards `area` against the previous call, so
+// consecutive calls in a block must alternate between two areas (a thread still reading the total of call i is then
+// never overtaken by the partial writes of call i + 1, and call i + 2 is two barriers later). Everything a thread did
+// before the call (its shared-memory reads of the current row in particular) is ordered before the first barrier.
+template <bool kIsMax>
+__device__ __forceinline__ float block_reduce_2b(float v, float* area /*[kMaxWarps + 1]*/) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  v = kIsMax ? warp_max(v) : warp_sum(v);
+  if (lane == 0) area[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float r = lane < nwarps ? area[lane] : (kIsMax ? -INFINITY : 0.0f);
+    r = kIsMax ? warp_max(r) : warp_sum(r);
+    if (lane == 0) area[kMaxWarps] = r;
+  }
+  __syncthreads();
+  return area[kMaxWarps];
+}
+
 // ------------------------------------------------------------------ row pipeline plumbing
 constexpr unsigned long long kRowWaitBudgetNs = 1000000000ull;  // a row copy that takes 1 s is lost
 
@@ -34,13 +53,14 @@ constexpr unsigned long long kRowWaitBudgetNs = 1000000000ull;  // a row copy th
 struct RowPipe {
   uint32_t buf, bar;
   uint32_t phase;
-  __device__ __forceinline__ void init(uint8_t* smem, uint32_t row_bytes) {
+  __device__ __forceinline__ void init(uint8_t* smem, uint32_t row_bytes, int* failed_flag) {
     buf = sm100::smem_addr(smem);
     bar = buf + row_bytes;
     phase = 0;
     if (threadIdx.x == 0) {
       sm100::mbar_init(bar, 1);
       sm100::mbar_init_fence();
+      *failed_flag = 0;
     }
     __syncthreads();
   }
@@ -48,7 +68,7 @@ struct RowPipe {
     sm100::mbar_expect_tx(bar, row_bytes);
     sm100::bulk_copy_g2s(buf, row, row_bytes, bar);
   }
-  // Block-uniform: false when any thread's wait expired (the block then stops); *status_word is then set to 1.
+  // Block-uniform wait with a barrier of its own: false when any thread's wait expired (the block then stops).
   __device__ __forceinline__ bool arrived(int* status_word) {
     const bool ok = sm100::mbar_wait_bounded(bar, phase, kRowWaitBudgetNs);
     phase ^= 1u;
@@ -57,6 +77,13 @@ struct RowPipe {
       return false;
     }
     return true;
+  }
+  // Waits for the row without a barrier. A wait that runs out sets *failed_flag (shared memory, zeroed before the
+  // loop); the caller tests the flag after the next block-wide barrier, where every thread sees the same value, and
+  // leaves the loop there. Until then the threads work on whatever the buffer holds, which is harmless.
+  __device__ __forceinline__ void wait_row(int* failed_flag) {
+    if (!sm100::mbar_wait_bounded(bar, phase, kRowWaitBudgetNs)) *failed_flag = 1;
+    phase ^= 1u;
   }
 };
 

@@ -61,6 +61,27 @@ __device__ __forceinline__ ArgMax block_argmax(ArgMax a, float* sv /*[kMaxWarps 
   return ArgMax{sv[kMaxWarps], si[kMaxWarps]};
 }
 
+// Two-barrier form; the same alternation rule as block_reduce_2b applies to (sv, si).
+__device__ __forceinline__ ArgMax block_argmax_2b(ArgMax a, float* sv /*[kMaxWarps + 1]*/, int* si /*[kMaxWarps + 1]*/) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  a = warp_argmax(a);
+  if (lane == 0) {
+    sv[warp] = a.v;
+    si[warp] = a.idx;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    ArgMax r{lane < nwarps ? sv[lane] : -INFINITY, lane < nwarps ? si[lane] : 0x7fffffff};
+    r = warp_argmax(r);
+    if (lane == 0) {
+      sv[kMaxWarps] = r.v;
+      si[kMaxWarps] = r.idx;
+    }
+  }
+  __syncthreads();
+  return ArgMax{sv[kMaxWarps], si[kMaxWarps]};
+}
+
 __device__ int g_row_pipeline_status = 0;  // non-zero: a bounded wait of the row pipeline expired
 
 // ------------------------------------------------------------------ softmax, row in registers
@@ -70,16 +91,17 @@ __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict_
   using PK = Pack16<T>;
   constexpr int kN = PK::kN;
   extern __shared__ __align__(16) uint8_t row_smem[];
-  __shared__ float red[kMaxWarps + 1];
+  __shared__ float red[2][kMaxWarps + 1];
+  __shared__ int wait_failed;
   const int64_t np = N / kN;  // N % kN == 0 on this path
   const uint32_t row_bytes = static_cast<uint32_t>(N * sizeof(T));
   RowPipe pipe;
-  pipe.init(row_smem, row_bytes);
+  pipe.init(row_smem, row_bytes, &wait_failed);
   int64_t row = blockIdx.x;
   if (row < M && threadIdx.x == 0) pipe.fetch(x + row * N, row_bytes);
   const PK* srow = reinterpret_cast<const PK*>(row_smem);
   for (; row < M; row += gridDim.x) {
-    if (!pipe.arrived(&g_row_pipeline_status)) break;
+    pipe.wait_row(&wait_failed);
     PK* yr = reinterpret_cast<PK*>(y + row * N);
     float f[kPackets][kN];
     float mx = -INFINITY;
@@ -98,9 +120,13 @@ __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict_
         for (int e = 0; e < kN; ++e) f[q][e] = -INFINITY;
       }
     }
-    // block_reduce starts with a barrier: after it every thread has copied its part of the row out of
-    // shared memory, so thread 0 may let the next row overwrite the buffer.
-    mx = block_reduce<true>(mx, red);
+    // Past the reduction's barriers every thread has copied its part of the row out of shared memory, so thread 0
+    // may let the next row overwrite the buffer; a wait that ran out is seen by all threads here.
+    mx = block_reduce_2b<true>(mx, red[0]);
+    if (wait_failed) {
+      if (threadIdx.x == 0) atomicExch(&g_row_pipeline_status, 1);
+      break;
+    }
     if (threadIdx.x == 0 && row + gridDim.x < M) {
       sm100::fence_generic_to_async_smem();
       pipe.fetch(x + (row + gridDim.x) * N, row_bytes);
@@ -113,7 +139,7 @@ __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict_
         f[q][e] = fast_exp(f[q][e] - mx);  // exp(-inf) == 0 for the padding
         sum += f[q][e];
       }
-    sum = block_reduce<false>(sum, red);
+    sum = block_reduce_2b<false>(sum, red[1]);
     const float inv = 1.0f / sum;
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
@@ -161,21 +187,16 @@ Status softmax_run(const T* x, T* y, int64_t M, int64_t N, cudaStream_t stream) 
   }
   const int grid = streaming_grid(M, 1, row_pipe_blocks_per_sm(c.threads, smem));
   bool ok_attr = true;
+#define AICF_SM_LAUNCH(PK)                                           \
+  if ((ok_attr = allow_smem(softmax_regs_kernel<T, PK>, smem)))      \
+    softmax_regs_kernel<T, PK><<<grid, c.threads, smem, stream>>>(x, y, M, N)
   switch (c.packets) {
-    case 1:
-      if ((ok_attr = allow_smem(softmax_regs_kernel<T, 1>, smem))) softmax_regs_kernel<T, 1><<<grid, c.threads, smem, stream>>>(x, y, M, N);
-      break;
-    case 2:
-      if ((ok_attr = allow_smem(softmax_regs_kernel<T, 2>, smem))) softmax_regs_kernel<T, 2><<<grid, c.threads, smem, stream>>>(x, y, M, N);
-      break;
-    case 4:
-      if ((ok_attr = allow_smem(softmax_regs_kernel<T, 4>, smem))) softmax_regs_kernel<T, 4><<<grid, c.threads, smem, stream>>>(x, y, M, N);
-      break;
-    default:
-      if ((ok_attr = allow_smem(softmax_regs_kernel<T, kMaxPk>, smem)))
-        softmax_regs_kernel<T, kMaxPk><<<grid, c.threads, smem, stream>>>(x, y, M, N);
-      break;
+    case 1: AICF_SM_LAUNCH(1); break;
+    case 2: AICF_SM_LAUNCH(2); break;
+    case 4: AICF_SM_LAUNCH(4); break;
+    default: AICF_SM_LAUNCH(kMaxPk); break;
   }
+#undef AICF_SM_LAUNCH
   if (!ok_attr) {
     cudaGetLastError();
     return Status::Internal;
@@ -223,7 +244,10 @@ Status softmax_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, con
 // outputs [dlogits (B,C) same dtype, loss_row (B,) f32, argmax (B,) i32]   (argmax optional)
 //   loss_row = logsumexp(z) - z[label];  dlogits = (softmax(z) - onehot(label)) * scale
 // scale: 'SMCE' <f>, default 1/B. A label outside [0,C) contributes no one-hot term and a zero loss.
-template <typename T, int kPackets>
+// kLockstep: the wait for the row ends in a barrier and the reductions keep their leading barrier. With a single
+// 1024-thread block per SM (rows of tens of thousands of fp32 logits) that is measurably faster than the
+// two-barrier form, which wins whenever several blocks share an SM.
+template <typename T, int kPackets, bool kLockstep>
 __global__ void __launch_bounds__(1024)
     softmax_ce_regs_kernel(const T* __restrict__ z, const int32_t* __restrict__ labels, T* __restrict__ dz,
                            float* __restrict__ loss_row, int32_t* __restrict__ argmax_out, int64_t B, int64_t C,
@@ -231,17 +255,22 @@ __global__ void __launch_bounds__(1024)
   using PK = Pack16<T>;
   constexpr int kN = PK::kN;
   extern __shared__ __align__(16) uint8_t row_smem[];
-  __shared__ float red[kMaxWarps + 1];
+  __shared__ float red[2][kMaxWarps + 1];
+  __shared__ int wait_failed;
   __shared__ int redi[kMaxWarps + 1];
   const int64_t np = C / kN;
   const uint32_t row_bytes = static_cast<uint32_t>(C * sizeof(T));
   RowPipe pipe;
-  pipe.init(row_smem, row_bytes);
+  pipe.init(row_smem, row_bytes, &wait_failed);
   int64_t row = blockIdx.x;
   if (row < B && threadIdx.x == 0) pipe.fetch(z + row * C, row_bytes);
   const PK* srow = reinterpret_cast<const PK*>(row_smem);
   for (; row < B; row += gridDim.x) {
-    if (!pipe.arrived(&g_row_pipeline_status)) break;
+    if constexpr (kLockstep) {
+      if (!pipe.arrived(&g_row_pipeline_status)) break;
+    } else {
+      pipe.wait_row(&wait_failed);
+    }
     PK* dr = reinterpret_cast<PK*>(dz + row * C);
     const int label = labels[row];
     const bool label_ok = label >= 0 && label < C;
@@ -268,8 +297,13 @@ __global__ void __launch_bounds__(1024)
         for (int e = 0; e < kN; ++e) f[q][e] = -INFINITY;
       }
     }
-    // the first barrier inside block_argmax is passed only when every thread holds its part of the row
-    am = block_argmax(am, red, redi);
+    // past the barriers of the reduction every thread holds its part of the row (the buffer may be refilled), and a
+    // wait that ran out is seen by all threads
+    am = kLockstep ? block_argmax(am, red[0], redi) : block_argmax_2b(am, red[0], redi);
+    if (wait_failed) {
+      if (threadIdx.x == 0) atomicExch(&g_row_pipeline_status, 1);
+      break;
+    }
     if (threadIdx.x == 0 && row + gridDim.x < B) {
       sm100::fence_generic_to_async_smem();
       pipe.fetch(z + (row + gridDim.x) * C, row_bytes);
@@ -283,7 +317,7 @@ __global__ void __launch_bounds__(1024)
         f[q][e] = fast_exp(f[q][e] - mx);
         sum += f[q][e];
       }
-    sum = block_reduce<false>(sum, red);
+    sum = kLockstep ? block_reduce<false>(sum, red[1]) : block_reduce_2b<false>(sum, red[1]);
     const float k = scale / sum;
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
@@ -387,11 +421,16 @@ Status softmax_ce_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, 
     softmax_ce_multipass_kernel<T><<<streaming_grid(B, 1, 8), 256, 0, stream>>>(z, lab, dz, loss, am, B, C, scale);
     return launch_status();
   }
-  const int grid = streaming_grid(B, 1, row_pipe_blocks_per_sm(c.threads, smem));
   bool ok_attr = true;
-#define AICF_CE_LAUNCH(PK)                                                                            \
-  if ((ok_attr = allow_smem(softmax_ce_regs_kernel<T, PK>, smem)))                                    \
-    softmax_ce_regs_kernel<T, PK><<<grid, c.threads, smem, stream>>>(z, lab, dz, loss, am, B, C, scale)
+  const int per_sm = row_pipe_blocks_per_sm(c.threads, smem);
+  const bool lockstep = per_sm == 1;
+  const int grid = streaming_grid(B, 1, per_sm);
+#define AICF_CE_LAUNCH_M(PK, LS)                                                                          \
+  if ((ok_attr = allow_smem(softmax_ce_regs_kernel<T, PK, LS>, smem)))                                    \
+    softmax_ce_regs_kernel<T, PK, LS><<<grid, c.threads, smem, stream>>>(z, lab, dz, loss, am, B, C, scale)
+#define AICF_CE_LAUNCH(PK)                          \
+  if (lockstep) { AICF_CE_LAUNCH_M(PK, true); }     \
+  else { AICF_CE_LAUNCH_M(PK, false); }
   switch (c.packets) {
     case 1: AICF_CE_LAUNCH(1); break;
     case 2: AICF_CE_LAUNCH(2); break;
@@ -399,6 +438,7 @@ Status softmax_ce_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, 
     default: AICF_CE_LAUNCH(kMaxPk); break;
   }
 #undef AICF_CE_LAUNCH
+#undef AICF_CE_LAUNCH_M
   if (!ok_attr) {
     cudaGetLastError();
     return Status::Internal;

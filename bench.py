@@ -529,6 +529,7 @@ def run_kernel_workload(args):
                "l2": "operands exceed L2 at 8192; smaller sizes are L2-resident by nature"}
     elif w == "softmax":
         M, N = (4096, 4096) if small else (32768, 4096)
+        M, N = args.rows or M, args.cols or N
         dt = args.dtype
         X = dev_normal((M, N), dt, 3.0, 2)
         Y = Tensor.empty((M, N), dt)
@@ -539,6 +540,7 @@ def run_kernel_workload(args):
         cfg = {"workload": f"softmax_{dt}", "rows": M, "cols": N, "l2": "read+write bytes exceed L2"}
     elif w in ("ln_fwd", "ln_bwd"):
         M, N = (4096, 4096) if small else (32768, 4096)
+        M, N = args.rows or M, args.cols or N
         dt = args.dtype
         esz = 4 if dt == "f32" else 2
         X = dev_normal((M, N), dt, 2.0, 2)
@@ -560,6 +562,7 @@ def run_kernel_workload(args):
         cfg = {"workload": f"layernorm_{w[3:]}_{dt}", "rows": M, "cols": N, "l2": "read+write bytes exceed L2"}
     elif w == "reduce":
         M, N = (4096, 4096) if small else (32768, 4096)
+        M, N = args.rows or M, args.cols or N
         dt = args.dtype
         X = dev_normal((M, N), dt, 3.0, 2)
         O = Tensor.empty((M,), "f32")
@@ -572,6 +575,7 @@ def run_kernel_workload(args):
         cfg = {"workload": f"reduce_{args.reduce_kind}_{dt}", "rows": M, "cols": N, "l2": "input exceeds L2"}
     elif w == "ce":
         B, Cn = (1024, 32000) if small else (8192, 32000)
+        B, Cn = args.rows or B, args.cols or Cn
         Z = dev_normal((B, Cn), "f32", 2.0, 3)
         L = Tensor.from_numpy(rng.integers(0, Cn, B, dtype=np.int32))
         D, Lo, Am = Tensor.empty((B, Cn), "f32"), Tensor.empty((B,), "f32"), Tensor.empty((B,), "i32")
@@ -619,6 +623,8 @@ def main():
     ap.add_argument("--workload", default="mlp")
     ap.add_argument("--small", action="store_true", help="reduced shapes (profiler captures)")
     ap.add_argument("--size", type=int, default=0)
+    ap.add_argument("--rows", type=int, default=0, help="row count override for the softmax / ce / reduce / layer-norm workloads")
+    ap.add_argument("--cols", type=int, default=0, help="row width override for the same workloads")
     ap.add_argument("--dtype", default="f32")
     ap.add_argument("--reduce-kind", default="sum")
     ap.add_argument("--transb", action="store_true")

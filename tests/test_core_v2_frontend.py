@@ -195,7 +195,6 @@ def test_executor_runs_the_fixture_model_like_the_reference(gpu):
     ex.trace_enable(True)
     env = ex.run(inputs=inputs, params=params, reuse_static=True)
     ex.sync()
-    ex.trace_enable(False)
     assert ex.trace_get() == FIX["runtime_trace"]
     names = {v.id: v.name for v in ir.values.values()}
     by_name = {**h_in, **h_par}

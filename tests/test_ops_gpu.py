@@ -191,7 +191,7 @@ def test_reference_alias_ids_and_legacy_dispatch(gpu):
     with pytest.raises(RuntimeError, match="InvalidArgument"):  # shape mismatch
         by_id("relu_f16_v0", OpKind.EltwiseRelu, [X], [Tensor.empty((64, 255), "f16")])
     with pytest.raises(RuntimeError, match="NotImplemented"):
-        by_id("layernorm_fwd_f16_v0", OpKind.LayerNormFwd, [X], [O])
+        by_id("batchnorm_fwd_f16_v0", OpKind.BatchNormFwd, [X], [O])
     with pytest.raises(RuntimeError, match="InvalidArgument"):  # sgd output may not alias the gradient
         by_id("sgd_step_f16_v0", OpKind.SgdStep, [X, O], [O])
 

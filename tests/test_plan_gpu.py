@@ -205,6 +205,7 @@ def test_global_graph_api_like_the_reference_binding(gpu):
     with pytest.raises(RuntimeError, match="graph_launch called but no captured graph exists"):
         _C.graph_reset()
         _C.graph_launch()
+    _C.trace_enable(True)  # the binding's default; another test may have switched it off
     s = _C.graph_begin()
     assert s != 0 and _C.graph_stream() == s
     _C.launch_by_id("adam_step_f32_v0", OpKind.AdamStep, [P, G, M, V, bc1, bc2], [P, M, V], 0x4D414441, pay, s)

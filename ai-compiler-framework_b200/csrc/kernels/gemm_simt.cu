@@ -6,14 +6,19 @@
 // kernel, per output element, so results agree bit for bit); (2) shapes the TMA path cannot take
 // (rows not 16-byte aligned, tiny problems).
 //
-// Tile 128x128x8, 256 threads, 8x8 outputs per thread, register-staged double buffering.
+// 256 threads, register-staged double buffering, four tile shapes with BM*BK = BN*BK = 1024 (every thread stages
+// four elements of each operand per k-step): 128x128x8 with 8x8 outputs per thread for large problems, then
+// 64x64x16 (4x4), 32x32x32 (2x2) and 16x16x64 (1x1). The launcher takes the largest tile that still yields at
+// least one block per SM: a 64x256x784 product is 2 blocks of the large tile (142 us, two SMs busy) but 64 blocks
+// of the smallest (a few us). The order of the k loop per output element is the same in all of them.
+#include <type_traits>
+
 #include "gemm_common.cuh"
 
 namespace aicf::cuda {
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 8, TM = 8, TN = 8;
 
 __device__ __forceinline__ float load_elem(const void* base, int64_t idx, DType dt) {
   switch (dt) {
@@ -48,15 +53,19 @@ __device__ __forceinline__ float ld_in(const void* base, int64_t idx) {
   return Cvt<TIn>::to_f(static_cast<const TIn*>(base)[idx]);
 }
 
-template <typename TIn>
+template <typename TIn, int BM, int BN, int BK, int TM, int TN>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(SimtArgs g) {
-  __shared__ __align__(16) float As[2][BK][BM];
-  __shared__ __align__(16) float Bs[2][BK][BN];
+  static_assert(BM * BK == 1024 && BN * BK == 1024 && (BM / TM) * (BN / TN) == 256, "256 threads, 4 staged elements each");
+  // Row padding keeps the k-fast staging writes off a single bank; it is a multiple of the vector width of the reads.
+  constexpr int PADA = TM >= 4 ? 4 : TM, PADB = TN >= 4 ? 4 : TN;
+  __shared__ __align__(16) float As[2][BK][BM + PADA];
+  __shared__ __align__(16) float Bs[2][BK][BN + PADB];
   const int tid = threadIdx.x;
-  const int tx = tid % 16, ty = tid / 16;  // thread owns rows ty*8.., cols tx*8..
+  constexpr int kTX = BN / TN;
+  const int tx = tid % kTX, ty = tid / kTX;  // thread owns rows ty*TM.., cols tx*TN..
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
 
-  // each thread stages 4 elements of the A tile (128x8) and 4 of the B tile (8x128)
+  // each thread stages 4 elements of the A tile (BM x BK) and 4 of the B tile (BK x BN)
   int am[4], ak[4], bk[4], bn[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -81,6 +90,19 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(SimtArgs g) {
       Bs[buf][bk[i]][bn[i]] = rb[i];
     }
   };
+  auto load_vec = [](float* dst, const float* src, auto n_tag) {
+    constexpr int n = decltype(n_tag)::value;
+    if constexpr (n == 8) {
+      *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+      *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(src + 4);
+    } else if constexpr (n == 4) {
+      *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+    } else if constexpr (n == 2) {
+      *reinterpret_cast<float2*>(dst) = *reinterpret_cast<const float2*>(src);
+    } else {
+      dst[0] = src[0];
+    }
+  };
 
   float acc[TM][TN];
 #pragma unroll
@@ -98,10 +120,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(SimtArgs g) {
 #pragma unroll
     for (int k = 0; k < BK; ++k) {
       float a[TM], b[TN];
-      *reinterpret_cast<float4*>(&a[0]) = *reinterpret_cast<const float4*>(&As[buf][k][ty * TM]);
-      *reinterpret_cast<float4*>(&a[4]) = *reinterpret_cast<const float4*>(&As[buf][k][ty * TM + 4]);
-      *reinterpret_cast<float4*>(&b[0]) = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * TN]);
-      *reinterpret_cast<float4*>(&b[4]) = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * TN + 4]);
+      load_vec(a, &As[buf][k][ty * TM], std::integral_constant<int, TM>{});
+      load_vec(b, &Bs[buf][k][tx * TN], std::integral_constant<int, TN>{});
 #pragma unroll
       for (int i = 0; i < TM; ++i)
 #pragma unroll
@@ -147,14 +167,28 @@ Status gemm_simt_run(const GemmProblem& p, cudaStream_t stream) {
   g.relu = p.relu ? 1 : 0;
   g.a_k_fast = p.A.cs <= p.A.rs;
   g.b_n_fast = p.B.cs <= p.B.rs;
-  const dim3 grid(static_cast<unsigned>((p.N + BN - 1) / BN), static_cast<unsigned>((p.M + BM - 1) / BM));
+  // Largest tile that gives every SM a block; the smallest tile when even that one does not.
+  const int64_t sms = sm_count();
+  auto blocks = [&](int64_t bm, int64_t bn) { return ((p.M + bm - 1) / bm) * ((p.N + bn - 1) / bn); };
+  const int tile = blocks(128, 128) >= sms ? 128 : blocks(64, 64) >= sms ? 64 : blocks(32, 32) >= sms ? 32 : 16;
   cudaGetLastError();
+#define AICF_SIMT_LAUNCH(TIN)                                                                                   \
+  switch (tile) {                                                                                               \
+    case 128: gemm_simt_kernel<TIN, 128, 128, 8, 8, 8><<<grid_for(128, 128), 256, 0, stream>>>(g); break;         \
+    case 64: gemm_simt_kernel<TIN, 64, 64, 16, 4, 4><<<grid_for(64, 64), 256, 0, stream>>>(g); break;             \
+    case 32: gemm_simt_kernel<TIN, 32, 32, 32, 2, 2><<<grid_for(32, 32), 256, 0, stream>>>(g); break;             \
+    default: gemm_simt_kernel<TIN, 16, 16, 64, 1, 1><<<grid_for(16, 16), 256, 0, stream>>>(g); break;             \
+  }
+  auto grid_for = [&](int64_t bm, int64_t bn) {
+    return dim3(static_cast<unsigned>((p.N + bn - 1) / bn), static_cast<unsigned>((p.M + bm - 1) / bm));
+  };
   switch (p.A.dtype) {
-    case DType::kF32: gemm_simt_kernel<float><<<grid, 256, 0, stream>>>(g); break;
-    case DType::kF16: gemm_simt_kernel<__half><<<grid, 256, 0, stream>>>(g); break;
-    case DType::kBF16: gemm_simt_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(g); break;
+    case DType::kF32: AICF_SIMT_LAUNCH(float); break;
+    case DType::kF16: AICF_SIMT_LAUNCH(__half); break;
+    case DType::kBF16: AICF_SIMT_LAUNCH(__nv_bfloat16); break;
     default: return Status::InvalidArgument;
   }
+#undef AICF_SIMT_LAUNCH
   return launch_status();
 }
 

@@ -106,6 +106,50 @@ def main(out_path: Path) -> None:
                            [((LM, LN), "f32"), ((LN,), "f32"), ((LN,), "f32")])
     g.update(ln_dx_affine=dx, ln_dgamma=dg, ln_dbeta=db)
     g["ln_dx_plain"] = run_multi("layernorm_bwd_f32_v0", OpKind.LayerNormBwd, [LX, LDY, MU, RS], [((LM, LN), "f32")])[0]
+    # f16 variants of the same ops (drawn last; values are stored as float32 holding exact f16 numbers)
+    h16 = lambda a: np.asarray(a, np.float32).astype(np.float16)
+    hshape = (6, 40, 64)
+    hx, hy = h16(rng.standard_normal(hshape)), h16(rng.standard_normal(hshape))
+    hb = h16(rng.standard_normal(hshape[-1]))
+    g.update(h_x=hx.astype(np.float32), h_y=hy.astype(np.float32), h_bias=hb.astype(np.float32))
+    HX, HY, HB = Tensor.from_numpy(hx), Tensor.from_numpy(hy), Tensor.from_numpy(hb)
+    f16out = lambda kid, kind, ins, shape, **kw: run(kid, kind, ins, shape, out_dtype="f16", **kw)[0].astype(np.float32)
+    g["h_relu"] = f16out("relu_f16_v0", OpKind.EltwiseRelu, [HX], hshape)
+    g["h_relu_bwd"] = f16out("relu_bwd_f16_v0", OpKind.ReluBwd, [HX, HY], hshape)
+    g["h_add"] = f16out("add_f16_v0", OpKind.EltwiseAdd, [HX, HY], hshape)
+    g["h_mse_grad"] = f16out("mse_grad_f16_v0", OpKind.MseGrad, [HX, HY], hshape)
+    g["h_sgd"] = f16out("sgd_step_f16_v0", OpKind.SgdStep, [HX, HY], hshape)
+    g["h_bias_add"] = f16out("bias_add_f16_v0", OpKind.BiasAdd, [HX, HB], hshape)
+    hr = h16(rng.standard_normal((129, 48)))
+    g["h_red_x"] = hr.astype(np.float32)
+    HR = Tensor.from_numpy(hr)
+    g["h_colsum_f16"] = f16out("reduce_sum_keep_lastdim_f16_v0", OpKind.ReduceSum, [HR], (48,))
+    g["h_colsum_f32"] = run("reduce_sum_keep_lastdim_f16_to_f32_v0", OpKind.ReduceSum, [HR], (48,))[0]
+    HMm, HKk, HNn = 64, 48, 80
+    hA, hB = h16(rng.uniform(-1, 1, (HMm, HKk))), h16(rng.uniform(-1, 1, (HKk, HNn)))
+    hbias = h16(rng.standard_normal(HNn))
+    g.update(h_gemm_A=hA.astype(np.float32), h_gemm_B=hB.astype(np.float32), h_gemm_bias=hbias.astype(np.float32))
+    for ta in (0, 1):
+        for tb in (0, 1):
+            a = Tensor.from_numpy(np.ascontiguousarray(hA.T) if ta else hA)
+            b = Tensor.from_numpy(np.ascontiguousarray(hB.T) if tb else hB)
+            g[f"h_gemm_{ta}{tb}"] = f16out("gemm_f16_tc_wmma_out_f16_v0", OpKind.Gemm, [a, b], (HMm, HNn), schema=0x47454D4D,
+                                           payload=struct.pack("<ii", ta, tb))
+            g[f"h_gemm_epi_{ta}{tb}"] = f16out("gemm_bias_relu_f16_tc_wmma_out_f16_v0", OpKind.GemmEpilogue,
+                                               [a, b, Tensor.from_numpy(hbias)], (HMm, HNn), schema=0x4750454C,
+                                               payload=struct.pack("<iii", ta, tb, 1))
+    hlx, hldy = h16(rng.standard_normal((LM, LN)) * 2.0 + 0.5), h16(rng.standard_normal((LM, LN)))
+    hlg, hlb = h16(1.0 + 0.1 * rng.standard_normal(LN)), h16(0.1 * rng.standard_normal(LN))
+    g.update(h_ln_x=hlx.astype(np.float32), h_ln_dy=hldy.astype(np.float32), h_ln_gamma=hlg.astype(np.float32),
+             h_ln_beta=hlb.astype(np.float32))
+    HLX, HLDY, HLG, HLB = (Tensor.from_numpy(a) for a in (hlx, hldy, hlg, hlb))
+    y, mu, rs = run_multi("layernorm_fwd_f16_v0", OpKind.LayerNormFwd, [HLX, HLG, HLB],
+                          [((LM, LN), "f16"), ((LM,), "f32"), ((LM,), "f32")], 0x50454E4C, lnep)
+    g.update(h_ln_y=y.astype(np.float32), h_ln_mean=mu, h_ln_rstd=rs)
+    dx, dg, db = run_multi("layernorm_bwd_f16_v0", OpKind.LayerNormBwd,
+                           [HLX, HLDY, HLG, Tensor.from_numpy(mu), Tensor.from_numpy(rs)],
+                           [((LM, LN), "f16"), ((LN,), "f32"), ((LN,), "f32")])
+    g.update(h_ln_dx=dx.astype(np.float32), h_ln_dgamma=dg, h_ln_dbeta=db)
     out_path.parent.mkdir(parents=True, exist_ok=True)
     np.savez_compressed(out_path, **g)
     print(f"wrote {out_path} ({out_path.stat().st_size >> 10} KiB, {len(g)} arrays)")

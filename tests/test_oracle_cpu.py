@@ -202,3 +202,40 @@ def test_oracle_against_reference_cuda_golden_vectors():
     assert np.allclose(dx, g["ln_dx_affine"], rtol=1e-5, atol=1e-5)
     assert np.allclose(dg, g["ln_dgamma"], rtol=1e-5, atol=1e-5) and np.allclose(db, g["ln_dbeta"], rtol=1e-5, atol=1e-5)
     assert np.allclose(oracle.layernorm_bwd(lx, ldy, None, g["ln_mean"], g["ln_rstd"])[0], g["ln_dx_plain"], rtol=1e-5, atol=1e-5)
+
+
+def _f16_ulps(got, want):
+    """Largest distance in units of the f16 spacing at `want` (normal range floor 2^-14)."""
+    want, got = np.asarray(want, np.float64), np.asarray(got, np.float64)
+    return float(np.max(np.abs(got - want) / (np.maximum(np.abs(want), 2.0 ** -14) * 2.0 ** -10)))
+
+
+def test_oracle_against_reference_cuda_f16_golden_vectors():
+    """The f16 variants of the reference's kernels (same generator, arrays prefixed h_): the oracle computes in fp64
+    and rounds once to f16; the reference computes in half2 or fp32 and rounds. Exact where the operation is exactly
+    representable before the rounding, one f16 spacing otherwise (two roundings in mse_grad, fp32 accumulation in the
+    wmma GEMM and in layer norm)."""
+    g = np.load(GOLDEN / "ref_cuda_golden.npz")
+    assert "h_x" in g.files, "regenerate tests/golden/ref_cuda_golden.npz with tests/golden/make_ref_golden.py"
+    r16 = oracle.f16_round
+    x, y = g["h_x"], g["h_y"]
+    assert np.array_equal(g["h_relu"], oracle.relu(x)) and np.array_equal(g["h_relu_bwd"], oracle.relu_bwd(x, y))
+    assert np.array_equal(g["h_add"], r16(oracle.add(x, y)))
+    assert np.array_equal(g["h_sgd"], r16(oracle.sgd_step(x, y)))
+    assert np.array_equal(g["h_bias_add"], r16(oracle.bias_add(x, g["h_bias"])))
+    assert _f16_ulps(g["h_mse_grad"], r16(oracle.mse_grad(x, y))) <= 1.0
+    assert np.array_equal(g["h_colsum_f16"], r16(oracle.reduce_sum_columns(g["h_red_x"])))
+    assert np.allclose(g["h_colsum_f32"], oracle.reduce_sum_columns(g["h_red_x"]), rtol=1e-6, atol=1e-5)
+    A, B, bias = g["h_gemm_A"], g["h_gemm_B"], g["h_gemm_bias"]
+    for ta in (0, 1):
+        for tb in (0, 1):
+            a = A.T.copy() if ta else A
+            b = B.T.copy() if tb else B
+            assert _f16_ulps(g[f"h_gemm_{ta}{tb}"], r16(oracle.gemm(a, b, ta, tb))) <= 1.0
+            assert _f16_ulps(g[f"h_gemm_epi_{ta}{tb}"], r16(oracle.gemm_epilogue(a, b, bias, ta, tb, 1))) <= 1.0
+    yy, mu, rs = oracle.layernorm_fwd(g["h_ln_x"], g["h_ln_gamma"], g["h_ln_beta"], np.float32(1e-5))
+    assert _f16_ulps(g["h_ln_y"], r16(yy)) <= 1.0
+    assert np.allclose(mu, g["h_ln_mean"], rtol=1e-5, atol=1e-6) and np.allclose(rs, g["h_ln_rstd"], rtol=1e-5)
+    dx, dgam, dbet = oracle.layernorm_bwd(g["h_ln_x"], g["h_ln_dy"], g["h_ln_gamma"], g["h_ln_mean"], g["h_ln_rstd"])
+    assert _f16_ulps(g["h_ln_dx"], r16(dx)) <= 1.0
+    assert np.allclose(dgam, g["h_ln_dgamma"], rtol=1e-5, atol=1e-5) and np.allclose(dbet, g["h_ln_dbeta"], rtol=1e-5, atol=1e-5)

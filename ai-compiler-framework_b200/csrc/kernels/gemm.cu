@@ -3,6 +3,7 @@
 // Each variant validates its contract and then routes to one of two sm_100a kernels:
 //   gemm_tcgen05_run  16-bit operands whose rows are 16-byte aligned (TMA + tcgen05/TMEM)
 //   gemm_simt_run     fp32 operands (exact fp32), or shapes the TMA path cannot express
+//   gemm_tf32x3_run   fp32 operands on the tensor cores (three TF32 products per k step), only under its own ids
 // The reference ids keep the reference's dtype contracts
 // (ops/gemm/launcher.cu:272-287,330-361; ops/gemm_epilogue/launcher.cu:333-349,399-431).
 #include "gemm_common.cuh"
@@ -97,6 +98,46 @@ Status launch(const TensorDesc* in, int ni, TensorDesc* out, int no, const void*
   if (!check(Contracts<kId>::value, in, ni, out, no, attr, &p)) return Status::InvalidArgument;
   return run(p, stream);
 }
+// fp32 on the tensor cores: opt-in ids, never chosen over the exact kernel by priority dispatch (lower priority).
+template <int kId>
+size_t tf32x3_workspace(const TensorDesc* in, int ni, const void* attr) {
+  if (!in || ni < 2 || in[0].rank() != 2 || in[1].rank() != 2) return 0;
+  bool ta, tb, relu;
+  if (Contracts<kId>::value.bias == BiasRule::None) read_gemm_attr(attr, &ta, &tb);
+  else read_gemm_epilogue_attr(attr, &ta, &tb, &relu);
+  GemmProblem p;
+  p.A = view_of(in[0], ta);
+  p.B = view_of(in[1], tb);
+  p.M = p.A.rows;
+  p.K = p.A.cols;
+  p.N = p.B.cols;
+  if (p.M <= 0 || p.N <= 0 || p.K <= 0) return 0;
+  return gemm_tf32x3_workspace(p);
+}
+template <int kId>
+bool tf32x3_supported(const TensorDesc* in, int ni, const TensorDesc* out, int no, const void* attr) {
+  GemmProblem p;
+  return check(Contracts<kId>::value, in, ni, out, no, attr, &p) && gemm_tf32x3_eligible(p);
+}
+template <int kId>
+Status tf32x3_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, const void* attr, void* ws, size_t ws_bytes,
+                     cudaStream_t stream) {
+  GemmProblem p;
+  if (!check(Contracts<kId>::value, in, ni, out, no, attr, &p) || !gemm_tf32x3_eligible(p)) return Status::InvalidArgument;
+  return gemm_tf32x3_run(p, ws, ws_bytes, stream);
+}
+template <int kId>
+KernelVariant tf32x3_variant(const char* name) {
+  KernelVariant v{};
+  v.name = name;
+  v.flags = kKV_CaptureSafe;
+  v.expected_attr_schema_id = 0;
+  v.launch = tf32x3_launch<kId>;
+  v.supported = tf32x3_supported<kId>;
+  v.query_workspace = tf32x3_workspace<kId>;
+  return v;
+}
+
 template <int kId>
 KernelVariant variant(const char* name) {
   KernelVariant v{};
@@ -122,6 +163,9 @@ KernelVariant make_gemm_bias_relu_f16_tc_wmma_out_f16_variant() { return variant
 KernelVariant make_gemm_bias_relu_bf16_tcgen05_out_bf16_variant() { return variant<12>("gemm_bias_relu_bf16_tcgen05_out_bf16"); }
 KernelVariant make_gemm_bias_relu_bf16_tcgen05_out_f32_variant() { return variant<13>("gemm_bias_relu_bf16_tcgen05_out_f32"); }
 KernelVariant make_gemm_bias_relu_f16_tcgen05_out_f16_variant() { return variant<14>("gemm_bias_relu_f16_tcgen05_out_f16"); }
+
+KernelVariant make_gemm_f32_3xtf32_variant() { return tf32x3_variant<0>("gemm_f32_3xtf32_tcgen05"); }
+KernelVariant make_gemm_bias_relu_f32_3xtf32_variant() { return tf32x3_variant<10>("gemm_bias_relu_f32_3xtf32_tcgen05"); }
 
 KernelVariant make_gemm_relu_bwd_bf16_variant() { return variant<20>("gemm_relu_bwd_bf16_tcgen05"); }
 KernelVariant make_gemm_relu_bwd_f16_variant() { return variant<21>("gemm_relu_bwd_f16_tcgen05"); }

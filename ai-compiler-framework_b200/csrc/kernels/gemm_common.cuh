@@ -91,5 +91,10 @@ Status gemm_simt_run(const GemmProblem& p, cudaStream_t stream);
 // alignment rules, so the caller can fall through to the SIMT kernel.
 Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream);
 bool gemm_tcgen05_eligible(const GemmProblem& p);
+// Implemented in gemm_tcgen05.cu: fp32 operands on the tensor cores as three TF32 products per k step (hi/lo split
+// of both operands, staged in `ws`). Not bit-identical to an fp32 FMA chain; error is of the order of fp32 rounding.
+bool gemm_tf32x3_eligible(const GemmProblem& p);
+size_t gemm_tf32x3_workspace(const GemmProblem& p);
+Status gemm_tf32x3_run(const GemmProblem& p, void* ws, size_t ws_bytes, cudaStream_t stream);
 
 }  // namespace aicf::cuda

@@ -794,6 +794,213 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (tl && threadIdx.x == 0) g_gemm_timeline[8] = global_ns();
 }
 
+// ================================================================== fp32 on the tensor cores: 3xTF32
+// C = A * B with fp32 operands at close to fp32 accuracy, using kind::tf32 MMAs. Every operand is first split into
+// hi = tf32(x) and lo = tf32(x - hi) (both exactly representable in TF32, x = hi + lo up to 2^-22 |x|), written
+// K-major into the workspace by tf32_split_kernel; the main loop then accumulates, per 8-wide k step,
+// A_lo*B_hi + A_hi*B_lo + A_hi*B_hi into the same fp32 accumulator in tensor memory (small terms first; the
+// dropped A_lo*B_lo term is below 2^-22 of the product). Same roles, barriers and epilogue as the 16-bit kernel;
+// tile 128x128, k slab 32 (one 128-byte swizzle row of fp32), 3 stages of 4 x 16 KiB, two 128-column accumulators.
+constexpr int k3TileN = 128;
+constexpr int k3TileK = 32;
+constexpr int k3Stages = 3;
+constexpr int k3TileBytes = kTileM * k3TileK * 4;            // 16 KiB: one operand part of one stage
+constexpr int k3StageBytes = 4 * k3TileBytes;               // A_hi, A_lo, B_hi, B_lo
+constexpr int k3TmemCols = 256;
+constexpr size_t k3SmemBytes = 1024 + size_t(k3Stages) * k3StageBytes + 256 + 4 * k3TileN * sizeof(float);
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// src(r, k) = src[r * r_stride + k * k_stride] for r < R, k < K  ->  hi/lo[r * Kp + k] (Kp >= K, pad untouched:
+// the tensor maps are encoded with K columns, so the pad is never read). 32x32 tiles through shared memory make
+// both the read (along whichever index has unit stride) and the write (along k) coalesced.
+__global__ void __launch_bounds__(256)
+    tf32_split_kernel(const float* __restrict__ src, int64_t r_stride, int64_t k_stride, int64_t R, int64_t K, int64_t Kp,
+                      float* __restrict__ hi, float* __restrict__ lo) {
+  __shared__ float tile[32][33];
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * 32, k0 = static_cast<int64_t>(blockIdx.x) * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const bool k_fast = k_stride <= r_stride;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int a = ty + 8 * i;  // slow index within the tile
+    const int64_t r = k_fast ? r0 + a : r0 + tx, k = k_fast ? k0 + tx : k0 + a;
+    const float v = (r < R && k < K) ? src[r * r_stride + k * k_stride] : 0.0f;
+    if (k_fast) tile[a][tx] = v; else tile[tx][a] = v;  // tile[r][k]
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int rr = ty + 8 * i;
+    const int64_t r = r0 + rr, k = k0 + tx;
+    if (r < R && k < K) {
+      const float v = tile[rr][tx];
+      uint32_t h, l;
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(v));
+      const float rest = v - __uint_as_float(h);
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rest));
+      hi[r * Kp + k] = __uint_as_float(h);
+      lo[r * Kp + k] = __uint_as_float(l);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_ahi, const __grid_constant__ CUtensorMap tmap_alo,
+                       const __grid_constant__ CUtensorMap tmap_bhi, const __grid_constant__ CUtensorMap tmap_blo,
+                       const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const uint32_t bars = base + k3Stages * k3StageBytes;
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * k3Stages, bar_acc_full = bars + 16 * k3Stages,
+                 bar_acc_empty = bars + 16 * k3Stages + 8 * kAccBufs;
+  uint8_t* misc = base_ptr + k3Stages * k3StageBytes + 16 * k3Stages + 16 * kAccBufs;
+  volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(misc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 4);
+  float* bias_smem = reinterpret_cast<float*>(base_ptr + k3Stages * k3StageBytes + 256);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + k3TileN - 1) / k3TileN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_blocks = (p.K + k3TileK - 1) / k3TileK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < k3Stages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < kAccBufs; ++b) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_empty + 8 * b, 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), k3TmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {  // TMA producer
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+        const int m0 = tm * kTileM, n0 = tn * k3TileN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1)) { alive = false; break; }
+          const uint32_t full = bar_full + 8 * stage;
+          const uint32_t s0 = base + stage * k3StageBytes;
+          const int k0 = kb * k3TileK;
+          mbar_expect_tx(full, k3StageBytes);
+          tma_load_2d(s0, &tmap_ahi, k0, m0, full);
+          tma_load_2d(s0 + k3TileBytes, &tmap_alo, k0, m0, full);
+          tma_load_2d(s0 + 2 * k3TileBytes, &tmap_bhi, k0, n0, full);
+          tma_load_2d(s0 + 3 * k3TileBytes, &tmap_blo, k0, n0, full);
+          if (++stage == k3Stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {  // MMA issuer
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool alive = true;
+      constexpr uint32_t kStep = (8 * 4) >> 4;  // one k step of 8 fp32 = 32 B, in descriptor units of 16 B
+      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+        if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, 2)) { alive = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * k3TileN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3)) { alive = false; break; }
+          tc_fence_after();
+          const uint32_t s0 = base + stage * k3StageBytes;
+          const uint64_t ahi = make_smem_desc(s0, 0), alo = make_smem_desc(s0 + k3TileBytes, 0);
+          const uint64_t bhi = make_smem_desc(s0 + 2 * k3TileBytes, 0), blo = make_smem_desc(s0 + 3 * k3TileBytes, 0);
+#pragma unroll
+          for (int k = 0; k < k3TileK / 8; ++k) {
+            umma_tf32(tmem_d, alo + k * kStep, bhi + k * kStep, p.idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_tf32(tmem_d, ahi + k * kStep, blo + k * kStep, p.idesc, 1u);
+            umma_tf32(tmem_d, ahi + k * kStep, bhi + k * kStep, p.idesc, 1u);
+          }
+          umma_commit(bar_empty + 8 * stage);
+          if (++stage == k3Stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!alive) break;
+        umma_commit(bar_acc_full + 8 * acc);
+        if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else {
+    const int sub = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+      const int row = tm * kTileM + sub * 32 + lane;
+      const int n0 = tn * k3TileN;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, 4))) { alive = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * k3TileN;
+      float* bs = bias_smem + (warp - 2) * k3TileN;
+#pragma unroll
+      for (int h = 0; h < k3TileN / 32; ++h) {
+        const int col = n0 + lane + 32 * h;
+        bs[lane + 32 * h] = (p.bias_dtype != 0 && col < p.N) ? bias_at(p, col) : 0.0f;
+      }
+      __syncwarp();
+#pragma unroll 1
+      for (int c = 0; c < k3TileN / 32; c += 2) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;
+        uint32_t r[64];
+        const bool two = col0 + 32 < p.N;
+        if (two) {
+          tmem_ld_32x32_pair(taddr + c * 32, r);
+        } else {
+          tmem_ld_32x32(taddr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        }
+        epilogue_chunk(p, row, col0, &r[0], bs + c * 32);
+        if (two) epilogue_chunk(p, row, col0 + 32, &r[32], bs + c * 32 + 32);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+      if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(16384);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, k3TmemCols);
+  }
+}
+
 // ------------------------------------------------------------------ host side
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -951,6 +1158,103 @@ Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream) {
   const int64_t tiles = ((p.M + kTileM - 1) / kTileM) * ((p.N + kTileN - 1) / kTileN);
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
   gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, g);
+  return launch_status();
+}
+
+// ------------------------------------------------------------------ 3xTF32 host side
+namespace {
+
+int64_t tf32_kp(int64_t K) { return (K + 3) / 4 * 4; }  // row pitch of the split operands: a multiple of 16 bytes
+
+bool encode_f32_kmajor(CUtensorMap* map, const float* base, int64_t K, int64_t rows, int64_t Kp, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(Kp) * 4};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(k3TileK), box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool gemm_tf32x3_eligible(const GemmProblem& p) {
+  if (p.A.dtype != DType::kF32 || p.B.dtype != DType::kF32 || p.C.dtype != DType::kF32) return false;
+  if (p.bias && p.bias_dtype != DType::kF32) return false;
+  if (p.C.cs != 1) return false;
+  if (p.M > 0x7fffff00 || p.N > 0x7fffff00 || p.K > 0x7fffff00) return false;
+  return encode_fn() != nullptr;
+}
+
+// hi and lo copies of both operands, K-major: 2 * (M + N) * Kp floats, each part 1024-byte aligned.
+size_t gemm_tf32x3_workspace(const GemmProblem& p) {
+  const size_t kp = static_cast<size_t>(tf32_kp(p.K));
+  auto part = [&](int64_t rows) { return (static_cast<size_t>(rows) * kp * 4 + 1023) / 1024 * 1024; };
+  return 2 * part(p.M) + 2 * part(p.N) + 1024;
+}
+
+Status gemm_tf32x3_run(const GemmProblem& p, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  if (!gemm_tf32x3_eligible(p)) return Status::NotImplemented;
+  const size_t need = gemm_tf32x3_workspace(p);
+  if (!ws || ws_bytes < need) return Status::InvalidArgument;
+  const int64_t kp = tf32_kp(p.K);
+  auto part = [&](int64_t rows) { return (static_cast<size_t>(rows) * kp * 4 + 1023) / 1024 * 1024; };
+  uint8_t* w = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ws) + 1023) & ~uintptr_t(1023));
+  float* ahi = reinterpret_cast<float*>(w);
+  float* alo = reinterpret_cast<float*>(w + part(p.M));
+  float* bhi = reinterpret_cast<float*>(w + 2 * part(p.M));
+  float* blo = reinterpret_cast<float*>(w + 2 * part(p.M) + part(p.N));
+
+  cudaGetLastError();
+  const dim3 ga(static_cast<unsigned>((p.K + 31) / 32), static_cast<unsigned>((p.M + 31) / 32));
+  const dim3 gb(static_cast<unsigned>((p.K + 31) / 32), static_cast<unsigned>((p.N + 31) / 32));
+  if (ga.y > 65535u || gb.y > 65535u) return Status::NotImplemented;
+  // A is [M,K]: rs walks M, cs walks K.  B is [K,N]: rs walks K, cs walks N; its split copy is [N,K].
+  tf32_split_kernel<<<ga, 256, 0, stream>>>(static_cast<const float*>(p.A.data), p.A.rs, p.A.cs, p.M, p.K, kp, ahi, alo);
+  tf32_split_kernel<<<gb, 256, 0, stream>>>(static_cast<const float*>(p.B.data), p.B.cs, p.B.rs, p.N, p.K, kp, bhi, blo);
+  if (launch_status() != Status::Ok) return Status::Internal;
+
+  CUtensorMap mahi, malo, mbhi, mblo;
+  if (!encode_f32_kmajor(&mahi, ahi, p.K, p.M, kp, kTileM) || !encode_f32_kmajor(&malo, alo, p.K, p.M, kp, kTileM) ||
+      !encode_f32_kmajor(&mbhi, bhi, p.K, p.N, kp, k3TileN) || !encode_f32_kmajor(&mblo, blo, p.K, p.N, kp, k3TileN))
+    return Status::Internal;
+
+  GemmParams g{};
+  g.C = const_cast<void*>(p.C.data);
+  g.bias = p.bias;
+  g.ldc = p.C.rs;
+  g.bias_stride = p.bias_stride;
+  g.mask = p.mask;
+  g.mask_ld = p.mask_ld;
+  g.mask_vec_ok = p.mask ? (aligned_to(p.mask, 16) && ((p.mask_ld * 4) % 16 == 0)) : 0;
+  g.M = static_cast<int>(p.M);
+  g.N = static_cast<int>(p.N);
+  g.K = static_cast<int>(p.K);
+  g.c_dtype = static_cast<int>(DType::kF32);
+  g.bias_dtype = p.bias ? static_cast<int>(p.bias_dtype) : 0;
+  g.relu = p.relu ? 1 : 0;
+  // D = f32, A/B format TF32 (2), both K-major, N >> 3, M >> 4
+  g.idesc = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(k3TileN >> 3) << 17) |
+            (static_cast<uint32_t>(kTileM >> 4) << 24);
+  g.c_vec_ok = aligned_to(p.C.data, 16) && ((p.C.rs * 4) % 16 == 0);
+
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16) dev = 0;
+  static bool attr_set[16] = {false};
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(k3SmemBytes)) != cudaSuccess) {
+      cudaGetLastError();
+      return Status::Internal;
+    }
+    attr_set[dev] = true;
+  }
+  const int64_t tiles = ((p.M + kTileM - 1) / kTileM) * ((p.N + k3TileN - 1) / k3TileN);
+  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  gemm_tf32x3_kernel<<<grid, kThreads, k3SmemBytes, stream>>>(mahi, malo, mbhi, mblo, g);
   return launch_status();
 }
 

@@ -60,6 +60,8 @@ KernelVariant make_reduce_mean_lastaxis_f32_variant();
 KernelVariant make_reduce_mean_lastaxis_bf16_variant();
 KernelVariant make_reduce_mean_lastaxis_f16_variant();
 // softmax.cu
+KernelVariant make_gemm_f32_3xtf32_variant();
+KernelVariant make_gemm_bias_relu_f32_3xtf32_variant();
 KernelVariant make_layernorm_fwd_f32_variant();
 KernelVariant make_layernorm_fwd_f16_variant();
 KernelVariant make_layernorm_fwd_bf16_variant();
@@ -160,6 +162,8 @@ extern "C" void aicf_cuda_register_all_kernels() {
       {K::Gemm, make_gemm_bf16_tcgen05_out_f32_variant, 24, "gemm_bf16_tcgen05_out_f32_v0"},
       {K::Gemm, make_gemm_f16_tcgen05_out_f16_variant, 19, "gemm_f16_tcgen05_out_f16_v0"},
       {K::Gemm, make_gemm_f16_tcgen05_out_f32_variant, 18, "gemm_f16_tcgen05_out_f32_v0"},
+      {K::Gemm, make_gemm_f32_3xtf32_variant, -20, "gemm_f32_3xtf32_v0"},
+      {K::GemmEpilogue, make_gemm_bias_relu_f32_3xtf32_variant, -20, "gemm_bias_relu_f32_3xtf32_v0"},
       {K::GemmEpilogue, make_gemm_bias_relu_bf16_tcgen05_out_bf16_variant, 25, "gemm_bias_relu_bf16_tcgen05_out_bf16_v0"},
       {K::GemmEpilogue, make_gemm_bias_relu_bf16_tcgen05_out_f32_variant, 24, "gemm_bias_relu_bf16_tcgen05_out_f32_v0"},
       {K::GemmEpilogue, make_gemm_bias_relu_f16_tcgen05_out_f16_variant, 19, "gemm_bias_relu_f16_tcgen05_out_f16_v0"},

@@ -164,3 +164,61 @@ def test_f32_4096_sampled_rows(gpu):
     rows = np.random.default_rng(0).choice(n, 32, replace=False)
     want = np.maximum(A[rows].astype(np.float64) @ B.astype(np.float64) + bias, 0)
     assert rel_err(host(C)[rows], want) <= 1e-5
+
+
+# ------------------------------------------------------------------ fp32 on the tensor cores (3xTF32, opt-in ids)
+def _tf32x3_tol(K):
+    """Normwise error bound of the 3xTF32 path against fp64: the split loses 2^-22 per product and the tensor core's
+    fp32 accumulator rounds toward zero at every 8-wide k step, which grows linearly in K (measured 2.8e-5 at
+    K = 4096, 8e-6 at 1024); the bound keeps a factor ~3 of slack."""
+    return 2e-8 * K + 2e-6
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES + [(130, 70, 50), (64, 200, 37), (1, 1, 1), (300, 129, 1001)])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_gemm_f32_3xtf32_all_transposes(gpu, M, N, K, ta, tb):
+    A, B, bias, sa, sb = _operands(M, N, K, ta, tb, "f32")
+    C = Tensor.zeros((M, N), "f32")
+    by_id("gemm_f32_3xtf32_v0", OpKind.Gemm, [dev(sa), dev(sb)], [C], GEMM, struct.pack("<ii", ta, tb))
+    assert rel_err(host(C), oracle.gemm(A, B)) <= _tf32x3_tol(K)
+    for relu in (1, 0):
+        by_id("gemm_bias_relu_f32_3xtf32_v0", OpKind.GemmEpilogue, [dev(sa), dev(sb), dev(bias)], [C], GPEL,
+              struct.pack("<iii", ta, tb, relu))
+        assert rel_err(host(C), oracle.gemm_epilogue(A, B, bias, False, False, bool(relu))) <= _tf32x3_tol(K)
+    assert _C.gemm_status() == 0
+
+
+def test_gemm_f32_3xtf32_is_opt_in_and_much_closer_than_one_tf32_pass(gpu):
+    M = N = 256
+    K = 512
+    A, B, bias, sa, sb = _operands(M, N, K, 0, 1, "f32")
+    exact, fast = Tensor.zeros((M, N)), Tensor.zeros((M, N))
+    # priority dispatch keeps choosing the exact kernel for fp32 operands
+    op_call(OpKind.Gemm, [dev(sa), dev(sb)], [exact], GEMM, struct.pack("<ii", 0, 1))
+    ref = Tensor.zeros((M, N))
+    by_id("gemm_f32_naive_v0", OpKind.Gemm, [dev(sa), dev(sb)], [ref], GEMM, struct.pack("<ii", 0, 1))
+    assert np.array_equal(host(exact), host(ref))
+    by_id("gemm_f32_3xtf32_v0", OpKind.Gemm, [dev(sa), dev(sb)], [fast], GEMM, struct.pack("<ii", 0, 1))
+    want = oracle.gemm(A, B)
+    tf32 = lambda a: (np.asarray(a, np.float32).view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+    one_pass = tf32(A).astype(np.float64) @ tf32(B).astype(np.float64)
+    assert rel_err(host(fast), want) <= _tf32x3_tol(K) < 0.05 * rel_err(one_pass, want)
+    # 16-bit operands are not this id's contract
+    with pytest.raises(RuntimeError, match="InvalidArgument"):
+        by_id("gemm_f32_3xtf32_v0", OpKind.Gemm, [dev(oracle.f16_round(sa), "f16"), dev(oracle.f16_round(sb), "f16")],
+              [Tensor.zeros((M, N), "f16")], GEMM, struct.pack("<ii", 0, 1))
+    # the result does not depend on the run
+    again = Tensor.zeros((M, N))
+    by_id("gemm_f32_3xtf32_v0", OpKind.Gemm, [dev(sa), dev(sb)], [again], GEMM, struct.pack("<ii", 0, 1))
+    assert np.array_equal(host(again), host(fast))
+
+
+def test_gemm_f32_3xtf32_4096_sampled_rows(gpu):
+    n = 4096
+    A, B, bias = oracle.gemm_inputs(n, n, n, seed=1)
+    C = Tensor.empty((n, n))
+    by_id("gemm_bias_relu_f32_3xtf32_v0", OpKind.GemmEpilogue, [dev(A), dev(B), dev(bias)], [C], GPEL, struct.pack("<iii", 0, 0, 1))
+    rows = np.random.default_rng(0).choice(n, 32, replace=False)
+    want = np.maximum(A[rows].astype(np.float64) @ B.astype(np.float64) + bias, 0)
+    assert rel_err(host(C)[rows], want) <= _tf32x3_tol(n)
+    assert _C.gemm_status() == 0

@@ -800,13 +800,19 @@ __global__ void __launch_bounds__(kThreads, 1)
 // K-major into the workspace by tf32_split_kernel; the main loop then accumulates, per 8-wide k step,
 // A_lo*B_hi + A_hi*B_lo + A_hi*B_hi into the same fp32 accumulator in tensor memory (small terms first; the
 // dropped A_lo*B_lo term is below 2^-22 of the product). Same roles, barriers and epilogue as the 16-bit kernel;
-// tile 128x128, k slab 32 (one 128-byte swizzle row of fp32), 3 stages of 4 x 16 KiB, two 128-column accumulators.
+// tile 128x128, k slab 32 (one 128-byte swizzle row of fp32), 3 stages of 4 x 16 KiB.
+// The tensor core rounds its fp32 accumulator toward zero at every k step, an error that grows linearly with the
+// number of steps accumulated in place. K is therefore cut into chunks of 512: each chunk accumulates from zero in
+// one of four 128-column accumulators, and the epilogue warps add the chunk results in registers with ordinary
+// round-to-nearest fp32 additions while the next chunks are already being multiplied.
 constexpr int k3TileN = 128;
 constexpr int k3TileK = 32;
 constexpr int k3Stages = 3;
 constexpr int k3TileBytes = kTileM * k3TileK * 4;            // 16 KiB: one operand part of one stage
 constexpr int k3StageBytes = 4 * k3TileBytes;               // A_hi, A_lo, B_hi, B_lo
-constexpr int k3TmemCols = 256;
+constexpr int k3AccBufs = 4;
+constexpr int k3ChunkBlocks = 8;                            // k slabs per accumulation chunk: 8 x 32 = 256
+constexpr int k3TmemCols = k3AccBufs * k3TileN;             // 512
 constexpr size_t k3SmemBytes = 1024 + size_t(k3Stages) * k3StageBytes + 256 + 4 * k3TileN * sizeof(float);
 
 __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -862,8 +868,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* base_ptr = smem_raw + (base - raw);
   const uint32_t bars = base + k3Stages * k3StageBytes;
   const uint32_t bar_full = bars, bar_empty = bars + 8 * k3Stages, bar_acc_full = bars + 16 * k3Stages,
-                 bar_acc_empty = bars + 16 * k3Stages + 8 * kAccBufs;
-  uint8_t* misc = base_ptr + k3Stages * k3StageBytes + 16 * k3Stages + 16 * kAccBufs;
+                 bar_acc_empty = bars + 16 * k3Stages + 8 * k3AccBufs;
+  uint8_t* misc = base_ptr + k3Stages * k3StageBytes + 16 * k3Stages + 16 * k3AccBufs;
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 4);
   float* bias_smem = reinterpret_cast<float*>(base_ptr + k3Stages * k3StageBytes + 256);
@@ -878,7 +884,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int b = 0; b < kAccBufs; ++b) {
+    for (int b = 0; b < k3AccBufs; ++b) {
       mbar_init(bar_acc_full + 8 * b, 1);
       mbar_init(bar_acc_empty + 8 * b, 4);
     }
@@ -925,27 +931,30 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool alive = true;
       constexpr uint32_t kStep = (8 * 4) >> 4;  // one k step of 8 fp32 = 32 B, in descriptor units of 16 B
       for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-        if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, 2)) { alive = false; break; }
-        tc_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * k3TileN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3)) { alive = false; break; }
+        for (int kb0 = 0; kb0 < k_blocks && alive; kb0 += k3ChunkBlocks) {
+          if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, 2)) { alive = false; break; }
           tc_fence_after();
-          const uint32_t s0 = base + stage * k3StageBytes;
-          const uint64_t ahi = make_smem_desc(s0, 0), alo = make_smem_desc(s0 + k3TileBytes, 0);
-          const uint64_t bhi = make_smem_desc(s0 + 2 * k3TileBytes, 0), blo = make_smem_desc(s0 + 3 * k3TileBytes, 0);
+          const uint32_t tmem_d = tmem_base + acc * k3TileN;
+          const int kb1 = min(kb0 + k3ChunkBlocks, k_blocks);
+          for (int kb = kb0; kb < kb1; ++kb) {
+            if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3)) { alive = false; break; }
+            tc_fence_after();
+            const uint32_t s0 = base + stage * k3StageBytes;
+            const uint64_t ahi = make_smem_desc(s0, 0), alo = make_smem_desc(s0 + k3TileBytes, 0);
+            const uint64_t bhi = make_smem_desc(s0 + 2 * k3TileBytes, 0), blo = make_smem_desc(s0 + 3 * k3TileBytes, 0);
 #pragma unroll
-          for (int k = 0; k < k3TileK / 8; ++k) {
-            umma_tf32(tmem_d, alo + k * kStep, bhi + k * kStep, p.idesc, (kb | k) != 0 ? 1u : 0u);
-            umma_tf32(tmem_d, ahi + k * kStep, blo + k * kStep, p.idesc, 1u);
-            umma_tf32(tmem_d, ahi + k * kStep, bhi + k * kStep, p.idesc, 1u);
+            for (int k = 0; k < k3TileK / 8; ++k) {
+              umma_tf32(tmem_d, alo + k * kStep, bhi + k * kStep, p.idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+              umma_tf32(tmem_d, ahi + k * kStep, blo + k * kStep, p.idesc, 1u);
+              umma_tf32(tmem_d, ahi + k * kStep, bhi + k * kStep, p.idesc, 1u);
+            }
+            umma_commit(bar_empty + 8 * stage);
+            if (++stage == k3Stages) { stage = 0; phase ^= 1u; }
           }
-          umma_commit(bar_empty + 8 * stage);
-          if (++stage == k3Stages) { stage = 0; phase ^= 1u; }
+          if (!alive) break;
+          umma_commit(bar_acc_full + 8 * acc);  // this chunk's partial product is complete
+          if (++acc == k3AccBufs) { acc = 0; acc_phase ^= 1u; }
         }
-        if (!alive) break;
-        umma_commit(bar_acc_full + 8 * acc);
-        if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
       }
     }
     __syncwarp();
@@ -959,9 +968,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
       const int row = tm * kTileM + sub * 32 + lane;
       const int n0 = tn * k3TileN;
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, 4))) { alive = false; break; }
-      tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * k3TileN;
       float* bs = bias_smem + (warp - 2) * k3TileN;
 #pragma unroll
       for (int h = 0; h < k3TileN / 32; ++h) {
@@ -969,24 +975,36 @@ __global__ void __launch_bounds__(kThreads, 1)
         bs[lane + 32 * h] = (p.bias_dtype != 0 && col < p.N) ? bias_at(p, col) : 0.0f;
       }
       __syncwarp();
-#pragma unroll 1
-      for (int c = 0; c < k3TileN / 32; c += 2) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= p.N) break;
-        uint32_t r[64];
-        const bool two = col0 + 32 < p.N;
-        if (two) {
-          tmem_ld_32x32_pair(taddr + c * 32, r);
-        } else {
-          tmem_ld_32x32(taddr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+      // Running sum of this thread's row over the chunks: 128 floats in registers (every index below is a
+      // compile-time constant), added with round-to-nearest.
+      float run[k3TileN];
+      for (int kb0 = 0; kb0 < k_blocks; kb0 += k3ChunkBlocks) {
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, 4))) { alive = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * k3TileN;
+#pragma unroll
+        for (int c = 0; c < k3TileN / 64; ++c) {
+          uint32_t r[64];
+          tmem_ld_32x32_pair(taddr + c * 64, r);
+          if (kb0 == 0) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) run[c * 64 + j] = __uint_as_float(r[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) run[c * 64 + j] += __uint_as_float(r[j]);
+          }
         }
-        epilogue_chunk(p, row, col0, &r[0], bs + c * 32);
-        if (two) epilogue_chunk(p, row, col0 + 32, &r[32], bs + c * 32 + 32);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+        if (++acc == k3AccBufs) { acc = 0; acc_phase ^= 1u; }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
-      if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
+      if (!alive) break;
+#pragma unroll
+      for (int c = 0; c < k3TileN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 < p.N) epilogue_chunk(p, row, col0, reinterpret_cast<const uint32_t*>(&run[c * 32]), bs + c * 32);
+      }
     }
   }
 

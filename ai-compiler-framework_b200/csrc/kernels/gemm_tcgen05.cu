@@ -20,6 +20,7 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <type_traits>
 
 #include "gemm_common.cuh"
 
@@ -42,8 +43,6 @@ constexpr int kThreads = 192;
 constexpr int kGroupM = 16;   // tile rasterisation: 16 row-tiles share their column tiles in L2
 constexpr unsigned long long kWaitBudgetNs = 1000000000ull;
 
-constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + 256 /*barriers etc.*/ +
-                              4 * kTileN * sizeof(float) /*bias staging, one strip per epilogue warp*/;
 
 __device__ int g_gemm_status = 0;  // 0 ok; otherwise (role << 8) | reason of the first CTA that gave up
 
@@ -308,31 +307,42 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int row, int
 }
 
 // ------------------------------------------------------------------ kernel
+// TN = tile width (256, 128 or 64 columns). Narrow tiles are for problems with too few 128x256 tiles to occupy the
+// SMs: more CTAs, a shorter epilogue per CTA and a deeper ring in the same shared memory.
+template <int TN> struct SingleCfg {
+  static constexpr int kSt = TN == 256 ? 4 : TN == 128 ? 6 : 8;     // ring depth
+  static constexpr int kStB = kAStageBytes + TN * kTileK * 2;        // bytes per stage
+  static constexpr int kTm = 2 * TN;                                 // TMEM columns: two accumulators
+  static constexpr size_t kSmem = 1024 + size_t(kSt) * kStB + 256 + 4 * TN * sizeof(float);
+};
+
+template <int TN>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const GemmParams p) {
+  constexpr int kSt = SingleCfg<TN>::kSt, kStB = SingleCfg<TN>::kStB, kTm = SingleCfg<TN>::kTm;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // 128B swizzle atoms repeat every 1024 B
   uint8_t* base_ptr = smem_raw + (base - raw);
-  const uint32_t bars = base + kStages * kStageBytes;
-  // barrier map (8 B each): full[0..3], empty[0..3], acc_full[0..1], acc_empty[0..1]
-  const uint32_t bar_full = bars, bar_empty = bars + 8 * kStages, bar_acc_full = bars + 16 * kStages,
-                 bar_acc_empty = bars + 16 * kStages + 8 * kAccBufs;
-  uint8_t* misc = base_ptr + kStages * kStageBytes + 16 * kStages + 16 * kAccBufs;
+  const uint32_t bars = base + kSt * kStB;
+  // barrier map (8 B each): full[kSt], empty[kSt], acc_full[0..1], acc_empty[0..1]
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * kSt, bar_acc_full = bars + 16 * kSt,
+                 bar_acc_empty = bars + 16 * kSt + 8 * kAccBufs;
+  uint8_t* misc = base_ptr + kSt * kStB + 16 * kSt + 16 * kAccBufs;
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 4);
-  float* bias_smem = reinterpret_cast<float*>(base_ptr + kStages * kStageBytes + 256);
+  float* bias_smem = reinterpret_cast<float*>(base_ptr + kSt * kStB + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + kTileN - 1) / kTileN;
+  const int tiles_m = (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + TN - 1) / TN;
   const int num_tiles = tiles_m * tiles_n;
   const int k_blocks = (p.K + kTileK - 1) / kTileK;
 
   const bool tl = g_gemm_timeline_on != 0 && blockIdx.x == 0;
   if (tl && threadIdx.x == 0) g_gemm_timeline[0] = global_ns();
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kSt; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
@@ -344,7 +354,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), kTmemCols);
+  if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), kTm);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -362,7 +372,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
         int tm, tn;
         tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
-        const int m0 = tm * kTileM, n0 = tn * kTileN;
+        const int m0 = tm * kTileM, n0 = tn * TN;
         for (int kb = 0; kb < k_blocks; ++kb) {
           const unsigned long long w0 = tl ? global_ns() : 0;
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1)) { alive = false; break; }
@@ -371,9 +381,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (first) { g_gemm_timeline[2] = global_ns(); first = false; }
           }
           const uint32_t full = bar_full + 8 * stage;
-          const uint32_t sa = base + stage * kStageBytes, sb = sa + kAStageBytes;
+          const uint32_t sa = base + stage * kStB, sb = sa + kAStageBytes;
           const int k0 = kb * kTileK;
-          mbar_expect_tx(full, kStageBytes);
+          mbar_expect_tx(full, kStB);
           if (p.a_mn_major) {
             tma_load_2d(sa, &tmap_a, m0, k0, full);
             tma_load_2d(sa + kChunkBytes, &tmap_a, m0 + 64, k0, full);
@@ -382,11 +392,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           if (p.b_mn_major) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) tma_load_2d(sb + j * kChunkBytes, &tmap_b, n0 + 64 * j, k0, full);
+            for (int j = 0; j < TN / 64; ++j) tma_load_2d(sb + j * kChunkBytes, &tmap_b, n0 + 64 * j, k0, full);
           } else {
             tma_load_2d(sb, &tmap_b, k0, n0, full);
           }
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          if (++stage == kSt) { stage = 0; phase ^= 1u; }
         }
       }
       if (tl) g_gemm_timeline[11] = waited;
@@ -409,7 +419,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, 2)) { alive = false; break; }
         if (tl) wait_acc += global_ns() - w0;
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * kTileN;
+        const uint32_t tmem_d = tmem_base + acc * TN;
         for (int kb = 0; kb < k_blocks; ++kb) {
           w0 = tl ? global_ns() : 0;
           if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3)) { alive = false; break; }
@@ -418,14 +428,14 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (first) { g_gemm_timeline[3] = global_ns(); first = false; }
           }
           tc_fence_after();
-          const uint32_t sa = base + stage * kStageBytes, sb = sa + kAStageBytes;
+          const uint32_t sa = base + stage * kStB, sb = sa + kAStageBytes;
           const uint64_t adesc = make_smem_desc(sa, p.a_mn_major);
           const uint64_t bdesc = make_smem_desc(sb, p.b_mn_major);
 #pragma unroll
           for (int k = 0; k < kTileK / kUmmaK; ++k)
             umma_f16(tmem_d, adesc + k * a_step, bdesc + k * b_step, p.idesc, (kb | k) != 0 ? 1u : 0u);
           umma_commit(bar_empty + 8 * stage);  // stage is free once these MMAs have read it
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          if (++stage == kSt) { stage = 0; phase ^= 1u; }
         }
         if (!alive) break;
         umma_commit(bar_acc_full + 8 * acc);   // accumulator complete
@@ -447,7 +457,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
       const int row = tm * kTileM + sub * 32 + lane;
-      const int n0 = tn * kTileN;
+      const int n0 = tn * TN;
       const unsigned long long e0 = tle ? global_ns() : 0;
       // the TMEM loads below are warp-collective: the whole warp proceeds or the whole warp leaves
       if (!__all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, 4))) { alive = false; break; }
@@ -457,18 +467,18 @@ __global__ void __launch_bounds__(kThreads, 1)
         e_wait += e1 - e0;
         if (e_tiles == 0) g_gemm_timeline[5] = e1;
       }
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * kTileN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * TN;
       // bias of this tile's 256 columns -> this warp's private strip of shared memory (no cross-warp barrier,
       // so a warp that gives up on a wait can never leave another one stuck)
-      float* bs = bias_smem + (warp - 2) * kTileN;
+      float* bs = bias_smem + (warp - 2) * TN;
 #pragma unroll
-      for (int h = 0; h < kTileN / 32; ++h) {
+      for (int h = 0; h < TN / 32; ++h) {
         const int col = n0 + lane + 32 * h;
         bs[lane + 32 * h] = (p.bias_dtype != 0 && col < p.N) ? bias_at(p, col) : 0.0f;
       }
       __syncwarp();
 #pragma unroll 1
-      for (int c = 0; c < kTileN / 32; c += 2) {
+      for (int c = 0; c < TN / 32; c += 2) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;  // warp-uniform
         uint32_t r[64];
@@ -505,7 +515,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc(tmem_base, kTm);
   }
   if (tl && threadIdx.x == 0) g_gemm_timeline[8] = global_ns();
 }
@@ -1086,13 +1096,22 @@ Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream) {
 
   // One CTA per tile (128x256) or a CTA pair per 256x256 tile. The pair needs at least two row tiles to have
   // work for both halves. AICF_GEMM_CTA_GROUP=1|2 overrides the choice (tuning and A/B tests).
-  bool pair = p.M > kTileM;
+  // CTA pairs when their 256x256 tiles occupy at least half of the SM pairs; otherwise one CTA per tile with the
+  // widest tile (256, 128, 64 columns) that still gives every SM a tile, or the narrowest when none does.
+  const int64_t pair_tiles_all = ((p.M + 2 * kTileM - 1) / (2 * kTileM)) * ((p.N + kTileN - 1) / kTileN);
+  bool pair = p.M > kTileM && pair_tiles_all * 4 >= sm_count();
   if (const char* e = std::getenv("AICF_GEMM_CTA_GROUP")) {
     if (e[0] == '1') pair = false;
     if (e[0] == '2') pair = true;
   }
+  auto single_tiles = [&](int64_t w) { return ((p.M + kTileM - 1) / kTileM) * ((p.N + w - 1) / w); };
+  int tn = single_tiles(256) >= sm_count() ? 256 : single_tiles(128) >= sm_count() ? 128 : 64;
+  if (const char* e = std::getenv("AICF_GEMM_TILE_N")) {
+    const int v = std::atoi(e);
+    if (v == 256 || v == 128 || v == 64) tn = v;
+  }
   CUtensorMap ta, tb;
-  const uint32_t b_rows = pair ? k2HalfN : kTileN;
+  const uint32_t b_rows = pair ? k2HalfN : static_cast<uint32_t>(tn);
   bool ok_maps = a_major == 0 ? encode_operand(&ta, p.A.data, p.A.dtype, p.K, p.M, p.A.rs, kTileK, kTileM)
                               : encode_operand(&ta, p.A.data, p.A.dtype, p.M, p.K, p.A.cs, 64, kTileK);
   ok_maps = ok_maps && (b_major == 0 ? encode_operand(&tb, p.B.data, p.B.dtype, p.K, p.N, p.B.cs, kTileK, b_rows)
@@ -1119,7 +1138,7 @@ Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream) {
   // instruction descriptor: D=f32 (bits 4-5 = 1), A/B format (bits 7-9 / 10-12), A/B major (bits 15/16),
   // N>>3 (bits 17-22), M>>4 (bits 24-28)
   g.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(a_major) << 15) |
-            (static_cast<uint32_t>(b_major) << 16) | (static_cast<uint32_t>(kTileN >> 3) << 17) |
+            (static_cast<uint32_t>(b_major) << 16) | (static_cast<uint32_t>((pair ? kTileN : tn) >> 3) << 17) |
             (static_cast<uint32_t>((pair ? 2 * kTileM : kTileM) >> 4) << 24);
   const int c_elem = dtype_size_bytes(p.C.dtype);
   g.c_vec_ok = aligned_to(p.C.data, 16) && ((p.C.rs * c_elem) % 16 == 0);
@@ -1164,19 +1183,25 @@ Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream) {
     }
     return launch_status();
   }
-  static bool attr_set[16] = {false};
-  if (!attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(kSmemBytes)) != cudaSuccess) {
-      cudaGetLastError();
-      return Status::Internal;
-    }
-    attr_set[dev] = true;
-  }
-  const int64_t tiles = ((p.M + kTileM - 1) / kTileM) * ((p.N + kTileN - 1) / kTileN);
+  const int64_t tiles = ((p.M + kTileM - 1) / kTileM) * ((p.N + tn - 1) / tn);
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-  gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, g);
-  return launch_status();
+  auto go = [&](auto tag) -> Status {
+    constexpr int TN = decltype(tag)::value;
+    static bool attr_set[16] = {false};
+    if (!attr_set[dev]) {
+      if (cudaFuncSetAttribute(gemm_tcgen05_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(SingleCfg<TN>::kSmem)) != cudaSuccess) {
+        cudaGetLastError();
+        return Status::Internal;
+      }
+      attr_set[dev] = true;
+    }
+    gemm_tcgen05_kernel<TN><<<grid, kThreads, SingleCfg<TN>::kSmem, stream>>>(ta, tb, g);
+    return launch_status();
+  };
+  if (tn == 256) return go(std::integral_constant<int, 256>{});
+  if (tn == 128) return go(std::integral_constant<int, 128>{});
+  return go(std::integral_constant<int, 64>{});
 }
 
 // ------------------------------------------------------------------ 3xTF32 host side

@@ -35,10 +35,14 @@ EPI_KID = {("bf16", "bf16"): "gemm_bias_relu_bf16_tcgen05_out_bf16_v0", ("bf16",
            ("f16", "f16"): "gemm_bias_relu_f16_tcgen05_out_f16_v0", ("f32", "f32"): "gemm_bias_relu_f32_naive_v0"}
 TOL = {"bf16": 2e-2, "f16": 2e-2, "f32": 1e-5}
 
-@pytest.fixture(params=["1", "2"], ids=["cta1", "cta2"])
+@pytest.fixture(params=["1:256", "1:128", "1:64", "2"], ids=["cta1_n256", "cta1_n128", "cta1_n64", "cta2"])
 def cta_group(request, monkeypatch):
-    """Runs a test once with one CTA per tile and once with CTA pairs (tcgen05 cta_group::2)."""
-    monkeypatch.setenv("AICF_GEMM_CTA_GROUP", request.param)
+    """Runs a test with one CTA per tile at each tile width (256, 128, 64 columns) and with CTA pairs (tcgen05
+    cta_group::2); without the overrides the launcher picks by tile count."""
+    group, _, width = request.param.partition(":")
+    monkeypatch.setenv("AICF_GEMM_CTA_GROUP", group)
+    if width:
+        monkeypatch.setenv("AICF_GEMM_TILE_N", width)
     return request.param
 
 

@@ -374,7 +374,7 @@ def run_mlp(args, dist: Dist):
             "gpu_launches": int(plan.graph_kernel_nodes) * args.steps,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None,
-                         "kernel": "gemm_tcgen05_kernel", "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
+                         "kernel": "gemm_tcgen05_2cta_kernel", "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
                          "note": "algorithmic GEMM FLOPs of one step / summed GEMM op times of one eager step"},
             "phase_ms": {k: round(v, 4) for k, v in sorted(by_kid.items(), key=lambda kv: -kv[1])},
             "loss": loss_after, "gemm_status": status, "ms_per_step_fastest_rank": ms_fastest / args.steps,

@@ -192,7 +192,7 @@ __global__ void __launch_bounds__(256)
 // waiting in shared memory while one is being worked on.
 // partial: [gridDim.x][2][N] floats (dgamma partials, then dbeta partials), written only when kAffine.
 template <typename T, int kPackets, bool kAffine>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__((kPackets * (16 / sizeof(T)) > 8) ? 512 : 1024)
     ln_bwd_regs_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ gamma,
                        const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
                        float* __restrict__ partial, int64_t M, int64_t N, int stages) {
@@ -484,11 +484,16 @@ struct BwdGeom {
 
 // Register path: 8 row elements per thread (two fp32 packets or one 16-bit packet), so that x-hat, dy and the two
 // column accumulators fit 64 registers and a 1024-thread block (N up to 8192) still launches; the shared memory
-// an SM has left per resident block is then spent on prefetch depth.
+// an SM has left per resident block is then spent on prefetch depth. Wide 16-bit rows are the exception (below).
 BwdGeom bwd_geom(int64_t M, int64_t N, size_t elem, bool vec_ok) {
   BwdGeom g;
   const int kn = static_cast<int>(16 / elem);
-  const int max_packets = 8 / kn;
+  // 16-bit rows of 4096 elements and more take 16 elements per thread (two packets, ~107 registers, 512-thread
+  // blocks at most): these kernels are bound by instruction issue, and the per-row overhead (barriers, shuffles, loop
+  // control) is then spread over twice the elements (4096 columns: 0.67 -> 0.78 of the copy rate). Narrower rows
+  // lose more from the halved number of resident blocks than they gain.
+  const bool wide = elem == 2 && N % kn == 0 && N / kn >= 512;
+  const int max_packets = wide ? 2 : 8 / kn;
   const int64_t col_blocks = (N + 127) / 128;
   int64_t sl = (static_cast<int64_t>(sm_count()) * 8) / col_blocks;
   sl = sl < 1 ? 1 : sl;
@@ -496,11 +501,11 @@ BwdGeom bwd_geom(int64_t M, int64_t N, size_t elem, bool vec_ok) {
   if (!vec_ok || N % kn != 0) return g;
   const int64_t np = N / kn;
   int threads = 128;
-  while (threads < 1024 && static_cast<int64_t>(threads) * max_packets < np) threads *= 2;
+  while (threads < (wide ? 512 : 1024) && static_cast<int64_t>(threads) * max_packets < np) threads *= 2;
   const int64_t per = (np + threads - 1) / threads;
   if (per > max_packets) return g;
   const size_t slot = static_cast<size_t>(2 * N * elem);
-  const int resident = 1024 / threads;  // 64 registers per thread: 1024 threads' worth of blocks share an SM
+  const int resident = (wide ? 512 : 1024) / threads;  // blocks that fit the register file (64 or ~107 registers per thread)
   const size_t budget = (227 * 1024) / static_cast<size_t>(resident) - 1024;
   int stages = static_cast<int>((budget - 64) / slot);
   stages = stages > 4 ? 4 : stages;
@@ -590,7 +595,7 @@ Status ln_bwd_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, cons
   } else {
     if (g.packets == 1) st = ln_bwd_go<T, 1>(affine, g, stream, x, dy, gamma, mean, rstd, dx, partial, M, N);
     else if constexpr (sizeof(T) == 4) st = ln_bwd_go<T, 2>(affine, g, stream, x, dy, gamma, mean, rstd, dx, partial, M, N);
-    else st = Status::Internal;  // 16-bit rows never ask for two packets (bwd_geom caps them at one)
+    else st = ln_bwd_go<T, 2>(affine, g, stream, x, dy, gamma, mean, rstd, dx, partial, M, N);
   }
   if (st != Status::Ok || !affine) return st;
   ln_bwd_finish_kernel<<<static_cast<unsigned>((2 * N + 31) / 32), dim3(32, 32), 0, stream>>>(

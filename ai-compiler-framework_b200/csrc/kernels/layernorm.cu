@@ -500,12 +500,13 @@ BwdGeom bwd_geom(int64_t M, int64_t N, size_t elem, bool vec_ok) {
   g.slices = static_cast<int>(sl < M ? sl : M);
   if (!vec_ok || N % kn != 0) return g;
   const int64_t np = N / kn;
-  int threads = 128;
+  int threads = 32;
   while (threads < (wide ? 512 : 1024) && static_cast<int64_t>(threads) * max_packets < np) threads *= 2;
   const int64_t per = (np + threads - 1) / threads;
   if (per > max_packets) return g;
   const size_t slot = static_cast<size_t>(2 * N * elem);
-  const int resident = (wide ? 512 : 1024) / threads;  // blocks that fit the register file (64 or ~107 registers per thread)
+  int resident = (wide ? 512 : 1024) / threads;  // blocks that fit the register file (64 or ~107 registers per thread)
+  resident = resident > 32 ? 32 : resident;
   const size_t budget = (227 * 1024) / static_cast<size_t>(resident) - 1024;
   int stages = static_cast<int>((budget - 64) / slot);
   stages = stages > 4 ? 4 : stages;

@@ -94,9 +94,13 @@ struct RowCfg {
 };
 // max_packets bounds the registers a thread spends on the row: 8 packets of fp32 or 4 packets of a
 // 16-bit type are 32 floats after unpacking, which fits the 64-register budget of a 1024-thread block.
+// Blocks start at one warp and grow only while a thread would hold more than four packets: a narrow row is then a
+// warp's job (its "block" barriers cost nothing and up to 32 such blocks share an SM) instead of leaving most of a
+// 128-thread block idle. Measured on [65536,1024]: bf16 softmax 0.65 -> 0.91 of the copy rate, f32 0.86 -> 0.94,
+// f32 cross-entropy 0.74 -> 0.91; on [262144,256] f32 softmax 0.51 -> 0.92.
 inline RowCfg pick_row_cfg(int64_t n_packets, int max_packets) {
   RowCfg c;
-  int threads = 128;
+  int threads = 32;
   while (threads < 1024 && static_cast<int64_t>(threads) * 4 < n_packets) threads *= 2;
   const int64_t per = (n_packets + threads - 1) / threads;
   c.threads = threads;
@@ -114,7 +118,7 @@ inline int row_pipe_blocks_per_sm(int threads, size_t smem) {
   int by_threads = 2048 / threads;
   int by_smem = static_cast<int>((227 * 1024) / (smem + 1024));
   int b = by_threads < by_smem ? by_threads : by_smem;
-  return b < 1 ? 1 : (b > 16 ? 16 : b);
+  return b < 1 ? 1 : (b > 32 ? 32 : b);
 }
 
 template <typename K>

@@ -13,6 +13,7 @@ namespace aicf::cuda {
 int gemm_tcgen05_status(bool clear);
 int row_pipeline_status(bool clear);
 int layernorm_pipeline_status(bool clear);
+int adam_pipeline_status(bool clear);
 int gemm_tcgen05_timeline(int enable, unsigned long long* out16);
 int dp_wait_status(bool clear);
 }
@@ -242,9 +243,10 @@ int aicf_b200_wait_status(int clear) {
   const int g = aicf::cuda::gemm_tcgen05_status(clear != 0);
   const int rs = aicf::cuda::row_pipeline_status(clear != 0);
   const int rl = aicf::cuda::layernorm_pipeline_status(clear != 0);
+  const int ra = aicf::cuda::adam_pipeline_status(clear != 0);
   const int d = aicf::cuda::dp_wait_status(clear != 0);
-  if (g < 0 || rs < 0 || rl < 0 || d < 0) return -1;
-  const int r = rs | rl;
+  if (g < 0 || rs < 0 || rl < 0 || ra < 0 || d < 0) return -1;
+  const int r = rs | rl | ra;
   return (g & 0xFFFF) | (r ? 0x10000 : 0) | ((d & 3) << 17);
 }
 

@@ -6,6 +6,7 @@
 // one launch covers any size (the reference caps its grid at 65535 blocks of scalar accesses).
 #include "adam_math.cuh"
 #include "common.cuh"
+#include "sm100_async.cuh"
 
 namespace aicf::cuda {
 
@@ -131,6 +132,104 @@ __global__ void __launch_bounds__(256) adam_kernel(AdamArgs a) {
   }
 }
 
+// ---- large arrays: the four input streams arrive by bulk asynchronous copies -------------------------------------
+// A block works on chunks of kBulkChunk floats per array. One thread keeps a ring of kBulkStages chunks in flight
+// (four cp.async.bulk per chunk, one mbarrier); all threads take their packets of an arrived chunk out of shared
+// memory, a single barrier frees the slot for the next copy, and the update is computed and stored from registers.
+// Compared with per-thread 16-byte loads this keeps many KiB per SM in flight with no registers or issue slots spent
+// on it. Waits are bounded; a wait that runs out ends the block and sets g_adam_status.
+constexpr int kBulkThreads = 256;
+constexpr int kBulkPackets = 4;                                   // 16-byte packets per thread per array per chunk
+constexpr int kBulkChunk = kBulkThreads * kBulkPackets * 4;       // floats per array per chunk (16 KiB)
+constexpr int kBulkStages = 3;
+constexpr uint32_t kBulkArrayBytes = kBulkChunk * 4;
+constexpr size_t kBulkSmem = size_t(kBulkStages) * 4 * kBulkArrayBytes + 8 * kBulkStages + 16;
+constexpr unsigned long long kBulkWaitBudgetNs = 1000000000ull;
+__device__ int g_adam_status = 0;
+
+template <bool kDivisorScalars, int kLp>
+__global__ void __launch_bounds__(kBulkThreads) adam_bulk_kernel(AdamArgs a, int64_t nchunks) {
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ int wait_failed;
+  float d1, d2;
+  if (kDivisorScalars) {
+    d1 = a.bc1[0];
+    d2 = a.bc2[0];
+  } else {
+    int t = a.step[0];
+    if (t < 1) t = 1;
+    d1 = static_cast<float>(1.0 - pow(static_cast<double>(a.h.beta1), static_cast<double>(t)));
+    d2 = static_cast<float>(1.0 - pow(static_cast<double>(a.h.beta2), static_cast<double>(t)));
+  }
+  using V4 = Pack16<float>;
+  const uint32_t buf0 = sm100::smem_addr(ring);
+  const uint32_t bar0 = buf0 + kBulkStages * 4 * kBulkArrayBytes;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kBulkStages; ++s) sm100::mbar_init(bar0 + 8u * s, 1);
+    sm100::mbar_init_fence();
+    wait_failed = 0;
+  }
+  __syncthreads();
+  auto fetch = [&](int64_t chunk, int slot) {  // thread 0 only
+    const uint32_t bar = bar0 + 8u * slot, buf = buf0 + static_cast<uint32_t>(slot) * 4 * kBulkArrayBytes;
+    const int64_t off = chunk * kBulkChunk;
+    sm100::mbar_expect_tx(bar, 4 * kBulkArrayBytes);
+    sm100::bulk_copy_g2s(buf, a.p + off, kBulkArrayBytes, bar);
+    sm100::bulk_copy_g2s(buf + kBulkArrayBytes, a.g + off, kBulkArrayBytes, bar);
+    sm100::bulk_copy_g2s(buf + 2 * kBulkArrayBytes, a.m + off, kBulkArrayBytes, bar);
+    sm100::bulk_copy_g2s(buf + 3 * kBulkArrayBytes, a.v + off, kBulkArrayBytes, bar);
+  };
+  if (threadIdx.x == 0)
+    for (int s = 0; s < kBulkStages; ++s) {
+      const int64_t c = blockIdx.x + static_cast<int64_t>(s) * gridDim.x;
+      if (c < nchunks) fetch(c, s);
+    }
+  int slot = 0;
+  uint32_t parity = 0;
+  for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+    if (!sm100::mbar_wait_bounded(bar0 + 8u * slot, parity, kBulkWaitBudgetNs)) wait_failed = 1;
+    const V4* sp = reinterpret_cast<const V4*>(ring + static_cast<size_t>(slot) * 4 * kBulkArrayBytes);
+    V4 p[kBulkPackets], g[kBulkPackets], m[kBulkPackets], v[kBulkPackets];
+#pragma unroll
+    for (int u = 0; u < kBulkPackets; ++u) {
+      const int j = threadIdx.x + u * kBulkThreads;
+      p[u] = sp[j];
+      g[u] = sp[kBulkChunk / 4 + j];
+      m[u] = sp[2 * (kBulkChunk / 4) + j];
+      v[u] = sp[3 * (kBulkChunk / 4) + j];
+    }
+    __syncthreads();  // every thread holds its packets: the slot may be refilled; the flag is seen by all
+    if (wait_failed) {
+      if (threadIdx.x == 0) atomicExch(&g_adam_status, 1);
+      break;
+    }
+    if (threadIdx.x == 0) {
+      const int64_t ahead = c + static_cast<int64_t>(kBulkStages) * gridDim.x;
+      if (ahead < nchunks) {
+        sm100::fence_generic_to_async_smem();
+        fetch(ahead, slot);
+      }
+    }
+    const int64_t base = c * (kBulkChunk / 4);
+#pragma unroll
+    for (int u = 0; u < kBulkPackets; ++u) {
+      const int64_t j = base + threadIdx.x + u * kBulkThreads;
+      V4 po, mo, vo;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        adam_one<kDivisorScalars>(p[u].v[e], g[u].v[e], m[u].v[e], v[u].v[e], a.h, d1, d2, po.v[e], mo.v[e], vo.v[e]);
+      st_stream(reinterpret_cast<V4*>(a.m_out) + j, mo);
+      st_stream(reinterpret_cast<V4*>(a.v_out) + j, vo);
+      st_stream(reinterpret_cast<V4*>(a.p_out) + j, po);
+      if (kLp) store_lp_x4<kLp>(a.p_lp, j, po);
+    }
+    if (++slot == kBulkStages) {
+      slot = 0;
+      parity ^= 1u;
+    }
+  }
+}
+
 template <bool kDiv, int kLp>
 Status launch_adam(AdamArgs a, cudaStream_t stream) {
   if (a.n <= 0) return Status::Ok;
@@ -138,6 +237,28 @@ Status launch_adam(AdamArgs a, cudaStream_t stream) {
   bool vec_ok = true;
   for (const void* q : ptrs) vec_ok = vec_ok && aligned_to(q, 16);
   if (kLp) vec_ok = vec_ok && aligned_to(a.p_lp, 8);
+  // Whole chunks of a large, aligned array go through the bulk-copy kernel; the rest (and small or unaligned
+  // arrays) through the per-thread-load kernel below.
+  const int64_t nchunks = vec_ok ? a.n / kBulkChunk : 0;
+  if (nchunks >= 2 * static_cast<int64_t>(sm_count())) {
+    static bool attr_ok = cudaFuncSetAttribute(adam_bulk_kernel<kDiv, kLp>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(kBulkSmem)) == cudaSuccess;
+    if (attr_ok) {
+      const int per_sm = static_cast<int>((227 * 1024) / (kBulkSmem + 1024));
+      const int grid = streaming_grid(nchunks, 1, per_sm);
+      cudaGetLastError();
+      adam_bulk_kernel<kDiv, kLp><<<grid, kBulkThreads, kBulkSmem, stream>>>(a, nchunks);
+      if (launch_status() != Status::Ok) return Status::Internal;
+      const int64_t done = nchunks * kBulkChunk;
+      if (done == a.n) return Status::Ok;
+      a.p += done; a.g += done; a.m += done; a.v += done;
+      a.p_out += done; a.m_out += done; a.v_out += done;
+      if (kLp) a.p_lp = static_cast<uint8_t*>(a.p_lp) + done * 2;
+      a.n -= done;
+    } else {
+      cudaGetLastError();
+    }
+  }
   a.nvec = vec_ok ? (a.n >> 2) : 0;
   constexpr int kThreads = 256;
   const int64_t items = vec_ok ? (a.nvec / 2 + 1) : a.n;
@@ -363,6 +484,20 @@ KernelVariant make(const char* name, uint32_t schema_gate,
 }
 
 }  // namespace
+
+// Reads (optionally clears) the status word of the bulk-copy Adam kernel's bounded waits. Synchronises the device.
+int adam_pipeline_status(bool clear) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_adam_status, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (clear && v != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_adam_status, &zero, sizeof(int));
+  }
+  return v;
+}
 
 KernelVariant make_adam_step_f32_variant() { return make("adam_step_f32_sm100", schema::kAdam, adam_v0_launch, adam_v0_supported); }
 KernelVariant make_adam_step_f32_fused_variant() { return make("adam_step_f32_fused_sm100", schema::kAdam, adam_v1_launch, adam_v1_supported); }

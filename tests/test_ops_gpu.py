@@ -66,7 +66,8 @@ def test_adam_v0_rejects_what_the_reference_rejects(gpu):
         by_id("adam_step_f32_v0", OpKind.AdamStep, [P, G, M, V, one, one], [P, M, V], ADAM, pay)
 
 
-@pytest.mark.parametrize("n", [1, 3, 1001, 4096, 1 << 20])
+# 4096 * 300 + 1001: past the size where whole 16 KiB chunks go through the bulk-copy kernel, with a ragged tail
+@pytest.mark.parametrize("n", [1, 3, 1001, 4096, 1 << 20, 4096 * 300 + 1001, 1 << 22])
 @pytest.mark.parametrize("wd,dec", [(0.0, 0), (0.01, 0), (0.01, 1)])
 def test_adam_fused_step_counter_weight_decay_and_bf16_copy(gpu, n, wd, dec):
     p, g = oracle.adam_inputs(n, seed=3)
@@ -81,6 +82,22 @@ def test_adam_fused_step_counter_weight_decay_and_bf16_copy(gpu, n, wd, dec):
     assert_close_f32(host(M), wm, atol=1e-9, what="m")   # operands ~1e-3: atol = 1e-6 x scale
     assert_close_f32(host(V), wv, atol=1e-12, what="v")  # operands ~1e-6
     assert np.array_equal(lp.numpy(), f32_to_bf16_bits(P.numpy()))  # bf16 copy is the rounded new parameter
+
+
+def test_adam_v0_large_out_of_place_uses_the_bulk_copy_kernel(gpu):
+    n = 4096 * 320 + 8
+    p, g, m, v = rnd((n,), 1), rnd((n,), 2, 1e-2), rnd((n,), 3, 1e-2), np.abs(rnd((n,), 4, 1e-3))
+    bc1, bc2 = 1 - 0.9 ** 3, 1 - 0.999 ** 3
+    P, G, M, V = dev(p), dev(g), dev(m), dev(v)
+    Po, Mo, Vo = Tensor.zeros((n,)), Tensor.zeros((n,)), Tensor.zeros((n,))
+    by_id("adam_step_f32_v0", OpKind.AdamStep, [P, G, M, V, scalar(bc1), scalar(bc2)], [Po, Mo, Vo], ADAM,
+          struct.pack("<ffff", 1e-3, 0.9, 0.999, 1e-8))
+    wp, wm, wv = oracle.adam_step_v0(p, g, m, v, F(bc1), F(bc2), F(1e-3), F(0.9), F(0.999), F(1e-8))
+    assert_close_f32(host(Po), wp, what="p")
+    assert_close_f32(host(Mo), wm, atol=1e-8, what="m")
+    assert_close_f32(host(Vo), wv, atol=1e-9, what="v")
+    assert np.array_equal(host(P), p), "inputs untouched out of place"
+    assert _C.wait_status() == 0
 
 
 def test_adam_fused_unaligned_views_take_the_scalar_path(gpu):

@@ -552,6 +552,38 @@ def apply_opt_rules(ir: Optional[IRGraph], lowered: Sequence[LoweredOp]) -> List
     return out
 
 
+def elide_saved_copies(ir: Optional[IRGraph], lowered: Sequence[LoweredOp]) -> List[LoweredOp]:
+    """Drops every `copy_saved (src) -> (saved)` whose source is not written again before the last read of `saved`,
+    and lets those reads use `src` directly. In the reference's lowering the activation saved for relu_bwd is a
+    second full-size copy of a value that stays alive and unchanged until the backward pass
+    (README_stage6.md:340-359 lists this as pending work); the copy is one read and one write of the activation per
+    hidden layer. Not part of compile_lowered(): the reference's lowered list keeps the copies."""
+    out: List[LoweredOp] = [dict(it) for it in lowered]
+    remap: Dict[int, int] = {}
+    keep = [True] * len(out)
+    for i, it in enumerate(out):
+        if _opname(it) != "copy_saved" or len(it.get("inputs", [])) != 1 or len(it.get("outputs", [])) != 1:
+            continue
+        src, saved = int(it["inputs"][0]), int(it["outputs"][0])
+        if src == saved:
+            continue
+        readers = [j for j in range(i + 1, len(out)) if saved in [int(v) for v in out[j].get("inputs", [])]]
+        last_read = max(readers) if readers else i
+        rewritten = any(src in [int(v) for v in out[j].get("outputs", [])] or saved in [int(v) for v in out[j].get("outputs", [])]
+                        for j in range(i + 1, last_read + 1))
+        if rewritten:
+            continue
+        keep[i] = False
+        remap[saved] = src
+    result: List[LoweredOp] = []
+    for flag, it in zip(keep, out):
+        if not flag:
+            continue
+        it["inputs"] = [remap.get(int(v), int(v)) for v in it.get("inputs", [])]
+        result.append(it)
+    return result
+
+
 def compile_lowered(ir: IRGraph, *, fuse: bool = True, pin_kernel_ids: bool = True) -> List[LoweredOp]:
     """The stages in the order the reference's end-to-end test runs them: A, B, C, then dtype-based ids for
     every op that is still without one."""
@@ -863,7 +895,7 @@ __all__ = [
     "SymTensor", "sym_tensor", "linear", "relu", "save", "mse_grad", "linear_bwd", "relu_bwd", "step_inc", "bias_corr",
     "adam_step", "sgd_step", "softmax_ce_grad",
     "lower_to_backend_ops", "pick_kernel_id", "apply_kernel_selection", "apply_kernel_decisions_stageB",
-    "stageC_fuse_gemm_epilogue", "apply_opt_rules", "compile_lowered",
+    "stageC_fuse_gemm_epilogue", "apply_opt_rules", "compile_lowered", "elide_saved_copies",
     "BindSpec", "BindingPlan", "PlanOptions", "build_binding_plan", "ROLE_INPUT", "ROLE_PARAM", "ROLE_STATIC",
     "dump_ir", "dump_lowered", "dump_plan", "ExecOptions", "PlannedExecutor", "opkind_from_name", "short_dtype", "long_dtype",
 ]

@@ -124,6 +124,22 @@ def test_fusion_rules():
     assert [it["op"] for it in cv.stageC_fuse_gemm_epilogue(None, [g, bias, cp, act])] == ["gemm", "bias_add", "copy", "relu"]
 
 
+def test_saved_activation_copies_can_be_elided():
+    low = cv.elide_saved_copies(None, FIX["lowered"])
+    assert len(low) == len(FIX["lowered"]) - 1 and all(it["op"] != "copy_saved" for it in low)
+    relu_bwd = [it for it in low if it["op"] == "relu_bwd"][0]
+    assert relu_bwd["inputs"] == [11, 4]                                   # reads relu0_out itself, not its copy
+    assert FIX["lowered"][8]["inputs"] == [11, 5]                          # the input list was not modified
+    # a source that is overwritten before the saved value is read keeps its copy
+    ops = [{"op": "copy_saved", "inputs": [1], "outputs": [2], "attrs": {}},
+           {"op": "relu", "inputs": [1], "outputs": [1], "attrs": {}},
+           {"op": "relu_bwd", "inputs": [3, 2], "outputs": [4], "attrs": {}}]
+    assert cv.elide_saved_copies(None, ops) == ops
+    # ... while one that is overwritten only after the last read does not
+    ops2 = [ops[0], ops[2], ops[1]]
+    assert [it["op"] for it in cv.elide_saved_copies(None, ops2)] == ["relu_bwd", "relu"]
+
+
 def test_tracing_rules_and_errors():
     with pytest.raises(RuntimeError, match="tracing-only"):
         cv.relu(cv.sym_tensor(name="x", shape=(2, 2), dtype="f32"))
@@ -207,6 +223,23 @@ def test_executor_runs_the_fixture_model_like_the_reference(gpu):
         np.testing.assert_allclose(env[vid].float_numpy(), ref[vid], rtol=4e-3, atol=2e-3, err_msg=name)
     # parameters were updated in place, in the caller's tensors
     assert not np.array_equal(params["0.W"].numpy(), h_par["0.W"])
+
+
+@pytest.mark.gpu
+def test_executor_with_elided_copies_gives_the_same_parameters(gpu):
+    from aicf_cuda import Tensor
+    ir = traced()
+    h_in, h_par = _host_inputs(2)
+    results = []
+    for lowered in (cv.compile_lowered(ir), cv.elide_saved_copies(ir, cv.compile_lowered(ir))):
+        ex = cv.PlannedExecutor(ir=ir, lowered=lowered, plan=cv.build_binding_plan(ir))
+        params = {k: Tensor.from_numpy(v) for k, v in h_par.items()}
+        for _ in range(2):
+            ex.run(inputs={k: Tensor.from_numpy(v) for k, v in h_in.items()}, params=params, reuse_static=False)
+        ex.sync()
+        results.append({k: v.numpy() for k, v in params.items()})
+    for k in results[0]:
+        np.testing.assert_array_equal(results[0][k], results[1][k], err_msg=k)
 
 
 @pytest.mark.gpu

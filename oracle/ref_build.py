@@ -1,7 +1,10 @@
 """Compiles the REFERENCE's own CUDA op backend, unmodified and from where its sources lie, into
 oracle/_ref/libaicf_ref.so for sm_100a. TEST INFRASTRUCTURE.
 
-    python oracle/ref_build.py [--reference /root/reference/ai-compiler-framework]
+    python oracle/ref_build.py [--reference <reference checkout>/ai-compiler-framework]
+
+Without --reference the tree is looked for in $AICF_REFERENCE_DIR, then in a `reference/` directory next to this
+repository.
 
 Only the reference's op launchers, registry.cpp and register_all.cpp are compiled (plain nvcc on the
 files; the reference's CMake project is not run), together with oracle/ref_shim.cpp, which adds C
@@ -13,6 +16,7 @@ from __future__ import annotations
 
 import argparse
 import concurrent.futures as cf
+import os
 import shutil
 import subprocess
 import sys
@@ -20,7 +24,7 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
-DEFAULT_REF = Path("/root/reference/ai-compiler-framework")
+DEFAULT_REF = Path(os.environ.get("AICF_REFERENCE_DIR") or HERE.parent.parent / "reference" / "ai-compiler-framework")
 GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

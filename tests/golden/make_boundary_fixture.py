@@ -1,6 +1,6 @@
 """Turns the reference's committed boundary dumps into tests/golden/boundary_fixture.json.
 
-    python tests/golden/make_boundary_fixture.py [--reference /root/reference/ai-compiler-framework]
+    python tests/golden/make_boundary_fixture.py [--reference <reference checkout>/ai-compiler-framework]
 
 Source: artifacts/20260128_222814_v2_kid_trace_by_id_test/{20_ir,30_lowered,40_plan,50_runtime_trace}.txt, the
 output of the reference's own python_framework_test/v2_kid_trace_by_id_test.py (a 2-layer f16 MLP,
@@ -11,6 +11,7 @@ and the three text dumps verbatim (they pin the printer's line formats).
 from __future__ import annotations
 
 import argparse
+import os
 import ast
 import json
 import re
@@ -69,7 +70,7 @@ def parse_ir_nodes(text: str):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", type=Path, default=Path("/root/reference/ai-compiler-framework"))
+    ap.add_argument("--reference", type=Path, default=Path(os.environ.get("AICF_REFERENCE_DIR") or HERE.parents[2] / "reference" / "ai-compiler-framework"))
     a = ap.parse_args()
     d = a.reference / ART
     fixture = {

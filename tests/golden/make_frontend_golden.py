@@ -1,6 +1,6 @@
 """Traces tests/frontend_models.py's models through the REFERENCE's core_v2 front end and records every stage.
 
-    python tests/golden/make_frontend_golden.py [--reference /root/reference/ai-compiler-framework]
+    python tests/golden/make_frontend_golden.py [--reference <reference checkout>/ai-compiler-framework]
 
 Needs the reference checkout and torch; no GPU. The reference's executor module imports `aicf_cuda._C` at
 import time, which resolves to this repository's binding module (nothing is launched). Per model the JSON
@@ -11,6 +11,7 @@ kernel_select, the binding-plan dump, and the lowered dump text.
 from __future__ import annotations
 
 import argparse
+import os
 import json
 import sys
 from pathlib import Path
@@ -21,7 +22,7 @@ REPO = HERE.parents[1]
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", type=Path, default=Path("/root/reference/ai-compiler-framework"))
+    ap.add_argument("--reference", type=Path, default=Path(os.environ.get("AICF_REFERENCE_DIR") or HERE.parents[2] / "reference" / "ai-compiler-framework"))
     a = ap.parse_args()
     # The reference's python directory goes first: this repository ships an `aicf_fw.core_v2` import shim of its own
     # (both `aicf_fw` directories are namespace portions, so path order decides).

@@ -333,6 +333,20 @@ int aicf_b200_device_count(void) {
   return n;
 }
 int aicf_b200_set_device(int device) { return check_cuda(cudaSetDevice(device), "cudaSetDevice"); }
+int aicf_b200_device_info(int device, int64_t* l2_bytes, int* sm_count, int64_t* total_bytes) {
+  int l2 = 0, sms = 0;
+  if (int rc = check_cuda(cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, device), "cudaDeviceGetAttribute(L2)")) return rc;
+  if (int rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute(SMs)"))
+    return rc;
+  if (l2_bytes) *l2_bytes = l2;
+  if (sm_count) *sm_count = sms;
+  if (total_bytes) {
+    cudaDeviceProp prop{};
+    if (int rc = check_cuda(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties")) return rc;
+    *total_bytes = static_cast<int64_t>(prop.totalGlobalMem);
+  }
+  return AICF_OK;
+}
 int aicf_b200_malloc(void** ptr, size_t bytes) {
   if (!ptr) return fail(Status::InvalidArgument, "malloc: null out pointer");
   return check_cuda(cudaMalloc(ptr, bytes ? bytes : 1), "cudaMalloc");

@@ -44,6 +44,15 @@ ADAM = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8)
 
 
 # ------------------------------------------------------------------------------------------ helpers
+def device_info(lib, device=0):
+    """L2 size, SM count and memory size of `device`, for the result line."""
+    import ctypes as C
+    l2, sms, mem = C.c_int64(0), C.c_int(0), C.c_int64(0)
+    if lib.aicf_b200_device_info(int(device), C.byref(l2), C.byref(sms), C.byref(mem)) != 0:
+        return {}
+    return {"l2_bytes": l2.value, "sm_count": sms.value, "memory_bytes": mem.value}
+
+
 def measured_peaks():
     p = REPO / "MEASURED_PEAKS.json"
     if p.exists():
@@ -366,7 +375,7 @@ def run_mlp(args, dist: Dist):
                        "gradient_exchange": ("none" if world == 1 else "dp_adam_step over NVLink peer memory" if args.dp_mode == "fused"
                                              else "NCCL all-reduce"),
                        "l2": "working set (>10 GB per step) far exceeds the 126 MB L2; no flush needed"},
-            "clocks": clocks.summary(),
+            "clocks": clocks.summary(), "device": device_info(lib, local_rank),
             "e2e": {"value": gbatch / (e2e_ms / e2e_steps * 1e-3), "unit": "samples/s",
                     "h2d_bytes_per_step": int(x_host.nbytes + y_host.nbytes), "d2h_bytes_per_step": 4, "steps": e2e_steps,
                     "note": "every step: pinned host X (fp32) + labels copied in on a copy stream (double-buffered, overlaps the "
@@ -455,7 +464,7 @@ def run_mlp_c1(args):
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
            "config": {"workload": "mlp_784_256_10_batch64", "kernels_per_step": plan.graph_kernel_nodes,
                       "l2": "3.3 MB working set: L2-resident by nature (latency-bound configuration)"},
-           "clocks": clocks.summary(), "gpu_launches": plan.graph_kernel_nodes * reps * args.steps,
+           "clocks": clocks.summary(), "device": device_info(aicf_cuda.lib), "gpu_launches": plan.graph_kernel_nodes * reps * args.steps,
            "roofline": {"bound": "latency", "achieved": flops / (ms * 1e-3) / 1e12, "peak": None, "unit": "TFLOP/s", "frac": None,
                         "traffic": None, "note": f"{plan.graph_kernel_nodes} dependent kernels per step; time is launch + drain latency"},
            "cpu_baseline": {"value": batch / cpu_s, "unit": "samples/s", "cores": blas_threads(), "kind": "port",
@@ -608,7 +617,7 @@ def run_kernel_workload(args):
     out = {"metric": metric, "value": achieved, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
            "ms_per_step": ms, "ms_min": min(times), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
            "dtype": cfg["workload"].split("_")[-1], "data": "synthetic", "config": cfg, "clocks": clocks,
-           "gpu_launches": args.steps * launches_per_step,
+           "device": device_info(lib), "gpu_launches": args.steps * launches_per_step,
            "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
                         "frac": (achieved / peak) if peak else None, "traffic": None, "peak_source": peaks["source"]},
            "gemm_status": _C.wait_status()}

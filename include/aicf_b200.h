@@ -153,6 +153,9 @@ aicf_stream aicf_b200_graph_stream(void); /* 0 before the first graph_begin */
  * these are thin wrappers over the CUDA runtime. */
 int aicf_b200_device_count(void);
 int aicf_b200_set_device(int device);
+/* Facts about a device that sizing decisions and benchmark reports need: L2 cache bytes, SM count, total global
+ * memory bytes (any pointer may be NULL). What a torch user reads from torch.cuda.get_device_properties. */
+int aicf_b200_device_info(int device, int64_t* l2_bytes, int* sm_count, int64_t* total_bytes);
 int aicf_b200_malloc(void** ptr, size_t bytes);
 int aicf_b200_free(void* ptr);
 int aicf_b200_host_alloc_pinned(void** ptr, size_t bytes);

@@ -19,8 +19,9 @@ LNEP = 0x50454E4C
 ROUND = {"f32": lambda a: np.asarray(a, np.float32), "f16": oracle.f16_round, "bf16": oracle.bf16_round}
 EPS_OUT = {"f32": 1e-5, "f16": 1.0e-3, "bf16": 7.9e-3}  # relative rounding step of the output type (f32: the tolerance)
 
+# (8,128), (64,256), (7,33) are the shapes of the reference's own layer-norm probe script
 SHAPES = [(64, 1024), (33, 4096), (16, 8192), (8, 16384), (4, 20000), (5, 1001), (7, 3), (1, 256), (300, 64), (2, 40000),
-          (129, 768)]
+          (129, 768), (8, 128), (64, 256), (7, 33)]
 
 
 def make(M, N, dt, seed=0, offset=0.5):
@@ -155,7 +156,7 @@ def test_layernorm_backward_is_deterministic(gpu):
         assert np.array_equal(u, v)
 
 
-@pytest.mark.parametrize("M,N", [(64, 256), (37, 96), (128, 1024), (5, 1001)])
+@pytest.mark.parametrize("M,N", [(64, 256), (37, 96), (128, 1024), (5, 1001), (8, 128), (7, 33), (16, 4096)])
 @pytest.mark.parametrize("dt", ["f32", "f16"])
 def test_layernorm_vs_reference_kernels(ref_lib, M, N, dt):
     x, dy, gamma, beta = make(M, N, dt, seed=11)

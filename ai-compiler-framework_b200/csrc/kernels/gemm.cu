@@ -103,8 +103,10 @@ template <int kId>
 size_t tf32x3_workspace(const TensorDesc* in, int ni, const void* attr) {
   if (!in || ni < 2 || in[0].rank() != 2 || in[1].rank() != 2) return 0;
   bool ta, tb, relu;
-  if (Contracts<kId>::value.bias == BiasRule::None) read_gemm_attr(attr, &ta, &tb);
-  else read_gemm_epilogue_attr(attr, &ta, &tb, &relu);
+  if (Contracts<kId>::value.bias == BiasRule::None || Contracts<kId>::value.bias == BiasRule::ReluBwdMask)
+    read_gemm_attr(attr, &ta, &tb);
+  else
+    read_gemm_epilogue_attr(attr, &ta, &tb, &relu);
   GemmProblem p;
   p.A = view_of(in[0], ta);
   p.B = view_of(in[1], tb);
@@ -166,6 +168,7 @@ KernelVariant make_gemm_bias_relu_f16_tcgen05_out_f16_variant() { return variant
 
 KernelVariant make_gemm_f32_3xtf32_variant() { return tf32x3_variant<0>("gemm_f32_3xtf32_tcgen05"); }
 KernelVariant make_gemm_bias_relu_f32_3xtf32_variant() { return tf32x3_variant<10>("gemm_bias_relu_f32_3xtf32_tcgen05"); }
+KernelVariant make_gemm_relu_bwd_f32_3xtf32_variant() { return tf32x3_variant<22>("gemm_relu_bwd_f32_3xtf32_tcgen05"); }
 
 KernelVariant make_gemm_relu_bwd_bf16_variant() { return variant<20>("gemm_relu_bwd_bf16_tcgen05"); }
 KernelVariant make_gemm_relu_bwd_f16_variant() { return variant<21>("gemm_relu_bwd_f16_tcgen05"); }

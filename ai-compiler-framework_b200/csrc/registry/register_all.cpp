@@ -62,6 +62,7 @@ KernelVariant make_reduce_mean_lastaxis_f16_variant();
 // softmax.cu
 KernelVariant make_gemm_f32_3xtf32_variant();
 KernelVariant make_gemm_bias_relu_f32_3xtf32_variant();
+KernelVariant make_gemm_relu_bwd_f32_3xtf32_variant();
 KernelVariant make_layernorm_fwd_f32_variant();
 KernelVariant make_layernorm_fwd_f16_variant();
 KernelVariant make_layernorm_fwd_bf16_variant();
@@ -188,6 +189,7 @@ extern "C" void aicf_cuda_register_all_kernels() {
       {K::GemmReluBwd, make_gemm_relu_bwd_bf16_variant, 20, "gemm_relu_bwd_bf16_tcgen05_out_bf16_v0"},
       {K::GemmReluBwd, make_gemm_relu_bwd_f16_variant, 10, "gemm_relu_bwd_f16_tcgen05_out_f16_v0"},
       {K::GemmReluBwd, make_gemm_relu_bwd_f32_variant, 0, "gemm_relu_bwd_f32_v0"},
+      {K::GemmReluBwd, make_gemm_relu_bwd_f32_3xtf32_variant, -20, "gemm_relu_bwd_f32_3xtf32_v0"},
       {K::AllReduce, make_all_reduce_nccl_f32_variant, 0, "all_reduce_nccl_f32_v0"},
       {K::DpAdamStep, make_dp_adam_step_variant, 0, "dp_adam_step_f32_p2p_v0"},
   };

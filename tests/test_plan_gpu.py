@@ -225,3 +225,35 @@ def test_global_graph_api_like_the_reference_binding(gpu):
     _C.graph_reset()
     with pytest.raises(RuntimeError, match="graph_end called but not capturing"):
         _C.graph_end()
+
+
+def test_fp32_mlp_on_the_tensor_cores_tracks_the_exact_plan(gpu):
+    """compute_dtype f32 with fp32_gemm='3xtf32': every GEMM of the step (forward with bias/ReLU, dW, dX with the ReLU
+    mask) runs under the 3xTF32 ids, whose staging copies come out of the plan's one workspace buffer. The loss follows
+    the exact-fp32 plan and the oracle to 1e-5 on the first step and to 2e-4 over five captured replays."""
+    dims, batch = [784, 256, 128, 10], 192
+    exact, vals, low, env, dtypes = make_plan(batch, dims, "f32", seed=2)
+    fast, vals_f, low_f, _, _ = make_plan(batch, dims, "f32", seed=2, fp32_gemm="3xtf32")
+    gemm_ids = {it["kernel_id"] for it in low_f if it["op"] in ("gemm", "gemm_epilogue", "gemm_relu_bwd")}
+    assert gemm_ids == {"gemm_f32_3xtf32_v0", "gemm_bias_relu_f32_3xtf32_v0", "gemm_relu_bwd_f32_3xtf32_v0"}
+    by = exact.by_name
+    fast.capture()
+    for step in range(5):
+        exact.run()
+        fast.replay(1)
+        exact.sync()
+        fast.sync()
+        oracle.run_lowered(low, env, dtypes, np.float64)
+        want = float(env[by["loss"]][0])
+        assert exact.tensor("loss").numpy()[0] == pytest.approx(want, rel=1e-5), f"exact, step {step}"
+        # the first step sees the same weights (error of the GEMM path only, measured 2e-6); afterwards the two
+        # trajectories separate slowly through Adam (2e-5 by the fifth step)
+        assert fast.tensor("loss").numpy()[0] == pytest.approx(want, rel=1e-5 if step == 0 else 2e-4), f"3xtf32, step {step}"
+    # Adam divides by sqrt(v): where a gradient is within rounding of zero the two plans may step in different
+    # directions, so the weights are compared by the fraction of elements that moved apart
+    for name in ("0.W", "2.W", "4.W"):
+        a, b = exact.tensor(name).numpy(), fast.tensor(name).numpy()
+        assert (~np.isclose(a, b, rtol=1e-3, atol=2e-5)).mean() <= 0.01, name
+    assert _C.gemm_status() == 0
+    exact.close()
+    fast.close()

@@ -98,6 +98,7 @@ struct aicf_plan {
   std::vector<Op> ops;
   bool finalized = false;
   void* arena = nullptr;
+  size_t pooled_bytes = 0;
   size_t arena_bytes = 0, no_reuse_bytes = 0;
   void* ws = nullptr;
   size_t ws_bytes = 0;
@@ -508,7 +509,8 @@ int aicf_b200_plan_finalize(aicf_plan* p) {
         std::find(arena_vals.begin(), arena_vals.end(), &v) == arena_vals.end())
       owned_static += round_up(v.bytes, kAlign);
   }
-  p->arena_bytes += owned_static;  // reported figure covers every STATIC byte, pooled or not
+  p->pooled_bytes = p->arena_bytes;  // extent of the shared arena itself
+  p->arena_bytes += owned_static;    // reported figure covers every STATIC byte, pooled or not
 
   // resolve variants, descriptors, workspace
   size_t ws_need = 0;
@@ -579,6 +581,13 @@ void* aicf_b200_plan_value_ptr(aicf_plan* p, int vid) {
 size_t aicf_b200_plan_value_bytes(aicf_plan* p, int vid) {
   Value* v = p ? p->find(vid) : nullptr;
   return v ? v->bytes : 0;
+}
+int64_t aicf_b200_plan_value_arena_offset(aicf_plan* p, int vid) {
+  Value* v = p ? p->resolve(vid) : nullptr;
+  if (!v || !v->ptr || !p->arena || p->pooled_bytes == 0) return -1;
+  const uint8_t* base = static_cast<const uint8_t*>(p->arena);
+  const uint8_t* q = static_cast<const uint8_t*>(v->ptr);
+  return (q >= base && q < base + p->pooled_bytes) ? static_cast<int64_t>(q - base) : -1;
 }
 size_t aicf_b200_plan_peer_pool_bytes(aicf_plan* p) { return p ? p->peer_pool_bytes : 0; }
 size_t aicf_b200_plan_arena_bytes(aicf_plan* p) { return p ? p->arena_bytes : 0; }

@@ -113,6 +113,7 @@ PROTOTYPES = {
     "aicf_b200_plan_finalize": (_i, [_vp]),
     "aicf_b200_plan_value_ptr": (_vp, [_vp, _i]),
     "aicf_b200_plan_value_bytes": (_sz, [_vp, _i]),
+    "aicf_b200_plan_value_arena_offset": (C.c_int64, [_vp, _i]),
     "aicf_b200_plan_arena_bytes": (_sz, [_vp]),
     "aicf_b200_plan_arena_bytes_no_reuse": (_sz, [_vp]),
     "aicf_b200_plan_num_ops": (_i, [_vp]),

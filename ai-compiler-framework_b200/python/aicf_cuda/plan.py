@@ -240,6 +240,26 @@ class Plan:
                 raise KeyError(f"state is missing {n!r}")
             self.tensor(n).copy_from_host(state[n])
 
+    def memory_map(self) -> List[Dict[str, Any]]:
+        """Where every value lives: bytes, and either its offset in the shared arena or None for a buffer of its own.
+        This is the arena layout of the compiled plan: values with disjoint live ranges share offsets. (`arena_bytes`
+        is the whole static footprint, the shared arena plus the statics that own their buffers.)"""
+        out = []
+        for vid, v in sorted(self.values.items()):
+            off = int(lib.aicf_b200_plan_value_arena_offset(self._h, vid))
+            out.append({"vid": vid, "name": v.name, "bytes": int(lib.aicf_b200_plan_value_bytes(self._h, vid)),
+                        "arena_offset": off if off >= 0 else None})
+        return out
+
+    def to_json(self) -> str:
+        """plan_to_json of this plan plus its memory layout (`arena_bytes`, `arena_bytes_no_reuse`, `memory_map`)."""
+        import json
+        d = json.loads(plan_to_json(self.name, self.values.values(), self.lowered))
+        d["arena_bytes"] = self.arena_bytes
+        d["arena_bytes_no_reuse"] = self.arena_bytes_no_reuse
+        d["memory_map"] = self.memory_map()
+        return json.dumps(d, indent=1)
+
     @property
     def arena_bytes(self) -> int:
         return int(lib.aicf_b200_plan_arena_bytes(self._h))

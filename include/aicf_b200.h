@@ -220,6 +220,10 @@ size_t aicf_b200_plan_peer_pool_bytes(aicf_plan* plan);
 int aicf_b200_plan_finalize(aicf_plan* plan);
 void* aicf_b200_plan_value_ptr(aicf_plan* plan, int vid);
 size_t aicf_b200_plan_value_bytes(aicf_plan* plan, int vid);
+/* Byte offset of a value inside the plan's shared arena, or -1 when the value has a buffer of its own (inputs,
+ * parameters, persistent and bound values, values in the peer pool) or is unknown. Values whose live ranges do not
+ * overlap may report overlapping ranges: that is the reuse. For dumps of the memory layout. */
+int64_t aicf_b200_plan_value_arena_offset(aicf_plan* plan, int vid);
 size_t aicf_b200_plan_arena_bytes(aicf_plan* plan);        /* bytes actually allocated for STATIC values */
 size_t aicf_b200_plan_arena_bytes_no_reuse(aicf_plan* plan); /* what one buffer per value would need */
 int aicf_b200_plan_num_ops(aicf_plan* plan);

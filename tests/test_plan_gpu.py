@@ -191,6 +191,18 @@ def test_arena_reuses_dead_buffers(gpu):
     assert 0 < plan.arena_bytes < plan.arena_bytes_no_reuse
     plan.run()
     plan.sync()
+    # the layout dump: parameters and inputs own their buffers, intermediates sit inside the arena, and some of them
+    # share bytes (their live ranges do not overlap)
+    import json
+    doc = json.loads(plan.to_json())
+    mm = {m["name"]: m for m in doc["memory_map"]}
+    assert doc["arena_bytes"] == plan.arena_bytes and doc["format"] == "aicf_b200.plan/1" and len(doc["lowered"]) == len(low)
+    assert mm["0.W"]["arena_offset"] is None and mm["x"]["arena_offset"] is None
+    inside = [m for m in doc["memory_map"] if m["arena_offset"] is not None]
+    assert inside and all(m["arena_offset"] + m["bytes"] <= plan.arena_bytes and m["arena_offset"] % 256 == 0 for m in inside)
+    spans = sorted((m["arena_offset"], m["arena_offset"] + m["bytes"]) for m in inside)
+    assert any(a2 < b1 for (a1, b1), (a2, b2) in zip(spans, spans[1:])), "no two values share arena bytes"
+    assert sum(m["bytes"] for m in inside) > max(b for _, b in spans), "pooled values must not fit side by side"
     plan.close()
 
 

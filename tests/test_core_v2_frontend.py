@@ -394,3 +394,56 @@ def test_compile_train_step_matches_the_oracle_eager_and_replayed(gpu, optimizer
         np.testing.assert_array_equal(graphed.params[nm].numpy(), eager.params[nm].numpy(), err_msg=f"replay {nm}")
     if optimizer == "adam":
         assert int(eager.value("opt.step").numpy()) == steps == int(graphed.value("opt.step").numpy())
+
+
+@pytest.mark.gpu
+def test_front_end_and_executor_take_torch_dtypes_and_tensors(gpu):
+    """What a script written against the reference does: torch dtypes and devices in sym_tensor, torch CUDA tensors
+    into PlannedExecutor.run. torch is only duck-typed (data_ptr / shape / dtype / is_contiguous)."""
+    torch = pytest.importorskip("torch")
+    if not torch.cuda.is_available():
+        pytest.skip("torch sees no CUDA device")
+    from aicf_fw.core_v2 import PlannedExecutor, dump_lowered, trace_ir
+    from aicf_fw.core_v2.exec import ExecOptions
+    from aicf_fw.core_v2.lower import lower_to_backend_ops
+    from aicf_fw.core_v2.ops import linear, linear_bwd, mse_grad, relu, relu_bwd, save, sgd_step, sym_tensor
+    from aicf_fw.core_v2.plan import apply_kernel_decisions_stageB, build_binding_plan
+    from aicf_fw.core_v2.rewrites.stageC_fuse_epilogue import stageC_fuse_gemm_epilogue
+    from aicf_fw.core_v2.kernel_select import apply_kernel_selection
+    device, dtype = torch.device("cuda:0"), torch.float16
+
+    def build():
+        sx, st = (sym_tensor(name=n, shape=(B, D), dtype=dtype, device=device) for n in ("x", "t"))
+        sW0, sW1 = (sym_tensor(name=n, shape=(D, D), dtype=dtype, device=device) for n in ("0.W", "2.W"))
+        sb0, sb1 = (sym_tensor(name=n, shape=(D,), dtype=dtype, device=device) for n in ("0.b", "2.b"))
+        r0 = relu(linear(sx, sW0, sb0, name="lin0_out"), name="relu0_out")
+        r0s = save(r0, name="relu0_saved")
+        dY = mse_grad(linear(r0, sW1, sb1, name="lin1_out"), st, name="dY")
+        d_r0, dW1, db1 = linear_bwd(r0, sW1, dY, bias=True, dx_name="d_relu0_out", dW_name="d_2.W", db_name="d_2.b")
+        _dx, dW0, db0 = linear_bwd(sx, sW0, relu_bwd(d_r0, r0s, name="d_lin0_out"), bias=True, dx_name="d_x",
+                                   dW_name="d_0.W", db_name="d_0.b")
+        for p, g in ((sW0, dW0), (sb0, db0), (sW1, dW1), (sb1, db1)):
+            sgd_step(p, g, lr=LR)
+
+    ir = trace_ir(build, name="v2_kid_trace_by_id_test")
+    lowered = apply_kernel_selection(ir, stageC_fuse_gemm_epilogue(ir, apply_kernel_decisions_stageB(ir, lower_to_backend_ops(ir))),
+                                     overwrite=False)
+    assert dump_lowered(lowered, name="v2_kid_trace_by_id_test") == FIX["text"]["lowered"]
+    h_in, h_par = _host_inputs(5)
+    t_in = {k: torch.from_numpy(v).to(device) for k, v in h_in.items()}
+    t_par = {k: torch.from_numpy(v).to(device) for k, v in h_par.items()}
+    ex = PlannedExecutor(ir=ir, lowered=lowered, plan=build_binding_plan(ir), opts=ExecOptions(require_kernel_id=True))
+    ex.trace_reset()
+    ex.trace_enable(True)
+    ex.run(inputs=t_in, params=t_par, reuse_static=True)
+    torch.cuda.synchronize()
+    assert ex.trace_get() == FIX["runtime_trace"]
+    # the same step on aicf_cuda.Tensor buffers gives the same parameters, bit for bit
+    from aicf_cuda import Tensor
+    ex2 = cv.PlannedExecutor(ir=ir, lowered=lowered, plan=cv.build_binding_plan(ir))
+    a_par = {k: Tensor.from_numpy(v) for k, v in h_par.items()}
+    ex2.run(inputs={k: Tensor.from_numpy(v) for k, v in h_in.items()}, params=a_par)
+    ex2.sync()
+    for k in h_par:
+        np.testing.assert_array_equal(t_par[k].cpu().numpy(), a_par[k].numpy(), err_msg=k)
+        assert not np.array_equal(t_par[k].cpu().numpy(), h_par[k]), f"{k} was not updated in place"

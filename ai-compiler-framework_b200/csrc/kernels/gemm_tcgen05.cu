@@ -1,18 +1,24 @@
 // Dense GEMM for Blackwell (sm_100a): C = [relu](op(A) * op(B) [+ bias]) with 16-bit operands
-// (bf16 or f16), fp32 accumulation in tensor memory, output bf16 / f16 / f32.
+// (bf16 or f16), fp32 accumulation in tensor memory, output bf16 / f16 / f32; and, under opt-in kernel ids, fp32
+// operands as three TF32 products per k step (section "3xTF32" below).
 //
-// Structure (one persistent CTA per SM, 192 threads):
-//   warp 0      TMA producer: cp.async.bulk.tensor 2-D tile loads (no multicast) into a 4-stage
-//               ring of 128B-swizzled shared-memory tiles, completion on mbarriers
-//   warp 1      owns tensor memory (tcgen05.alloc / dealloc of all 512 columns) and issues
-//               tcgen05.mma.cta_group::1.kind::f16 from one elected lane; tcgen05.commit releases
-//               smem stages and publishes finished accumulators
-//   warps 2-5   epilogue: tcgen05.ld of the 128x256 fp32 accumulator (each warp its own 32-lane
-//               TMEM sub-partition), + bias, ReLU, convert, 16-byte global stores
-// Two accumulator buffers (2 x 256 TMEM columns) let the epilogue of tile i overlap the main loop
-// of tile i+1. All four transpose combinations are handled without moving data: an operand whose
-// contiguous dimension is M/N instead of K is loaded as 64x64 boxes and described to the MMA as
-// "MN-major" through the shared-memory and instruction descriptors.
+// Three kernels share the helpers of this file:
+//   gemm_tcgen05_2cta_kernel   CTA pairs (clusters of 2) on 256x256 tiles with tcgen05.mma.cta_group::2; the default
+//                              for problems with enough tiles to occupy the SM pairs
+//   gemm_tcgen05_kernel<TN>    one CTA per 128 x TN tile, TN = 256 / 128 / 64 (4 / 6 / 8 stages): small problems
+//   gemm_tf32x3_kernel         one CTA per 128x128 tile, kind::tf32, hi/lo operand parts staged by tf32_split_kernel
+//
+// Structure of each (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor 2-D tile loads (no multicast) into a ring of 128B-swizzled
+//               shared-memory tiles, completion on mbarriers
+//   warp 1      owns tensor memory (tcgen05.alloc / dealloc) and issues tcgen05.mma from one elected lane;
+//               tcgen05.commit releases smem stages and publishes finished accumulators
+//   warps 2-5   epilogue: tcgen05.ld of the fp32 accumulator (each warp its own 32-lane TMEM sub-partition),
+//               + bias, ReLU (or the ReLU-backward mask), convert, 16-byte global stores
+// Two (3xTF32: four) accumulator buffers in TMEM let the epilogue of tile i overlap the main loop of tile i+1. All
+// four transpose combinations are handled without moving data: an operand whose contiguous dimension is M/N instead
+// of K is loaded as 64x64 boxes and described to the MMA as "MN-major" through the shared-memory and instruction
+// descriptors (the 3xTF32 path gets K-major operands from its split pre-pass instead).
 //
 // Every wait is bounded: after ~1 s without progress a role raises the CTA's abort flag, records a
 // code in the device status word, everybody leaves their loops, tensor memory is released and the

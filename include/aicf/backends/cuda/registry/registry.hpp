@@ -16,6 +16,9 @@
 
 namespace aicf::cuda {
 
+// One dispatch request. A plain aggregate passed by const reference; the field order and types are ABI (callers
+// built against the reference's header fill it positionally or by name). All pointers are borrowed for the
+// duration of the call; `attrs` is null or points at an AttrBlob whose payload dies when the call returns.
 struct OpCall {
   OpKind kind{};
   const TensorDesc* inputs = nullptr;
@@ -26,8 +29,11 @@ struct OpCall {
   cudaStream_t stream = nullptr;
 };
 
+// Process-wide table of kernel variants. Only the member functions below are interface; callers never look inside
+// the object (it lives in this library and is reached through instance()), so its private layout is free.
 class KernelRegistry {
  public:
+  // The one registry of the process (constructed on first use, never destroyed before exit).
   static KernelRegistry& instance();
 
   // Thread-safe. Variants without a kernel_id are ignored; the first registration of an id wins.
@@ -36,16 +42,21 @@ class KernelRegistry {
   // Stable pointers, taken under the lock so supported()/launch() run without it.
   void variants_snapshot(OpKind kind, std::vector<const KernelVariant*>& out) const;
 
+  // The variant registered under `kernel_id` for `kind`, or null. The pointer stays valid for the life of the
+  // process: variants are never removed.
   const KernelVariant* find_by_id(OpKind kind, const char* kernel_id) const;
 
+  // Runs aicf_cuda_register_all_kernels() exactly once per process, whatever thread gets here first.
   static void ensure_registered();
 
  private:
   KernelRegistry() = default;
   static constexpr int kKinds = static_cast<int>(OpKind::_Count);
+  // Per kind: variants in descending priority (ties in registration order), each owned here so that pointers
+  // handed out by variants_snapshot / find_by_id never move, and an index from kernel id to variant.
   std::vector<std::unique_ptr<KernelVariant>> table_[kKinds];
   std::unordered_map<std::string, const KernelVariant*> by_id_[kKinds];
-  mutable std::mutex mu_;
+  mutable std::mutex mu_;  // guards both tables; never held while supported() or launch() run
 };
 
 // Legacy runtime dispatch: first supported variant in priority order.

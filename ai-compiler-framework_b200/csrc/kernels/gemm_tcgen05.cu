@@ -1102,16 +1102,27 @@ Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream) {
 
   // One CTA per tile (128x256) or a CTA pair per 256x256 tile. The pair needs at least two row tiles to have
   // work for both halves. AICF_GEMM_CTA_GROUP=1|2 overrides the choice (tuning and A/B tests).
-  // CTA pairs when their 256x256 tiles occupy at least half of the SM pairs; otherwise one CTA per tile with the
-  // widest tile (256, 128, 64 columns) that still gives every SM a tile, or the narrowest when none does.
+  // Kernel and tile shape by a small cost model: (rounds of tiles over the SMs, or SM pairs) x (relative duration of
+  // one round). The weights are the measured round times of a long-K problem (K = 8192: 44 / 51 / 65 us for one CTA
+  // per 128x64 / 128x128 / 128x256 tile, 56 us for a CTA pair per 256x256 tile), normalised to the pair. A narrow tile
+  // is cheaper per round but needs more rounds once it stops fitting the machine: 256 x 8192 x 8192 takes 51 us as one
+  // round of 128x128 tiles and 89 us as two rounds of 128x64 tiles; 1024^3 is fastest as one round of 128x64 tiles.
+  const int64_t sms = sm_count();
+  const int64_t pair_slots = sms / 2 > 0 ? sms / 2 : 1;
+  auto rounds = [](int64_t tiles, int64_t slots) { return (tiles + slots - 1) / slots; };
+  auto single_tiles = [&](int64_t w) { return ((p.M + kTileM - 1) / kTileM) * ((p.N + w - 1) / w); };
   const int64_t pair_tiles_all = ((p.M + 2 * kTileM - 1) / (2 * kTileM)) * ((p.N + kTileN - 1) / kTileN);
-  bool pair = p.M > kTileM && pair_tiles_all * 4 >= sm_count();
+  const double cost_pair = p.M > kTileM ? 1.00 * static_cast<double>(rounds(pair_tiles_all, pair_slots)) : 1e30;
+  const double cost64 = 0.78 * static_cast<double>(rounds(single_tiles(64), sms));
+  const double cost128 = 0.90 * static_cast<double>(rounds(single_tiles(128), sms));
+  const double cost256 = 1.16 * static_cast<double>(rounds(single_tiles(256), sms));
+  int tn = cost64 <= cost128 && cost64 <= cost256 ? 64 : cost128 <= cost256 ? 128 : 256;
+  const double cost_single = tn == 64 ? cost64 : tn == 128 ? cost128 : cost256;
+  bool pair = cost_pair <= cost_single;
   if (const char* e = std::getenv("AICF_GEMM_CTA_GROUP")) {
     if (e[0] == '1') pair = false;
     if (e[0] == '2') pair = true;
   }
-  auto single_tiles = [&](int64_t w) { return ((p.M + kTileM - 1) / kTileM) * ((p.N + w - 1) / w); };
-  int tn = single_tiles(256) >= sm_count() ? 256 : single_tiles(128) >= sm_count() ? 128 : 64;
   if (const char* e = std::getenv("AICF_GEMM_TILE_N")) {
     const int v = std::atoi(e);
     if (v == 256 || v == 128 || v == 64) tn = v;

@@ -60,8 +60,8 @@ bool check(const GemmContract& c, const TensorDesc* in, int ni, const TensorDesc
   return true;
 }
 
-Status run(const GemmProblem& p, cudaStream_t stream) {
-  if (gemm_tcgen05_eligible(p)) return gemm_tcgen05_run(p, stream);
+Status run(const GemmProblem& p, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  if (gemm_tcgen05_eligible(p)) return gemm_tcgen05_run(p, ws, ws_bytes, stream);
   return gemm_simt_run(p, stream);
 }
 
@@ -92,11 +92,34 @@ bool supported(const TensorDesc* in, int ni, const TensorDesc* out, int no, cons
   return check(Contracts<kId>::value, in, ni, out, no, attr, nullptr);
 }
 template <int kId>
-Status launch(const TensorDesc* in, int ni, TensorDesc* out, int no, const void* attr, void*, size_t,
+Status launch(const TensorDesc* in, int ni, TensorDesc* out, int no, const void* attr, void* ws, size_t ws_bytes,
               cudaStream_t stream) {
   GemmProblem p;
   if (!check(Contracts<kId>::value, in, ni, out, no, attr, &p)) return Status::InvalidArgument;
-  return run(p, stream);
+  return run(p, ws, ws_bytes, stream);
+}
+// Workspace of the tensor-core path (split-K parts). The output is not known here; its dtype and layout follow from
+// the contract (dtype kId's out, packed rows), which is all the eligibility test and the size need.
+template <int kId>
+size_t gemm_workspace(const TensorDesc* in, int ni, const void* attr) {
+  constexpr GemmContract c = Contracts<kId>::value;
+  if (c.in == DType::kF32 || !in || ni < 2 || in[0].rank() != 2 || in[1].rank() != 2) return 0;
+  bool ta, tb, relu;
+  if (c.bias == BiasRule::None || c.bias == BiasRule::ReluBwdMask) read_gemm_attr(attr, &ta, &tb);
+  else read_gemm_epilogue_attr(attr, &ta, &tb, &relu);
+  GemmProblem p;
+  p.A = view_of(in[0], ta);
+  p.B = view_of(in[1], tb);
+  p.M = p.A.rows;
+  p.K = p.A.cols;
+  p.N = p.B.cols;
+  if (p.M <= 0 || p.N <= 0 || p.K <= 0 || p.B.rows != p.K) return 0;
+  p.C.dtype = c.out;
+  p.C.rows = p.M;
+  p.C.cols = p.N;
+  p.C.rs = p.N;
+  p.C.cs = 1;
+  return gemm_tcgen05_workspace(p);
 }
 // fp32 on the tensor cores: opt-in ids, never chosen over the exact kernel by priority dispatch (lower priority).
 template <int kId>
@@ -148,7 +171,7 @@ KernelVariant variant(const char* name) {
   v.expected_attr_schema_id = 0;  // schema 0 and the op's own schema are both parsed
   v.launch = launch<kId>;
   v.supported = supported<kId>;
-  v.query_workspace = no_workspace;
+  v.query_workspace = gemm_workspace<kId>;
   return v;
 }
 

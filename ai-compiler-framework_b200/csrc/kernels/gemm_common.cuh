@@ -89,7 +89,10 @@ inline bool build_problem(const TensorDesc* in, int ni, const TensorDesc* out, i
 Status gemm_simt_run(const GemmProblem& p, cudaStream_t stream);
 // Implemented in gemm_tcgen05.cu: returns NotImplemented when the problem does not meet the TMA
 // alignment rules, so the caller can fall through to the SIMT kernel.
-Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream);
+// `ws` (may be null) is scratch of at least gemm_tcgen05_workspace(p) bytes: with it, a product that has few tiles
+// and a long K is split over K; without it the same product runs unsplit.
+Status gemm_tcgen05_run(const GemmProblem& p, void* ws, size_t ws_bytes, cudaStream_t stream);
+size_t gemm_tcgen05_workspace(const GemmProblem& p);
 bool gemm_tcgen05_eligible(const GemmProblem& p);
 // Implemented in gemm_tcgen05.cu: fp32 operands on the tensor cores as three TF32 products per k step (hi/lo split
 // of both operands, staged in `ws`). Not bit-identical to an fp32 FMA chain; error is of the order of fp32 rounding.

@@ -75,6 +75,11 @@ struct GemmParams {
   int a_mn_major, b_mn_major;
   uint32_t idesc;
   int c_vec_ok;         // C rows allow 16-byte stores
+  // split-K (single-CTA kernel only): `splits` CTAs share a tile, each accumulating a contiguous range of k blocks
+  // and writing its raw fp32 accumulator to partial[split][M][N]; splitk_finish_kernel adds the parts in split order
+  // and applies the epilogue. splits <= 1: the kernel stores C itself.
+  int splits;
+  float* partial;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -342,8 +347,10 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + TN - 1) / TN;
-  const int num_tiles = tiles_m * tiles_n;
-  const int k_blocks = (p.K + kTileK - 1) / kTileK;
+  const int splits = p.splits > 1 ? p.splits : 1;
+  const int num_tiles = tiles_m * tiles_n * splits;  // work items: (tile, split), split fastest
+  const int k_blocks_all = (p.K + kTileK - 1) / kTileK;
+  const int kb_per_split = (k_blocks_all + splits - 1) / splits;
 
   const bool tl = g_gemm_timeline_on != 0 && blockIdx.x == 0;
   if (tl && threadIdx.x == 0) g_gemm_timeline[0] = global_ns();
@@ -377,9 +384,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool first = true;
       for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
         int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+        tile_coords(tile / splits, tiles_m, tiles_n, &tm, &tn);
         const int m0 = tm * kTileM, n0 = tn * TN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int kb_lo = (tile % splits) * kb_per_split, kb_hi = min(kb_lo + kb_per_split, k_blocks_all);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           const unsigned long long w0 = tl ? global_ns() : 0;
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1)) { alive = false; break; }
           if (tl) {
@@ -426,7 +434,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (tl) wait_acc += global_ns() - w0;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * TN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int kb_lo = (tile % splits) * kb_per_split, kb_hi = min(kb_lo + kb_per_split, k_blocks_all);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           w0 = tl ? global_ns() : 0;
           if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3)) { alive = false; break; }
           if (tl) {
@@ -439,7 +448,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint64_t bdesc = make_smem_desc(sb, p.b_mn_major);
 #pragma unroll
           for (int k = 0; k < kTileK / kUmmaK; ++k)
-            umma_f16(tmem_d, adesc + k * a_step, bdesc + k * b_step, p.idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16(tmem_d, adesc + k * a_step, bdesc + k * b_step, p.idesc, (kb != kb_lo || k != 0) ? 1u : 0u);
           umma_commit(bar_empty + 8 * stage);  // stage is free once these MMAs have read it
           if (++stage == kSt) { stage = 0; phase ^= 1u; }
         }
@@ -459,11 +468,22 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool alive = true;
     const bool tle = tl && warp == 2 && lane == 0;
     unsigned long long e_wait = 0, e_busy = 0, e_tiles = 0;
+    // With split-K the epilogue only parks the raw accumulator: fp32, no bias, no activation, packed [M][N] rows.
+    GemmParams q = p;
+    if (splits > 1) {
+      q.ldc = p.N;
+      q.c_dtype = static_cast<int>(DType::kF32);
+      q.bias_dtype = 0;
+      q.relu = 0;
+      q.mask = nullptr;
+      q.c_vec_ok = (p.N % 4) == 0;
+    }
     for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
       int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+      tile_coords(tile / splits, tiles_m, tiles_n, &tm, &tn);
       const int row = tm * kTileM + sub * 32 + lane;
       const int n0 = tn * TN;
+      if (splits > 1) q.C = p.partial + static_cast<int64_t>(tile % splits) * p.M * p.N;
       const unsigned long long e0 = tle ? global_ns() : 0;
       // the TMEM loads below are warp-collective: the whole warp proceeds or the whole warp leaves
       if (!__all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, 4))) { alive = false; break; }
@@ -480,7 +500,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
       for (int h = 0; h < TN / 32; ++h) {
         const int col = n0 + lane + 32 * h;
-        bs[lane + 32 * h] = (p.bias_dtype != 0 && col < p.N) ? bias_at(p, col) : 0.0f;
+        bs[lane + 32 * h] = (q.bias_dtype != 0 && col < p.N) ? bias_at(p, col) : 0.0f;
       }
       __syncwarp();
 #pragma unroll 1
@@ -494,8 +514,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         } else {
           tmem_ld_32x32(taddr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
         }
-        epilogue_chunk(p, row, col0, &r[0], bs + c * 32);
-        if (two) epilogue_chunk(p, row, col0 + 32, &r[32], bs + c * 32 + 32);
+        epilogue_chunk(q, row, col0, &r[0], bs + c * 32);
+        if (two) epilogue_chunk(q, row, col0 + 32, &r[32], bs + c * 32 + 32);
       }
       tc_fence_before();
       __syncwarp();
@@ -1095,18 +1115,30 @@ bool gemm_tcgen05_eligible(const GemmProblem& p) {
   return encode_fn() != nullptr;
 }
 
-Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream) {
-  if (!gemm_tcgen05_eligible(p)) return Status::NotImplemented;
-  const int a_major = operand_major(p.A.data, p.A.rs, p.A.cs, p.M, p.K);
-  const int b_major = operand_major(p.B.data, p.B.cs, p.B.rs, p.N, p.K);
+namespace {
 
-  // One CTA per tile (128x256) or a CTA pair per 256x256 tile. The pair needs at least two row tiles to have
-  // work for both halves. AICF_GEMM_CTA_GROUP=1|2 overrides the choice (tuning and A/B tests).
-  // Kernel and tile shape by a small cost model: (rounds of tiles over the SMs, or SM pairs) x (relative duration of
-  // one round). The weights are the measured round times of a long-K problem (K = 8192: 44 / 51 / 65 us for one CTA
-  // per 128x64 / 128x128 / 128x256 tile, 56 us for a CTA pair per 256x256 tile), normalised to the pair. A narrow tile
-  // is cheaper per round but needs more rounds once it stops fitting the machine: 256 x 8192 x 8192 takes 51 us as one
-  // round of 128x128 tiles and 89 us as two rounds of 128x64 tiles; 1024^3 is fastest as one round of 128x64 tiles.
+struct GemmChoice {
+  bool pair = false;  // CTA pairs on 256x256 tiles, else one CTA per 128 x tn tile
+  int tn = 256;
+  int splits = 1;     // > 1: split-K over that many CTAs per tile (single-CTA kernel only)
+};
+
+// Kernel and tile shape by a small cost model: (rounds of tiles over the SMs, or SM pairs) x (relative duration of
+// one round). The weights are the measured round times of a long-K problem (K = 8192: 44 / 51 / 65 us for one CTA
+// per 128x64 / 128x128 / 128x256 tile, 56 us for a CTA pair per 256x256 tile), normalised to the pair. A narrow tile
+// is cheaper per round but needs more rounds once it stops fitting the machine: 256 x 8192 x 8192 takes 51 us as one
+// round of 128x128 tiles and 89 us as two rounds of 128x64 tiles; 1024^3 is fastest as one round of 128x64 tiles.
+//
+// Split-K: a product with few tiles and a long K (a small batch against a large weight matrix) is bound by how many
+// bytes of the large operand are in flight; with one tile per CTA a 128x64 tile keeps 64 KiB of it in its ring and
+// most SMs of a wide-tile launch are idle. Such products run on 128x256 (or 128x128) tiles with K divided over up to
+// 8 CTAs per tile, so that all SMs stream the large operand with most of their shared memory; the fp32 parts are
+// added in split order by splitk_finish_kernel (deterministic). Considered only when it is predicted to win and each
+// part keeps at least 8 k blocks.
+// AICF_GEMM_CTA_GROUP=1|2, AICF_GEMM_TILE_N=256|128|64 and AICF_GEMM_SPLITK=<n> (0 or 1 = off) override the choice
+// (tuning and tests).
+GemmChoice choose_gemm(const GemmProblem& p) {
+  GemmChoice c;
   const int64_t sms = sm_count();
   const int64_t pair_slots = sms / 2 > 0 ? sms / 2 : 1;
   auto rounds = [](int64_t tiles, int64_t slots) { return (tiles + slots - 1) / slots; };
@@ -1116,17 +1148,118 @@ Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream) {
   const double cost64 = 0.78 * static_cast<double>(rounds(single_tiles(64), sms));
   const double cost128 = 0.90 * static_cast<double>(rounds(single_tiles(128), sms));
   const double cost256 = 1.16 * static_cast<double>(rounds(single_tiles(256), sms));
-  int tn = cost64 <= cost128 && cost64 <= cost256 ? 64 : cost128 <= cost256 ? 128 : 256;
-  const double cost_single = tn == 64 ? cost64 : tn == 128 ? cost128 : cost256;
-  bool pair = cost_pair <= cost_single;
+  c.tn = cost64 <= cost128 && cost64 <= cost256 ? 64 : cost128 <= cost256 ? 128 : 256;
+  double best = c.tn == 64 ? cost64 : c.tn == 128 ? cost128 : cost256;
+  c.pair = cost_pair <= best;
+  if (c.pair) best = cost_pair;
+
+  const int64_t k_blocks = (p.K + kTileK - 1) / kTileK;
+  auto split_for = [&](int64_t w) -> int {
+    const int64_t t = single_tiles(w);
+    int64_t s = sms / t;
+    if (s > k_blocks / 8) s = k_blocks / 8;
+    if (s > 8) s = 8;
+    if (s < 2) return 1;
+    const int64_t per = (k_blocks + s - 1) / s;
+    return static_cast<int>((k_blocks + per - 1) / per);  // no empty part
+  };
+  // Measured on M x 8192 x 8192 (bf16): M = 16 / 64 / 128 take 33 / 38 / 44 us split four ways on 128x256 tiles
+  // against 49 us unsplit (the pass that adds the parts costs 2-10 us, growing with M); at M = 256 (64 tiles) the
+  // split is already slower than one round of 128x128 tiles. Hence: only when the widest tiles fill at most a quarter
+  // of the SMs, and the widest tile whose parts occupy most of the machine.
+  if (k_blocks >= 64 && !c.pair) {
+    const int widths[3] = {256, 128, 64};
+    int best_w = 0, best_s = 1;
+    int64_t best_ctas = 0;
+    for (int i = 0; i < 3; ++i) {
+      const int64_t t = single_tiles(widths[i]);
+      if (single_tiles(256) * 4 > sms) break;
+      const int sp = split_for(widths[i]);
+      if (sp < 2) continue;
+      const int64_t ctas = t * sp;
+      if (ctas > best_ctas) {
+        best_ctas = ctas;
+        best_w = widths[i];
+        best_s = sp;
+      }
+      if (ctas * 10 >= sms * 7) break;  // this width already occupies 70 % of the SMs
+    }
+    if (best_w != 0) {
+      c.tn = best_w;
+      c.splits = best_s;
+    }
+  }
   if (const char* e = std::getenv("AICF_GEMM_CTA_GROUP")) {
-    if (e[0] == '1') pair = false;
-    if (e[0] == '2') pair = true;
+    if (e[0] == '1') c.pair = false;
+    if (e[0] == '2' && p.M > kTileM) c.pair = true, c.splits = 1;
   }
   if (const char* e = std::getenv("AICF_GEMM_TILE_N")) {
     const int v = std::atoi(e);
-    if (v == 256 || v == 128 || v == 64) tn = v;
+    if (v == 256 || v == 128 || v == 64) {
+      if (v != c.tn) c.splits = 1;
+      c.tn = v;
+    }
   }
+  if (const char* e = std::getenv("AICF_GEMM_SPLITK")) {
+    int v = std::atoi(e);
+    if (v <= 1) {
+      c.splits = 1;
+    } else if (!c.pair) {
+      if (v > 8) v = 8;
+      if (v > k_blocks) v = static_cast<int>(k_blocks);
+      const int64_t per = (k_blocks + v - 1) / v;
+      c.splits = static_cast<int>((k_blocks + per - 1) / per);
+    }
+  }
+  if (c.pair) c.splits = 1;
+  return c;
+}
+
+// result[m][n] = epilogue(sum over splits of partial[s][m][n]), parts added in split order.
+__global__ void __launch_bounds__(256) splitk_finish_kernel(GemmParams p) {
+  const int64_t total = static_cast<int64_t>(p.M) * p.N;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int row = static_cast<int>(i / p.N), col = static_cast<int>(i % p.N);
+    float v = 0.0f;
+    for (int s = 0; s < p.splits; ++s) v += __ldcs(p.partial + static_cast<int64_t>(s) * total + i);
+    if (p.bias_dtype != 0) v += bias_at(p, col);
+    if (p.relu) v = fmaxf(v, 0.0f);
+    const int64_t off = static_cast<int64_t>(row) * p.ldc + col;
+    if (p.mask) {
+      const int64_t moff = static_cast<int64_t>(row) * p.mask_ld + col;
+      float y;
+      if (p.c_dtype == static_cast<int>(DType::kF32)) y = static_cast<const float*>(p.mask)[moff];
+      else if (p.c_dtype == static_cast<int>(DType::kBF16)) y = __bfloat162float(static_cast<const __nv_bfloat16*>(p.mask)[moff]);
+      else y = __half2float(static_cast<const __half*>(p.mask)[moff]);
+      if (!(y > 0.0f)) v = 0.0f;
+    }
+    if (p.c_dtype == static_cast<int>(DType::kF32)) static_cast<float*>(p.C)[off] = v;
+    else if (p.c_dtype == static_cast<int>(DType::kBF16)) static_cast<__nv_bfloat16*>(p.C)[off] = __float2bfloat16_rn(v);
+    else static_cast<__half*>(p.C)[off] = __float2half_rn(v);
+  }
+}
+
+}  // namespace
+
+// Bytes of workspace the 16-bit GEMM wants for this problem (0 unless it is split over K).
+size_t gemm_tcgen05_workspace(const GemmProblem& p) {
+  if (!gemm_tcgen05_eligible(p)) return 0;
+  const GemmChoice c = choose_gemm(p);
+  return c.splits > 1 ? static_cast<size_t>(c.splits) * static_cast<size_t>(p.M) * static_cast<size_t>(p.N) * sizeof(float) : 0;
+}
+
+Status gemm_tcgen05_run(const GemmProblem& p, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  if (!gemm_tcgen05_eligible(p)) return Status::NotImplemented;
+  const int a_major = operand_major(p.A.data, p.A.rs, p.A.cs, p.M, p.K);
+  const int b_major = operand_major(p.B.data, p.B.cs, p.B.rs, p.N, p.K);
+  GemmChoice choice = choose_gemm(p);
+  if (choice.splits > 1) {  // no (or too little) workspace: run unsplit rather than fail
+    const size_t need = static_cast<size_t>(choice.splits) * static_cast<size_t>(p.M) * static_cast<size_t>(p.N) * sizeof(float);
+    if (!ws || ws_bytes < need || !aligned_to(ws, 16)) choice.splits = 1;
+  }
+  const bool pair = choice.pair;
+  const int tn = choice.tn;
   CUtensorMap ta, tb;
   const uint32_t b_rows = pair ? k2HalfN : static_cast<uint32_t>(tn);
   bool ok_maps = a_major == 0 ? encode_operand(&ta, p.A.data, p.A.dtype, p.K, p.M, p.A.rs, kTileK, kTileM)
@@ -1159,6 +1292,8 @@ Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream) {
             (static_cast<uint32_t>((pair ? 2 * kTileM : kTileM) >> 4) << 24);
   const int c_elem = dtype_size_bytes(p.C.dtype);
   g.c_vec_ok = aligned_to(p.C.data, 16) && ((p.C.rs * c_elem) % 16 == 0);
+  g.splits = choice.splits;
+  g.partial = choice.splits > 1 ? static_cast<float*>(ws) : nullptr;
 
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1200,7 +1335,7 @@ Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream) {
     }
     return launch_status();
   }
-  const int64_t tiles = ((p.M + kTileM - 1) / kTileM) * ((p.N + tn - 1) / tn);
+  const int64_t tiles = ((p.M + kTileM - 1) / kTileM) * ((p.N + tn - 1) / tn) * choice.splits;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
   auto go = [&](auto tag) -> Status {
     constexpr int TN = decltype(tag)::value;
@@ -1216,9 +1351,12 @@ Status gemm_tcgen05_run(const GemmProblem& p, cudaStream_t stream) {
     gemm_tcgen05_kernel<TN><<<grid, kThreads, SingleCfg<TN>::kSmem, stream>>>(ta, tb, g);
     return launch_status();
   };
-  if (tn == 256) return go(std::integral_constant<int, 256>{});
-  if (tn == 128) return go(std::integral_constant<int, 128>{});
-  return go(std::integral_constant<int, 64>{});
+  const Status st = tn == 256 ? go(std::integral_constant<int, 256>{})
+                              : tn == 128 ? go(std::integral_constant<int, 128>{}) : go(std::integral_constant<int, 64>{});
+  if (st != Status::Ok || choice.splits <= 1) return st;
+  const int64_t total = static_cast<int64_t>(p.M) * p.N;
+  splitk_finish_kernel<<<streaming_grid(total, 256, 8), 256, 0, stream>>>(g);
+  return launch_status();
 }
 
 // ------------------------------------------------------------------ 3xTF32 host side

@@ -226,3 +226,55 @@ def test_gemm_f32_3xtf32_4096_sampled_rows(gpu):
     want = np.maximum(A[rows].astype(np.float64) @ B.astype(np.float64) + bias, 0)
     assert rel_err(host(C)[rows], want) <= _tf32x3_tol(n)
     assert _C.gemm_status() == 0
+
+
+# ------------------------------------------------------------------ split-K (few tiles, long K)
+@pytest.fixture(params=["auto", "3", "8"], ids=["split_auto", "split3", "split8"])
+def splitk(request, monkeypatch):
+    """The launcher's own choice, and forced part counts (3 leaves a ragged last part)."""
+    if request.param != "auto":
+        monkeypatch.setenv("AICF_GEMM_SPLITK", request.param)
+    return request.param
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 512, 4096), (128, 1024, 8192), (200, 768, 4104), (64, 1000, 5000), (1, 256, 4096)])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("dt,out", [("bf16", "bf16"), ("bf16", "f32"), ("f16", "f16")])
+def test_gemm_split_over_k(gpu, splitk, monkeypatch, M, N, K, ta, tb, dt, out):
+    if ta and M % 8:
+        pytest.skip("a transposed A needs 16-byte aligned columns on the tensor-core path")
+    A, B, bias, sa, sb = _operands(M, N, K, ta, tb, dt)
+    X, W, Bv = dev(sa, dt), dev(sb, dt), dev(bias)
+    C = Tensor.zeros((M, N), out)
+    by_id(GEMM_KID[(dt, out)], OpKind.Gemm, [X, W], [C], GEMM, struct.pack("<ii", ta, tb))
+    want = oracle.gemm(A, B)
+    assert rel_err(host(C), want) <= TOL[dt]
+    split_result = host(C).copy()
+    if (dt, out) in EPI_KID:
+        for relu in (1, 0):
+            by_id(EPI_KID[(dt, out)], OpKind.GemmEpilogue, [X, W, Bv], [C], GPEL, struct.pack("<iii", ta, tb, relu))
+            assert rel_err(host(C), oracle.gemm_epilogue(A, B, bias, False, False, bool(relu))) <= TOL[dt]
+    # the unsplit kernel on the same operands: same product up to the order of the fp32 additions
+    monkeypatch.setenv("AICF_GEMM_SPLITK", "0")
+    by_id(GEMM_KID[(dt, out)], OpKind.Gemm, [X, W], [C], GEMM, struct.pack("<ii", ta, tb))
+    scale = float(np.abs(want).max())
+    assert np.abs(host(C) - split_result).max() <= (2e-5 if out == "f32" else 1e-2) * scale
+    assert _C.gemm_status() == 0
+
+
+def test_gemm_split_over_k_with_relu_backward_mask_and_determinism(gpu, monkeypatch):
+    M, N, K = 96, 512, 4096
+    A, B, bias, sa, sb = _operands(M, N, K, 0, 0, "bf16")
+    Y = oracle.bf16_round(np.random.default_rng(5).standard_normal((M, N)).astype(np.float32))
+    want = oracle.gemm_relu_bwd(A, B, Y)
+    outs = []
+    for force in ("4", "4", "0"):
+        monkeypatch.setenv("AICF_GEMM_SPLITK", force)
+        C = Tensor.zeros((M, N), "bf16")
+        by_id("gemm_relu_bwd_bf16_tcgen05_out_bf16_v0", OpKind.GemmReluBwd, [dev(sa, "bf16"), dev(sb, "bf16"), dev(Y, "bf16")], [C],
+              GEMM, struct.pack("<ii", 0, 0))
+        assert rel_err(host(C), want) <= TOL["bf16"]
+        assert np.array_equal(host(C) == 0, ~(Y > 0) | (host(C) == 0))
+        outs.append(host(C))
+    assert np.array_equal(outs[0], outs[1]), "parts are added in a fixed order"
+    assert _C.gemm_status() == 0

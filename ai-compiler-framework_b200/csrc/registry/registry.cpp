@@ -98,8 +98,13 @@ Status run_variant(const KernelVariant* v, const OpCall& c, const AttrBlob* attr
   if (v->query_workspace) {
     const size_t need = v->query_workspace(c.inputs, c.num_inputs, attrs);
     if (need != 0) {
-      const Status s = acquire_workspace(need, c.stream, &ws, &ws_bytes);
-      if (!ok(s)) return s;
+      // No arena to be had (a caller-provided one that is too small, or the first large request arriving while the
+      // stream is capturing): the variant is still called, without workspace. Variants that can do without it run
+      // their workspace-free form (the GEMM drops its split over K); the others refuse with InvalidArgument.
+      if (!ok(acquire_workspace(need, c.stream, &ws, &ws_bytes))) {
+        ws = nullptr;
+        ws_bytes = 0;
+      }
     }
   }
   return v->launch(c.inputs, c.num_inputs, c.outputs, c.num_outputs, attrs, ws, ws_bytes, c.stream);

@@ -524,18 +524,19 @@ def run_kernel_workload(args):
     if w in ("gemm", "gemm_f32", "gemm_tf32x3"):
         n = args.size or (2048 if small else 8192 if w == "gemm" else 4096)
         dt = "bf16" if w == "gemm" else "f32"
-        A = dev_normal((n, n), dt, 0.577, 1)  # U(-1,1) has sigma 0.577; the distribution does not affect timing
+        m = args.rows or n  # --rows M: a skinny product, M x n x n (a small batch against square weights)
+        A = dev_normal((m, n), dt, 0.577, 1)  # U(-1,1) has sigma 0.577; the distribution does not affect timing
         B = dev_normal((n, n), dt, 0.577, 2)
         bias = dev_normal((n,), "f32", 1.0, 3)
-        Cm = Tensor.empty((n, n), dt)
+        Cm = Tensor.empty((m, n), dt)
         kid = {"gemm": "gemm_bias_relu_bf16_tcgen05_out_bf16_v0", "gemm_f32": "gemm_bias_relu_f32_naive_v0",
                "gemm_tf32x3": "gemm_bias_relu_f32_3xtf32_v0"}[w]
         pay = struct.pack("<iii", 0, 1 if args.transb else 0, 1)
         fn = lambda st: _C.launch_by_id(kid, OpKind.GemmEpilogue, [A, B, bias], [Cm], 0x4750454C, pay, st)
-        work, unit, bound = 2.0 * n ** 3, "TFLOP/s", "tensor"
+        work, unit, bound = 2.0 * m * n * n, "TFLOP/s", "tensor"
         peak = peaks["bf16_tflops"] if w == "gemm" else None
         metric = f"GEMM+bias+ReLU {dt} TFLOP/s" + (" (3xTF32 tensor-core path; 2*M*N*K counted once)" if w == "gemm_tf32x3" else "")
-        cfg = {"workload": f"gemm_bias_relu_{dt}" if w != "gemm_tf32x3" else "gemm_bias_relu_3xtf32_f32", "M": n, "N": n, "K": n, "transB": bool(args.transb),
+        cfg = {"workload": f"gemm_bias_relu_{dt}" if w != "gemm_tf32x3" else "gemm_bias_relu_3xtf32_f32", "M": m, "N": n, "K": n, "transB": bool(args.transb),
                "l2": "operands exceed L2 at 8192; smaller sizes are L2-resident by nature"}
     elif w == "softmax":
         M, N = (4096, 4096) if small else (32768, 4096)

@@ -634,7 +634,7 @@ def main():
     ap.add_argument("--workload", default="mlp")
     ap.add_argument("--small", action="store_true", help="reduced shapes (profiler captures)")
     ap.add_argument("--size", type=int, default=0)
-    ap.add_argument("--rows", type=int, default=0, help="row count override for the softmax / ce / reduce / layer-norm workloads")
+    ap.add_argument("--rows", type=int, default=0, help="row count override for the softmax / ce / reduce / layer-norm workloads; M of the GEMM workloads (M x size x size)")
     ap.add_argument("--cols", type=int, default=0, help="row width override for the same workloads")
     ap.add_argument("--dtype", default="f32")
     ap.add_argument("--reduce-kind", default="sum")

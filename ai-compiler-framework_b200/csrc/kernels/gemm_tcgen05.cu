@@ -1184,6 +1184,13 @@ GemmChoice choose_gemm(const GemmProblem& p) {
       }
       if (ctas * 10 >= sms * 7) break;  // this width already occupies 70 % of the SMs
     }
+    // Same CTA count from tiles half as wide and half as many parts: the adding pass moves M x N x parts floats, so
+    // past M = 64 fewer parts win (M = 128: 40.5 us as 128x128 tiles in 2 parts, 43.7 us as 128x256 tiles in 4; at
+    // M = 16 the wide tile is ahead, 33.5 against 35.3 us).
+    if (best_w == 256 && best_s >= 4 && best_s % 2 == 0 && p.M > 64 && single_tiles(128) == 2 * single_tiles(256)) {
+      best_w = 128;
+      best_s /= 2;
+    }
     if (best_w != 0) {
       c.tn = best_w;
       c.splits = best_s;

@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdint>
 #include <cstring>
 
@@ -69,18 +70,51 @@ inline bool rows_cols_lastdim(const TensorDesc& t, int64_t* M, int64_t* N) {
 
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
+// Per-device state (SM counts, function attributes, shared-memory carveouts and symbol addresses are properties of
+// one device, not of the process) lives in tables of kMaxDevices slots indexed by the CUDA device ordinal.
+constexpr int kMaxDevices = 64;
+
+// Ordinal of the current device, or -1 when it does not fit the per-device tables (such a device still works: the
+// callers then redo their one-time set-up on every call instead of caching it).
+inline int device_slot() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return dev >= 0 && dev < kMaxDevices ? dev : -1;
+}
+
+// One "set-up done" flag per device. Set-up bodies are idempotent (cudaFuncSetAttribute and the like), so two threads
+// that both find the flag clear may both run them; the flags are atomics so that this is not a data race.
+struct PerDeviceOnce {
+  std::atomic<int> done[kMaxDevices] = {};
+  // Runs fn() (returning true on success) unless it already succeeded on the current device.
+  template <typename Fn> bool run(Fn&& fn) {
+    const int dev = device_slot();
+    if (dev >= 0 && done[dev].load(std::memory_order_acquire)) return true;
+    if (!fn()) return false;
+    if (dev >= 0) done[dev].store(1, std::memory_order_release);
+    return true;
+  }
+};
+
 // Number of SMs of the current device (148 on B200); cached per device.
 inline int sm_count() {
-  static int cached[16] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 16) dev = 0;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
+  static std::atomic<int> cached[kMaxDevices] = {};
+  const int dev = device_slot();
+  if (dev >= 0) {
+    const int c = cached[dev].load(std::memory_order_relaxed);
+    if (c > 0) return c;
   }
-  return cached[dev];
+  int cur = 0, n = 0;
+  cudaGetDevice(&cur);
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, cur) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    n = 148;
+  }
+  if (dev >= 0) cached[dev].store(n, std::memory_order_relaxed);
+  return n;
 }
 
 // Grid for a grid-stride streaming kernel: whole multiples of the SM count, no more blocks than

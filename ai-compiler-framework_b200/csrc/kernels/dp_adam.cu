@@ -7,20 +7,32 @@
 //      out of the peers' gradient buffers (P2P loads, always in rank order 0..N-1, so the sum is bit-reproducible),
 //      applies Adam to its shard of the fp32 master weights and moments, and stores the new weights into every
 //      rank's working copy (bf16 / f16 copy for matrices, the fp32 parameter itself for biases) with P2P stores;
-//   3. tells every peer "my stores into your memory are done" and the last CTA waits for all peers, so kernel
-//      completion means this rank's working copies are complete and its gradient buffer may be overwritten.
+//   3. tells every peer "my stores into your memory are done". The last CTA then waits for the same word from all
+//      peers, so kernel completion means this rank's working copies are complete and its gradient buffer may be
+//      overwritten - or, when the op carries `defer_done`, leaves that wait to the op of the step that carries
+//      `fence_slots` (the last exchange of the step waits for the done words of every slot): nothing inside a step
+//      reads a working copy or rewrites a gradient after its exchange, so one rendezvous at the end of the step
+//      replaces one per tensor and the exchanges of a step run back to back.
 // Reduce-scatter, update and all-gather travel over NVLink once each (4 B/param in, 2 B/param out per rank for
-// matrices) and Adam's 28 B/param of HBM traffic shrinks to 1/N per rank. The kernel uses no shared memory and 64
-// registers, so its CTAs co-reside with the persistent GEMM CTAs of the backward pass instead of waiting for SMs.
+// matrices) and Adam's 28 B/param of HBM traffic shrinks to 1/N per rank. Peer loads are latency-bound, so every
+// thread keeps the gradient packets of several iterations in flight (at least eight remote 16-byte loads per thread
+// whatever the number of ranks). The kernel uses a few bytes of shared memory and at most 144 registers x 256
+// threads, so its CTAs co-reside with the persistent GEMM CTAs of the backward pass (192 threads x 136 registers)
+// instead of waiting for SMs.
 //
 // fp32 master weights and moments of matrices are therefore sharded: rank r's copy is current only inside its
 // shard (gather the shards to read a whole master tensor). Working copies and biases are complete on every rank.
 //
-// Waits are bounded (~2 s); a wait that expires sets a status word, skips the work that depended on it and lets
-// the kernel finish. No TMA multicast, no multimem: plain peer loads and stores.
+// Waits are bounded (~2 s). The ready-phase wait is made by ONE thread of the launch (CTA 0), which publishes go or
+// no-go for all CTAs: either every CTA updates and broadcasts its part of the shard or none does, so a peer that
+// arrives around the limit cannot leave a tensor half updated. A wait that expires sets a status word
+// (aicf_b200_wait_status bits 17-18), skips the work that depended on it and lets the kernel finish; after a
+// non-zero status the replicas are no longer known to agree and training has to resume from a checkpoint.
+// No TMA multicast, no multimem: plain peer loads and stores.
 #include <algorithm>
 #include <mutex>
 #include <string>
+#include <type_traits>
 #include <vector>
 
 #include "../capi/capi_internal.hpp"
@@ -32,10 +44,10 @@ constexpr int kMaxRanks = 8;
 constexpr int kMaxSlots = 60;  // dp_adam_step ops per plan
 // Layout of the control block at the start of every peer pool (8 KiB):
 //   uint32 flags[kMaxSlots][2][kMaxRanks]   written by peers (phase 0 = ready, phase 1 = done)
-//   uint32 epoch[kMaxSlots]; uint32 done[kMaxSlots]   local
+//   uint32 epoch[kMaxSlots]; uint32 done[kMaxSlots]; uint32 go[kMaxSlots]   local
 constexpr size_t kFlagsBytes = size_t(kMaxSlots) * 2 * kMaxRanks * 4;
 constexpr size_t kControlBytes = 8192;
-static_assert(kFlagsBytes + size_t(kMaxSlots) * 8 <= kControlBytes, "control block layout");
+static_assert(kFlagsBytes + size_t(kMaxSlots) * 12 <= kControlBytes, "control block layout");
 
 namespace {
 
@@ -64,10 +76,14 @@ struct DpAdamArgs {
   uint32_t* flags_of[kMaxRanks];  // this op's flag block [2][kMaxRanks] in every rank's pool
   float *p, *m, *v;
   const int32_t* step;
-  uint32_t *epoch, *done;
+  uint32_t *epoch, *done, *go;  // this op's words in the local control block
   int64_t begin, end;  // this rank's shard
   int rank, world;
   int bcast_kind;  // 1 bf16, 2 f16, 3 fp32 (the parameter itself)
+  int defer_done;  // 1: do not wait for the peers' done words here
+  int fence_slots;  // > 0: before finishing, wait for the done words of slots [0, fence_slots) of this pool
+  const uint32_t* flags_base;  // flag blocks of all slots in the local pool (fence)
+  const uint32_t* epoch_base;  // epoch words of all slots in the local pool (fence)
   AdamHyper h;
 };
 
@@ -125,20 +141,88 @@ __device__ __forceinline__ void bcast_x1(const DpAdamArgs& a, int64_t i, float v
   }
 }
 
-template <int kBcast>
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// kUnroll packets per thread at a time, kW gradient sources each: every load (kUnroll x kW gradient packets, most of
+// them over NVLink, and the local p, m, v packets) is issued before the first one is used.
+template <int kBcast, int kW, int kUnroll>
+__device__ __forceinline__ void update_packets(const DpAdamArgs& a, int world, int64_t i, int64_t stride, float d1, float d2) {
+  using V4 = Pack16<float>;
+  float4 gk[kUnroll][kW];
+  V4 p[kUnroll], m[kUnroll], v[kUnroll];
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+    for (int k = 0; k < kW; ++k)
+      if (k < world) gk[u][k] = __ldcg(reinterpret_cast<const float4*>(a.g_of[k]) + (i + u * stride));
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    p[u] = ld_stream(reinterpret_cast<const V4*>(a.p) + (i + u * stride));
+    m[u] = ld_stream(reinterpret_cast<const V4*>(a.m) + (i + u * stride));
+    v[u] = ld_stream(reinterpret_cast<const V4*>(a.v) + (i + u * stride));
+  }
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    float4 acc = gk[u][0];
+#pragma unroll
+    for (int k = 1; k < kW; ++k)  // fixed rank order: the same bits whoever owns the shard
+      if (k < world) {
+        acc.x += gk[u][k].x;
+        acc.y += gk[u][k].y;
+        acc.z += gk[u][k].z;
+        acc.w += gk[u][k].w;
+      }
+    const float g[4] = {acc.x, acc.y, acc.z, acc.w};
+    V4 po, mo, vo;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) adam_one<false>(p[u].v[e], g[e], m[u].v[e], v[u].v[e], a.h, d1, d2, po.v[e], mo.v[e], vo.v[e]);
+    const int64_t at = i + u * stride;
+    st_stream(reinterpret_cast<V4*>(a.m) + at, mo);
+    st_stream(reinterpret_cast<V4*>(a.v) + at, vo);
+    if (kBcast != 3) st_stream(reinterpret_cast<V4*>(a.p) + at, po);
+    bcast_x4<kBcast>(a, at, po);
+  }
+}
+
+// kWorld: 2, 4 or 8 ranks with the loops over ranks unrolled to exactly that count, or 0 = any count up to
+// kMaxRanks (predicated). kUnroll: packets per thread per iteration.
+template <int kBcast, int kWorld, int kUnroll>
 __global__ void __launch_bounds__(256) dp_adam_kernel(const DpAdamArgs a) {
   __shared__ uint32_t s_epoch;
   __shared__ int s_go;
   if (threadIdx.x == 0) {
     const uint32_t e = *reinterpret_cast<volatile uint32_t*>(a.epoch) + 1u;
     s_epoch = e;
+    // go word of this launch: low 31 bits = the epoch it answers for, top bit = no-go
+    const uint32_t tag = e & 0x7FFFFFFFu;
     if (blockIdx.x == 0) {
       __threadfence_system();
       for (int k = 0; k < a.world; ++k) st_release_sys(a.flags_of[k] + 0 * kMaxRanks + a.rank, e);
+      const bool ok = wait_all_ranks(a.flags_of[a.rank] + 0 * kMaxRanks, a.world, e);
+      if (!ok) atomicCAS(&g_dp_status, 0, 1);
+      st_release_gpu(a.go, ok ? tag : (tag | 0x80000000u));
+      s_go = ok ? 1 : 0;
+    } else {
+      // CTA 0 is dispatched before any other CTA of the grid, so it is resident whenever this one is
+      const unsigned long long t0 = now_ns();
+      uint32_t spin = 0, w;
+      bool answered = true;
+      while (((w = ld_acquire_gpu(a.go)) & 0x7FFFFFFFu) != tag) {
+        if ((++spin & 63u) == 0u && now_ns() - t0 > kPeerWaitBudgetNs + kPeerWaitBudgetNs / 2) {
+          answered = false;
+          break;
+        }
+      }
+      if (!answered) atomicCAS(&g_dp_status, 0, 1);
+      s_go = (answered && (w >> 31) == 0u) ? 1 : 0;
     }
-    const bool ok = wait_all_ranks(a.flags_of[a.rank] + 0 * kMaxRanks, a.world, e);
-    if (!ok) atomicCAS(&g_dp_status, 0, 1);
-    s_go = ok ? 1 : 0;
   }
   __syncthreads();
 
@@ -147,47 +231,24 @@ __global__ void __launch_bounds__(256) dp_adam_kernel(const DpAdamArgs a) {
     if (t < 1) t = 1;
     const float d1 = static_cast<float>(1.0 - pow(static_cast<double>(a.h.beta1), static_cast<double>(t)));
     const float d2 = static_cast<float>(1.0 - pow(static_cast<double>(a.h.beta2), static_cast<double>(t)));
-    using V4 = Pack16<float>;
+    constexpr int kW = kWorld ? kWorld : kMaxRanks;
+    const int world = kWorld ? kWorld : a.world;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     // shard bounds are multiples of 4 except possibly the very end of the tensor
     const int64_t p_begin = a.begin >> 2, p_end = a.end >> 2;
-    for (int64_t i = p_begin + tid; i < p_end; i += stride) {
-      // all ranks' packets are requested before any is used: up to 8 independent NVLink loads in flight per thread
-      float4 gk[kMaxRanks];
-#pragma unroll
-      for (int k = 0; k < kMaxRanks; ++k)
-        if (k < a.world) gk[k] = __ldcg(reinterpret_cast<const float4*>(a.g_of[k]) + i);
-      float4 acc = gk[0];
-#pragma unroll
-      for (int k = 1; k < kMaxRanks; ++k)  // fixed rank order: the same bits whoever owns the shard
-        if (k < a.world) {
-          acc.x += gk[k].x;
-          acc.y += gk[k].y;
-          acc.z += gk[k].z;
-          acc.w += gk[k].w;
-        }
-      const V4 p = ld_stream(reinterpret_cast<const V4*>(a.p) + i);
-      const V4 m = ld_stream(reinterpret_cast<const V4*>(a.m) + i);
-      const V4 v = ld_stream(reinterpret_cast<const V4*>(a.v) + i);
-      const float g[4] = {acc.x, acc.y, acc.z, acc.w};
-      V4 po, mo, vo;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) adam_one<false>(p.v[e], g[e], m.v[e], v.v[e], a.h, d1, d2, po.v[e], mo.v[e], vo.v[e]);
-      st_stream(reinterpret_cast<V4*>(a.m) + i, mo);
-      st_stream(reinterpret_cast<V4*>(a.v) + i, vo);
-      if (kBcast != 3) st_stream(reinterpret_cast<V4*>(a.p) + i, po);
-      bcast_x4<kBcast>(a, i, po);
-    }
-    for (int64_t i = (p_end << 2) + tid; i < a.end; i += stride) {  // ragged end of the last shard
-      float g = __ldcg(a.g_of[0] + i);
-      for (int k = 1; k < a.world; ++k) g += __ldcg(a.g_of[k] + i);
+    int64_t i = p_begin + tid;
+    for (; i + (kUnroll - 1) * stride < p_end; i += kUnroll * stride) update_packets<kBcast, kW, kUnroll>(a, world, i, stride, d1, d2);
+    for (; i < p_end; i += stride) update_packets<kBcast, kW, 1>(a, world, i, stride, d1, d2);
+    for (int64_t j = (p_end << 2) + tid; j < a.end; j += stride) {  // ragged end of the last shard
+      float g = __ldcg(a.g_of[0] + j);
+      for (int k = 1; k < a.world; ++k) g += __ldcg(a.g_of[k] + j);
       float po, mo, vo;
-      adam_one<false>(a.p[i], g, a.m[i], a.v[i], a.h, d1, d2, po, mo, vo);
-      a.m[i] = mo;
-      a.v[i] = vo;
-      if (kBcast != 3) a.p[i] = po;
-      bcast_x1<kBcast>(a, i, po);
+      adam_one<false>(a.p[j], g, a.m[j], a.v[j], a.h, d1, d2, po, mo, vo);
+      a.m[j] = mo;
+      a.v[j] = vo;
+      if (kBcast != 3) a.p[j] = po;
+      bcast_x1<kBcast>(a, j, po);
     }
   }
 
@@ -200,25 +261,41 @@ __global__ void __launch_bounds__(256) dp_adam_kernel(const DpAdamArgs a) {
       const uint32_t e = s_epoch;
       __threadfence_system();
       for (int k = 0; k < a.world; ++k) st_release_sys(a.flags_of[k] + 1 * kMaxRanks + a.rank, e);
-      const bool ok = wait_all_ranks(a.flags_of[a.rank] + 1 * kMaxRanks, a.world, e);
-      if (!ok) atomicCAS(&g_dp_status, 0, 2);
       *reinterpret_cast<volatile uint32_t*>(a.epoch) = e;
       __threadfence();
+      bool ok = true;
+      if (!a.defer_done) ok = wait_all_ranks(a.flags_of[a.rank] + 1 * kMaxRanks, a.world, e);
+      // step-end fence: the done words of every slot of this pool, each against that slot's own epoch (slots
+      // that were launched earlier on this stream have published theirs; unused slots read 0 >= 0)
+      for (int sl = 0; ok && sl < a.fence_slots; ++sl) {
+        const uint32_t es = *reinterpret_cast<const volatile uint32_t*>(a.epoch_base + sl);
+        ok = wait_all_ranks(a.flags_base + (static_cast<size_t>(sl) * 2 + 1) * kMaxRanks, a.world, es);
+      }
+      if (!ok) atomicCAS(&g_dp_status, 0, 2);
     }
   }
 }
 
-// 'DPAD' payload: the Adam payload <ffff fI> followed by <i> slot (index of this op's flag block).
+// 'DPAD' payload: the Adam payload <ffff fI> followed by <i> slot (index of this op's flag block) and, optionally,
+// <ii> defer_done (1: leave the done-phase wait to the step's fence), fence_slots (> 0: this op is the fence).
 constexpr uint32_t kSchemaDpAdam = 0x44415044u;  // 'DPAD' little-endian
 struct DpAttrs {
   AdamHyper h;
   int32_t slot;
+  int32_t defer_done = 0;
+  int32_t fence_slots = 0;
 };
 bool read_dp_attrs(const void* attr, DpAttrs* out) {
   const AttrBlob& b = blob_of(attr);
   if (b.schema_id != kSchemaDpAdam || !b.data || b.bytes < 28) return false;
   std::memcpy(&out->h, b.data, 24);
   std::memcpy(&out->slot, static_cast<const uint8_t*>(b.data) + 24, 4);
+  out->defer_done = out->fence_slots = 0;
+  if (b.bytes >= 36) {
+    std::memcpy(&out->defer_done, static_cast<const uint8_t*>(b.data) + 28, 4);
+    std::memcpy(&out->fence_slots, static_cast<const uint8_t*>(b.data) + 32, 4);
+  }
+  if (out->fence_slots < 0 || out->fence_slots > kMaxSlots) return false;
   return out->slot >= 0 && out->slot < kMaxSlots;
 }
 
@@ -277,7 +354,12 @@ Status dp_adam_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, con
     }
     a.epoch = reinterpret_cast<uint32_t*>(gp->mine + kFlagsBytes) + at.slot;
     a.done = reinterpret_cast<uint32_t*>(gp->mine + kFlagsBytes) + kMaxSlots + at.slot;
+    a.go = reinterpret_cast<uint32_t*>(gp->mine + kFlagsBytes) + 2 * kMaxSlots + at.slot;
+    a.flags_base = reinterpret_cast<const uint32_t*>(gp->mine);
+    a.epoch_base = reinterpret_cast<const uint32_t*>(gp->mine + kFlagsBytes);
   }
+  a.defer_done = at.defer_done != 0 ? 1 : 0;
+  a.fence_slots = at.fence_slots;
   const void* must_align[] = {in[0].data, in[1].data, in[2].data, in[3].data, bcast_mine};
   for (const void* q : must_align)
     if (!aligned_to(q, 16)) return Status::InvalidArgument;
@@ -291,24 +373,37 @@ Status dp_adam_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, con
   const int64_t packets = (n + 3) / 4;
   a.begin = std::min<int64_t>(n, (packets * a.rank / a.world) * 4);
   a.end = std::min<int64_t>(n, (packets * (a.rank + 1) / a.world) * 4);
-  // One CTA per SM at most: 256 threads x 80 registers fit beside a persistent GEMM CTA (192 x 136), two would not,
-  // and a GEMM launched while this kernel is resident must still find room on every SM.
+  // One CTA per SM at most: 256 threads x (at most) 144 registers fit beside a persistent GEMM CTA (192 x 136), two
+  // would not, and a GEMM launched while this kernel is resident must still find room on every SM.
   const int grid = streaming_grid((a.end - a.begin) / 4 + 1, 256, 1);
   // The SM's L1/shared split is one setting for all resident CTAs. The GEMMs run with the largest shared-memory
   // split; asking for the same split here lets these CTAs and GEMM CTAs join each other's SMs in either order
   // (with the default split, a GEMM CTA would have to wait for the SM to drain first).
-  static bool carveout_set = false;
-  if (!carveout_set) {
-    cudaFuncSetAttribute(dp_adam_kernel<1>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    cudaFuncSetAttribute(dp_adam_kernel<2>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    cudaFuncSetAttribute(dp_adam_kernel<3>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    carveout_set = true;
-  }
-  cudaGetLastError();
+  // Ranks unrolled for 2, 4 and 8 (predicated loop otherwise); packets per thread chosen so that at least eight
+  // remote loads are in flight per thread.
+  auto launch = [&](auto bc, auto wd, auto un) {
+    constexpr int kB = decltype(bc)::value, kWd = decltype(wd)::value, kUn = decltype(un)::value;
+    static PerDeviceOnce carveout;  // a per-device function attribute
+    carveout.run([] {
+      cudaFuncSetAttribute(dp_adam_kernel<kB, kWd, kUn>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+      return true;
+    });
+    cudaGetLastError();
+    dp_adam_kernel<kB, kWd, kUn><<<grid, 256, 0, stream>>>(a);
+  };
+  auto by_world = [&](auto bc) {
+    using I = std::integral_constant<int, 0>;
+    switch (a.world) {
+      case 2: launch(bc, std::integral_constant<int, 2>{}, std::integral_constant<int, 4>{}); break;
+      case 4: launch(bc, std::integral_constant<int, 4>{}, std::integral_constant<int, 3>{}); break;
+      case 8: launch(bc, std::integral_constant<int, 8>{}, std::integral_constant<int, 2>{}); break;
+      default: launch(bc, I{}, std::integral_constant<int, 1>{}); break;
+    }
+  };
   switch (bcast_kind) {
-    case 1: dp_adam_kernel<1><<<grid, 256, 0, stream>>>(a); break;
-    case 2: dp_adam_kernel<2><<<grid, 256, 0, stream>>>(a); break;
-    default: dp_adam_kernel<3><<<grid, 256, 0, stream>>>(a); break;
+    case 1: by_world(std::integral_constant<int, 1>{}); break;
+    case 2: by_world(std::integral_constant<int, 2>{}); break;
+    default: by_world(std::integral_constant<int, 3>{}); break;
   }
   return launch_status();
 }

@@ -838,7 +838,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 // dropped A_lo*B_lo term is below 2^-22 of the product). Same roles, barriers and epilogue as the 16-bit kernel;
 // tile 128x128, k slab 32 (one 128-byte swizzle row of fp32), 3 stages of 4 x 16 KiB.
 // The tensor core rounds its fp32 accumulator toward zero at every k step, an error that grows linearly with the
-// number of steps accumulated in place. K is therefore cut into chunks of 512: each chunk accumulates from zero in
+// number of steps accumulated in place. K is therefore cut into chunks of 256: each chunk accumulates from zero in
 // one of four 128-column accumulators, and the epilogue warps add the chunk results in registers with ordinary
 // round-to-nearest fp32 additions while the next chunks are already being multiplied.
 constexpr int k3TileN = 128;
@@ -1136,7 +1136,24 @@ struct GemmChoice {
 // added in split order by splitk_finish_kernel (deterministic). Considered only when it is predicted to win and each
 // part keeps at least 8 k blocks.
 // AICF_GEMM_CTA_GROUP=1|2, AICF_GEMM_TILE_N=256|128|64 and AICF_GEMM_SPLITK=<n> (0 or 1 = off) override the choice
-// (tuning and tests).
+// (tuning and tests). The environment is read once, at the first GEMM of the process.
+struct GemmEnvOverrides {
+  int cta_group = 0;  // 0 = no override
+  int tile_n = 0;
+  bool splitk_set = false;
+  int splitk = 0;
+};
+const GemmEnvOverrides& gemm_env_overrides() {
+  static const GemmEnvOverrides env = [] {
+    GemmEnvOverrides e;
+    if (const char* s = std::getenv("AICF_GEMM_CTA_GROUP")) e.cta_group = s[0] == '1' ? 1 : s[0] == '2' ? 2 : 0;
+    if (const char* s = std::getenv("AICF_GEMM_TILE_N")) e.tile_n = std::atoi(s);
+    if (const char* s = std::getenv("AICF_GEMM_SPLITK")) e.splitk_set = true, e.splitk = std::atoi(s);
+    return e;
+  }();
+  return env;
+}
+
 GemmChoice choose_gemm(const GemmProblem& p) {
   GemmChoice c;
   const int64_t sms = sm_count();
@@ -1196,19 +1213,15 @@ GemmChoice choose_gemm(const GemmProblem& p) {
       c.splits = best_s;
     }
   }
-  if (const char* e = std::getenv("AICF_GEMM_CTA_GROUP")) {
-    if (e[0] == '1') c.pair = false;
-    if (e[0] == '2' && p.M > kTileM) c.pair = true, c.splits = 1;
+  const GemmEnvOverrides& env = gemm_env_overrides();
+  if (env.cta_group == 1) c.pair = false;
+  if (env.cta_group == 2 && p.M > kTileM) c.pair = true, c.splits = 1;
+  if (env.tile_n == 256 || env.tile_n == 128 || env.tile_n == 64) {
+    if (env.tile_n != c.tn) c.splits = 1;
+    c.tn = env.tile_n;
   }
-  if (const char* e = std::getenv("AICF_GEMM_TILE_N")) {
-    const int v = std::atoi(e);
-    if (v == 256 || v == 128 || v == 64) {
-      if (v != c.tn) c.splits = 1;
-      c.tn = v;
-    }
-  }
-  if (const char* e = std::getenv("AICF_GEMM_SPLITK")) {
-    int v = std::atoi(e);
+  if (env.splitk_set) {
+    int v = env.splitk;
     if (v <= 1) {
       c.splits = 1;
     } else if (!c.pair) {
@@ -1334,12 +1347,10 @@ Status gemm_tcgen05_run(const GemmProblem& p, void* ws, size_t ws_bytes, cudaStr
   g.splits = choice.splits;
   g.partial = choice.splits > 1 ? static_cast<float*>(ws) : nullptr;
 
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 16) dev = 0;
+  const int dev = device_slot();  // -1: a device beyond the per-device tables, set up again on every call
   cudaGetLastError();
   if (pair) {
-    static int max_clusters[16] = {0};
+    static std::atomic<int> max_clusters[kMaxDevices] = {};
     cudaLaunchConfig_t cfg{};
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1351,7 +1362,8 @@ Status gemm_tcgen05_run(const GemmProblem& p, void* ws, size_t ws_bytes, cudaStr
     cfg.stream = stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (max_clusters[dev] == 0) {
+    int device_clusters = dev >= 0 ? max_clusters[dev].load(std::memory_order_acquire) : 0;
+    if (device_clusters == 0) {
       if (cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(k2SmemBytes)) != cudaSuccess) {
         cudaGetLastError();
@@ -1363,10 +1375,11 @@ Status gemm_tcgen05_run(const GemmProblem& p, void* ws, size_t ws_bytes, cudaStr
         cudaGetLastError();
         n = sm_count() / 2;
       }
-      max_clusters[dev] = n;
+      device_clusters = n;
+      if (dev >= 0) max_clusters[dev].store(n, std::memory_order_release);
     }
     const int64_t pair_tiles = ((p.M + 2 * kTileM - 1) / (2 * kTileM)) * ((p.N + kTileN - 1) / kTileN);
-    const int clusters = static_cast<int>(pair_tiles < max_clusters[dev] ? pair_tiles : max_clusters[dev]);
+    const int clusters = static_cast<int>(pair_tiles < device_clusters ? pair_tiles : device_clusters);
     cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters));
     if (cudaLaunchKernelEx(&cfg, gemm_tcgen05_2cta_kernel, ta, tb, g) != cudaSuccess) {
       cudaGetLastError();
@@ -1378,14 +1391,13 @@ Status gemm_tcgen05_run(const GemmProblem& p, void* ws, size_t ws_bytes, cudaStr
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
   auto go = [&](auto tag) -> Status {
     constexpr int TN = decltype(tag)::value;
-    static bool attr_set[16] = {false};
-    if (!attr_set[dev]) {
-      if (cudaFuncSetAttribute(gemm_tcgen05_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(SingleCfg<TN>::kSmem)) != cudaSuccess) {
-        cudaGetLastError();
-        return Status::Internal;
-      }
-      attr_set[dev] = true;
+    static PerDeviceOnce smem_opt_in;
+    if (!smem_opt_in.run([] {
+          return cudaFuncSetAttribute(gemm_tcgen05_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(SingleCfg<TN>::kSmem)) == cudaSuccess;
+        })) {
+      cudaGetLastError();
+      return Status::Internal;
     }
     gemm_tcgen05_kernel<TN><<<grid, kThreads, SingleCfg<TN>::kSmem, stream>>>(ta, tb, g);
     return launch_status();
@@ -1477,17 +1489,13 @@ Status gemm_tf32x3_run(const GemmProblem& p, void* ws, size_t ws_bytes, cudaStre
             (static_cast<uint32_t>(kTileM >> 4) << 24);
   g.c_vec_ok = aligned_to(p.C.data, 16) && ((p.C.rs * 4) % 16 == 0);
 
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 16) dev = 0;
-  static bool attr_set[16] = {false};
-  if (!attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(k3SmemBytes)) != cudaSuccess) {
-      cudaGetLastError();
-      return Status::Internal;
-    }
-    attr_set[dev] = true;
+  static PerDeviceOnce smem_opt_in;
+  if (!smem_opt_in.run([] {
+        return cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(k3SmemBytes)) == cudaSuccess;
+      })) {
+    cudaGetLastError();
+    return Status::Internal;
   }
   const int64_t tiles = ((p.M + kTileM - 1) / kTileM) * ((p.N + k3TileN - 1) / k3TileN);
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());

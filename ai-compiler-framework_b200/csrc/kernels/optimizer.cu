@@ -241,8 +241,11 @@ Status launch_adam(AdamArgs a, cudaStream_t stream) {
   // arrays) through the per-thread-load kernel below.
   const int64_t nchunks = vec_ok ? a.n / kBulkChunk : 0;
   if (nchunks >= 2 * static_cast<int64_t>(sm_count())) {
-    static bool attr_ok = cudaFuncSetAttribute(adam_bulk_kernel<kDiv, kLp>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               static_cast<int>(kBulkSmem)) == cudaSuccess;
+    static PerDeviceOnce smem_opt_in;  // function attributes are per device
+    const bool attr_ok = smem_opt_in.run([] {
+      return cudaFuncSetAttribute(adam_bulk_kernel<kDiv, kLp>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(kBulkSmem)) == cudaSuccess;
+    });
     if (attr_ok) {
       const int per_sm = static_cast<int>((227 * 1024) / (kBulkSmem + 1024));
       const int grid = streaming_grid(nchunks, 1, per_sm);

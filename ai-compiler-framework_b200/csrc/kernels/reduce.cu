@@ -342,8 +342,7 @@ constexpr size_t kNoAllocScratchBytes = size_t(512) << 10;
 static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchBytes / sizeof(float)];
 
 namespace {
-constexpr int kMaxDevices = 64;
-float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};  // kMaxDevices: the one limit of every per-device table (common.cuh)
 std::mutex g_noalloc_mu;
 
 // Device address of the scratch array on the current device (looked up on the first call there).

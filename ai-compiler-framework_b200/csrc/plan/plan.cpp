@@ -206,8 +206,11 @@ size_t assign_arena(std::vector<Value*>& vals, int num_ops, std::map<int, size_t
 }
 
 int enqueue_all(aicf_plan* p, cudaStream_t main, std::vector<cudaEvent_t>* marks = nullptr) {
-  // vid -> event a later op on `main` must wait for (pending all_reduce on the comm stream)
-  std::map<int, cudaEvent_t> pending;
+  // Values in use by ops forked to the communication stream, and the event that ends that use: `pending` holds what
+  // a forked op writes (a later reader or writer on `main` waits), `pending_reads` what it only reads (a later
+  // WRITER on `main` waits: write after read). The communication stream runs its ops in order, so the event of the
+  // latest forked op that touches a value covers the earlier ones.
+  std::map<int, cudaEvent_t> pending, pending_reads;
   // AICF_PLAN_NO_OVERLAP=1 keeps the exchange on the main stream (to measure what the side stream buys)
   static const bool no_overlap = std::getenv("AICF_PLAN_NO_OVERLAP") != nullptr;
   const bool overlap = (aicf_b200_dp_world_size() > 1 || p->peer_world > 1) && !marks && !no_overlap;
@@ -224,10 +227,21 @@ int enqueue_all(aicf_plan* p, cudaStream_t main, std::vector<cudaEvent_t>* marks
       pending.erase(it);
       return rc;
     };
+    auto wait_for_readers = [&](int vid) -> int {
+      Value* v = p->resolve(vid);
+      if (!v) return AICF_OK;
+      auto it = pending_reads.find(v->vid);
+      if (it == pending_reads.end()) return AICF_OK;
+      const int rc = check_cuda(cudaStreamWaitEvent(main, it->second, 0), "cudaStreamWaitEvent(join readers)");
+      pending_reads.erase(it);
+      return rc;
+    };
     for (int vid : op.in)
       if (int rc = wait_for(vid)) return rc;
-    for (int vid : op.out)
+    for (int vid : op.out) {
       if (int rc = wait_for(vid)) return rc;
+      if (int rc = wait_for_readers(vid)) return rc;
+    }
 
     cudaStream_t s = main;
     const bool on_comm = overlap && (op.kind == OpKind::AllReduce || op.kind == OpKind::DpAdamStep) && op.ev_ready && op.ev_done;
@@ -250,9 +264,15 @@ int enqueue_all(aicf_plan* p, cudaStream_t main, std::vector<cudaEvent_t>* marks
         Value* v = p->resolve(vid);
         if (v) pending[v->vid] = op.ev_done;
       }
+      for (int vid : op.in) {
+        Value* v = p->resolve(vid);
+        if (v && !pending.count(v->vid)) pending_reads[v->vid] = op.ev_done;
+      }
     }
   }
   for (auto& kv : pending)  // every forked branch rejoins before the step ends
+    if (int rc = check_cuda(cudaStreamWaitEvent(main, kv.second, 0), "cudaStreamWaitEvent(final join)")) return rc;
+  for (auto& kv : pending_reads)
     if (int rc = check_cuda(cudaStreamWaitEvent(main, kv.second, 0), "cudaStreamWaitEvent(final join)")) return rc;
   if (marks)
     if (int rc = check_cuda(cudaEventRecord(marks->back(), main), "cudaEventRecord(profile)")) return rc;
@@ -442,6 +462,16 @@ int aicf_b200_plan_finalize(aicf_plan* p) {
         if (v->first < 0) v->first = i;
         v->last = i;
       }
+  }
+  // Ops that may run on the communication stream (all_reduce, dp_adam_step) finish at an unknown point after their
+  // position in op order, so every value they touch stays live to the end of the step: its arena bytes are never
+  // handed to a value that a later main-stream op writes while the exchange may still be reading.
+  for (int i = 0; i < nops; ++i) {
+    const Op& op = p->ops[static_cast<size_t>(i)];
+    if (op.kind != OpKind::AllReduce && op.kind != OpKind::DpAdamStep) continue;
+    for (const std::vector<int>* lst : {&op.in, &op.out})
+      for (int vid : *lst)
+        if (Value* v = p->resolve(vid)) v->last = nops - 1;
   }
   // a value that is an alias target of a persistent value is persistent too
   for (auto& kv : p->values)

@@ -21,15 +21,25 @@ namespace aicf::cuda {
 namespace {
 
 // ---- dispatch scratch arena ------------------------------------------------------------------
-// Owned arena grows on demand, but never while the target stream is being captured (allocation
-// is illegal there): a capture that needs more than is available fails with Internal.
+// One arena per device, grown on demand, but never while the target stream is being captured (allocation is illegal
+// there): a capture that needs more than is available gets no workspace.
+// A block that has been handed to a launch is never freed or moved before the process exits: a CUDA graph captured
+// earlier keeps the block's address inside its kernel nodes, so growing allocates a second, larger block and retires
+// the first one in place. Growth is geometric, so the retired blocks together stay below the size of the live one.
+// The arena is shared by every stream of its device: two launches that need workspace and are not ordered against
+// each other (different streams, no event between them) use the same bytes. Callers that run such launches
+// concurrently give each stream its own buffer through aicf_b200_launch_ws instead.
+constexpr int kArenaDevices = 64;
+struct DeviceArena {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  std::vector<void*> retired;  // earlier blocks, kept alive for graphs that captured them
+};
 struct DispatchArena {
   std::mutex mu;
   void* user_ptr = nullptr;
   size_t user_bytes = 0;
-  void* own_ptr = nullptr;
-  size_t own_bytes = 0;
-  int own_device = -1;
+  DeviceArena dev[kArenaDevices];
 };
 DispatchArena& arena() {
   static DispatchArena a;
@@ -47,10 +57,14 @@ Status acquire_workspace(size_t need, cudaStream_t stream, void** ptr, size_t* b
     return Status::Ok;
   }
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (a.own_ptr && a.own_device == dev && need <= a.own_bytes) {
-    *ptr = a.own_ptr;
-    *bytes = a.own_bytes;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kArenaDevices) {
+    cudaGetLastError();
+    return Status::Internal;
+  }
+  DeviceArena& d = a.dev[dev];
+  if (d.ptr && need <= d.bytes) {
+    *ptr = d.ptr;
+    *bytes = d.bytes;
     return Status::Ok;
   }
   cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
@@ -59,23 +73,22 @@ Status acquire_workspace(size_t need, cudaStream_t stream, void** ptr, size_t* b
     return Status::Internal;
   }
   if (cs != cudaStreamCaptureStatusNone) return Status::Internal;  // cannot allocate under capture
-  if (a.own_ptr) {
-    cudaSetDevice(a.own_device);
-    cudaFree(a.own_ptr);
-    cudaSetDevice(dev);
-    a.own_ptr = nullptr;
-    a.own_bytes = 0;
-  }
-  const size_t want = need > kDefaultArenaBytes ? need : kDefaultArenaBytes;
-  if (cudaMalloc(&a.own_ptr, want) != cudaSuccess) {
+  size_t want = need > kDefaultArenaBytes ? need : kDefaultArenaBytes;
+  if (want < 2 * d.bytes) want = 2 * d.bytes;
+  void* fresh = nullptr;
+  if (cudaMalloc(&fresh, want) != cudaSuccess) {
     cudaGetLastError();
-    a.own_ptr = nullptr;
-    return Status::Internal;
+    want = need;  // the doubled size may not fit; the request itself might
+    if (cudaMalloc(&fresh, want) != cudaSuccess) {
+      cudaGetLastError();
+      return Status::Internal;
+    }
   }
-  a.own_bytes = want;
-  a.own_device = dev;
-  *ptr = a.own_ptr;
-  *bytes = a.own_bytes;
+  if (d.ptr) d.retired.push_back(d.ptr);
+  d.ptr = fresh;
+  d.bytes = want;
+  *ptr = d.ptr;
+  *bytes = d.bytes;
   return Status::Ok;
 }
 

@@ -755,6 +755,11 @@ class PlannedExecutor:
     plan's arena, zero-filled for 'opt.step*', 'opt.m.*' and 'opt.v.*', and are returned as `aicf_cuda.Tensor` views.
     Calling run()/capture() again with tensors at other addresses rebuilds the plan (statics start afresh) and
     drops a captured graph.
+
+    AICF_WARMUP=1 in the environment (read at every run()/capture(), like the reference's executor,
+    python/aicf_fw/core_v2/exec.py:396,422-431) makes a step that leaves the model where it is, so that gradients
+    of a first step can be inspected before any weight moves: `step_inc` becomes a copy of its input to its output
+    (the counter does not advance) and every `adam_step` runs with lr = 0 (moments are still updated, as there).
     """
 
     def __init__(self, *, ir: IRGraph, lowered: Sequence[LoweredOp], plan: BindingPlan, device: Any = None,
@@ -768,6 +773,7 @@ class PlannedExecutor:
         self._captured = False
         self._cplan = None
         self._bound_ptrs: Dict[int, int] = {}
+        self._plan_is_warmup = False
         if self.opts.require_kernel_id:
             for i, it in enumerate(self.lowered):
                 if it.get("kernel_id") is None:
@@ -808,6 +814,28 @@ class PlannedExecutor:
         if callable(contiguous) and not contiguous():
             raise RuntimeError(f"[plan] '{spec.name}' must be contiguous")
 
+    @staticmethod
+    def _warmup_requested() -> bool:
+        import os
+        return os.getenv("AICF_WARMUP", "0") == "1"
+
+    def _effective_lowered(self, warmup: bool) -> List[Dict[str, Any]]:
+        """The lowered list as it is launched: unchanged, or the warm-up form (see the class docstring)."""
+        if not warmup:
+            return self.lowered
+        out = []
+        for it in self.lowered:
+            op = str(it["op"])
+            if op == "step_inc":
+                src, dst = list(it.get("inputs", [])), list(it.get("outputs", []))
+                if src and dst and int(src[0]) != int(dst[0]):
+                    out.append({"op": "copy", "inputs": src[:1], "outputs": dst[:1], "attrs": {}, "kernel_id": "copy_i32_v0"})
+                continue  # in place: copying a counter onto itself is nothing
+            if op == "adam_step":
+                it = dict(it, attrs=dict(it.get("attrs") or {}, lr=0.0))
+            out.append(it)
+        return out
+
     def build_env(self, *, inputs: Dict[str, Any], params: Dict[str, Any], reuse_static: bool = False) -> Dict[int, Any]:
         from .plan import ROLE_INPUT as R_IN, ROLE_PARAM as R_PARAM, ROLE_STATIC as R_STATIC, Plan, ValueSpec
         bound: Dict[int, Any] = {}
@@ -824,7 +852,8 @@ class PlannedExecutor:
                 spec = self.plan.specs[vid]
                 raise RuntimeError(f"[plan] env missing vid{vid} ({spec.name}) role={spec.role}")
         ptrs = {vid: int(t.data_ptr()) for vid, t in bound.items()}
-        if self._cplan is None or ptrs != self._bound_ptrs or not reuse_static:
+        warmup = self._warmup_requested()
+        if self._cplan is None or ptrs != self._bound_ptrs or not reuse_static or warmup != self._plan_is_warmup:
             if self._cplan is not None:
                 self._cplan.close()
             role_code = {ROLE_INPUT: R_IN, ROLE_PARAM: R_PARAM, ROLE_STATIC: R_STATIC}
@@ -832,7 +861,8 @@ class PlannedExecutor:
             specs = [ValueSpec(s.vid, s.name, tuple(s.shape), short_dtype(s.dtype), role_code[s.role],
                                persistent=(s.role == ROLE_STATIC))
                      for _, s in sorted(self.plan.specs.items())]
-            self._cplan = Plan(self.ir.name, specs, self.lowered, bind=bound)
+            self._cplan = Plan(self.ir.name, specs, self._effective_lowered(warmup), bind=bound)
+            self._plan_is_warmup = warmup
             self._bound_ptrs = ptrs
             self._captured = False
         self.env = {vid: bound[vid] if vid in bound else self._cplan.tensor(vid) for vid in sorted(self.plan.specs)}
@@ -842,7 +872,7 @@ class PlannedExecutor:
     def _execute_lowered(self, *, stream: int) -> None:
         from . import _C
         from .plan import pack_attrs
-        for i, it in enumerate(self.lowered):
+        for i, it in enumerate(self._effective_lowered(self._warmup_requested())):
             op = str(it["op"])
             kind = opkind_from_name(op)
             ins = [self.env[int(v)] for v in it.get("inputs", [])]

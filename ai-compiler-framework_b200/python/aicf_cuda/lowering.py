@@ -17,7 +17,7 @@ from __future__ import annotations
 
 from typing import Any, Dict, List, Sequence, Tuple
 
-from .plan import ROLE_INPUT, ROLE_PARAM, ROLE_STATIC, ValueSpec
+from .spec import ROLE_INPUT, ROLE_PARAM, ROLE_STATIC, ValueSpec
 
 
 def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str = "bf16", global_batch: int | None = None,
@@ -154,10 +154,14 @@ def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str 
                 op("relu_bwd", [dX, acts[i]], [dX], None, relu_bwd_kid)  # in place: dX becomes d(pre-activation)
             dY = dX
         if fused_dp:
-            # after dX: from here on this rank no longer reads layer i's weights, so peers may overwrite them
+            # after dX: from here on this rank no longer reads layer i's weights, so peers may overwrite them.
+            # No exchange waits for its peers' "done" words by itself: nothing later in the step reads a working
+            # copy or rewrites a gradient, so the last exchange of the step (layer 0's bias) is the one fence for all.
             outs = [W[i], mW[i], vW[i]] + ([Wlp[i]] if mixed else [])
-            op("dp_adam_step", [W[i], dW[i], mW[i], vW[i], step], outs, dict(hyper, slot=2 * i), "dp_adam_step_f32_p2p_v0")
-            op("dp_adam_step", [b[i], db[i], mb[i], vb[i], step], [b[i], mb[i], vb[i]], dict(hyper, slot=2 * i + 1),
+            op("dp_adam_step", [W[i], dW[i], mW[i], vW[i], step], outs, dict(hyper, slot=2 * i, defer_done=True),
+               "dp_adam_step_f32_p2p_v0")
+            fence = {"fence_slots": 2 * L} if i == 0 else {"defer_done": True}
+            op("dp_adam_step", [b[i], db[i], mb[i], vb[i], step], [b[i], mb[i], vb[i]], dict(hyper, slot=2 * i + 1, **fence),
                "dp_adam_step_f32_p2p_v0")
     if fused_dp:
         return vals, ops

@@ -14,9 +14,9 @@ from dataclasses import dataclass, field
 from typing import Any, Dict, Iterable, List, Optional, Sequence, Tuple
 
 from ._lib import check, lib
+from .spec import ROLE_INPUT, ROLE_PARAM, ROLE_STATIC, ValueSpec, classify_role, needs_zero_init  # noqa: F401  (re-exported)
 from .tensor import DTYPE_CODES, Tensor
 
-ROLE_INPUT, ROLE_PARAM, ROLE_STATIC = 0, 1, 2
 
 # Attr schema tags: the contract is the numeric value (the reference spells some big-endian).
 SCHEMA_GEMM = 0x47454D4D
@@ -66,10 +66,14 @@ def pack_attrs(op: str, attrs: Optional[Dict[str, Any]]) -> Tuple[int, bytes]:
             payload += struct.pack("<fI", float(a.get("weight_decay", 0.0)), 1 if a.get("decoupled", False) else 0)
         return SCHEMA_ADAM, payload
     if op == "dp_adam_step":
-        return SCHEMA_DP_ADAM, struct.pack("<fffffIi", float(a.get("lr", 1e-3)), float(a.get("beta1", 0.9)),
-                                           float(a.get("beta2", 0.999)), float(a.get("eps", 1e-8)),
-                                           float(a.get("weight_decay", 0.0)), 1 if a.get("decoupled", False) else 0,
-                                           int(a["slot"]))
+        payload = struct.pack("<fffffIi", float(a.get("lr", 1e-3)), float(a.get("beta1", 0.9)),
+                              float(a.get("beta2", 0.999)), float(a.get("eps", 1e-8)),
+                              float(a.get("weight_decay", 0.0)), 1 if a.get("decoupled", False) else 0, int(a["slot"]))
+        if a.get("defer_done") or a.get("fence_slots"):
+            # defer_done: this op does not wait for the peers' "done" words; fence_slots = n: this op (the last
+            # exchange of the step) waits for the done words of slots [0, n) before it finishes
+            payload += struct.pack("<ii", 1 if a.get("defer_done") else 0, int(a.get("fence_slots", 0)))
+        return SCHEMA_DP_ADAM, payload
     if op == "bias_corr":
         return SCHEMA_BIAS_CORR, struct.pack("<ff", float(a.get("beta1", 0.9)), float(a.get("beta2", 0.999)))
     if op == "sgd_step" and "lr" in a:
@@ -104,37 +108,6 @@ def pack_attrs_like_reference_executor(op: str, attrs: Optional[Dict[str, Any]])
         return SCHEMA_ADAM, struct.pack("<ffff", float(a.get("lr", 1e-3)), float(a.get("beta1", 0.9)),
                                         float(a.get("beta2", 0.999)), float(a.get("eps", 1e-8)))
     return 0, b""
-
-
-_PARAM_RE = re.compile(r"^\d+\.(W|b)$")
-
-
-def classify_role(name: str) -> int:
-    """Role of a value from its name, as the reference's binding plan decides it:
-    'x' / 't' (and 'labels' for the cross-entropy graphs) are inputs, '<n>.W' / '<n>.b' are
-    parameters, everything else is a plan-owned static."""
-    if name in ("x", "t", "labels"):
-        return ROLE_INPUT
-    if _PARAM_RE.match(name):
-        return ROLE_PARAM
-    return ROLE_STATIC
-
-
-def needs_zero_init(name: str) -> bool:
-    return name.startswith("opt.step") or name.startswith("opt.m.") or name.startswith("opt.v.")
-
-
-@dataclass
-class ValueSpec:
-    vid: int
-    name: str
-    shape: Tuple[int, ...]
-    dtype: str
-    role: Optional[int] = None        # None -> classify_role(name)
-    persistent: bool = False          # keep out of arena reuse (read after the step)
-    zero_init: Optional[bool] = None  # None -> needs_zero_init(name)
-    alias_of: Optional[int] = None
-    peer_visible: bool = False        # mapped by the other data-parallel ranks (gradients, broadcast copies)
 
 
 def plan_to_json(name: str, values: Iterable[ValueSpec], lowered: Sequence[Dict[str, Any]]) -> str:
@@ -176,6 +149,7 @@ class Plan:
         self.values: Dict[int, ValueSpec] = {}
         self.by_name: Dict[str, int] = {}
         self.lowered = [dict(it) for it in lowered]
+        self._has_exchange = any(str(it.get("op")) == "dp_adam_step" for it in self.lowered)
         self._keep: List[Any] = []
         for v in values:
             role = classify_role(v.name) if v.role is None else v.role
@@ -322,7 +296,17 @@ class Plan:
         self._captured = False
 
     def sync(self) -> None:
+        """Waits for everything the plan has enqueued. For a plan with dp_adam_step ops it then reads the wait-status
+        word and raises if a cross-GPU wait of the exchange expired: some rank skipped an update, the replicas can
+        no longer be assumed equal, and the model and optimizer state must be restored from a checkpoint. The word
+        is left set (clear it with `_C.wait_status(clear=True)`)."""
         check(lib.aicf_b200_plan_sync(self._h), "plan_sync")
+        if self._has_exchange:
+            st = int(lib.aicf_b200_wait_status(0))
+            if st > 0 and (st >> 17) & 3:
+                raise RuntimeError(f"[plan {self.name}] a bounded wait of the data-parallel exchange expired "
+                                   f"(phase {(st >> 17) & 3}: 1 = waiting for gradients, 2 = waiting for completion); "
+                                   "replicas may have diverged: restore parameters and optimizer state from a checkpoint")
 
     @property
     def graph_nodes(self) -> int:

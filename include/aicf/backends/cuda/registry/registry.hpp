@@ -62,7 +62,11 @@ class KernelRegistry {
 // Legacy runtime dispatch: first supported variant in priority order.
 Status Dispatch(const OpCall& call);
 
-// Scratch arena used by dispatch for variants whose query_workspace() is non-zero.
+// Scratch arena used by dispatch for variants whose query_workspace() is non-zero: one lazily allocated block per
+// device (64 MiB to start with, grown geometrically outside stream capture; outgrown blocks stay allocated because
+// captured graphs may still point into them). The arena belongs to the device, not to a stream: launches that need
+// workspace must be ordered against each other (same stream, or events between streams), or use
+// aicf_b200_launch_ws with a buffer of their own.
 // A caller-provided arena replaces the lazily allocated default (ptr == nullptr restores it).
 void set_dispatch_workspace(void* ptr, size_t bytes);
 

@@ -207,7 +207,14 @@ int aicf_b200_plan_bind(aicf_plan* plan, int vid, void* device_ptr);
  * peer-visible before finalize (gradients, broadcast working copies, biases) are placed in one pool allocation
  * per plan. After finalize every rank exports its pool as a 64-byte IPC handle (all zero when the plan has no
  * pool), the handles are exchanged by the caller, and open_peers maps the other ranks' pools
- * (handles = world x 64 bytes in rank order; the own entry is ignored). One process per GPU. */
+ * (handles = world x 64 bytes in rank order; the own entry is ignored). One process per GPU.
+ * Attrs of a dp_adam_step op: schema 'DPAD' (0x44415044), payload <fffffIi> lr, beta1, beta2, eps, weight_decay,
+ * decoupled, slot (index of the op's flag block, unique per op of a plan, < 60), optionally followed by <ii>
+ * defer_done, fence_slots. defer_done = 1: the op does not wait for the other ranks' "my stores into your memory are
+ * done" words; the plan must then end the step with a dp_adam_step op carrying fence_slots = n, which waits for
+ * those words of slots [0, n) before it completes. Without the two optional fields every op waits for itself.
+ * After a non-zero aicf_b200_wait_status (bits 17-18) the replicas are no longer known to agree: restore the model
+ * and optimizer state from a checkpoint before training on. */
 int aicf_b200_plan_set_peer_visible(aicf_plan* plan, int vid);
 int aicf_b200_plan_peer_handle(aicf_plan* plan, void* handle64, size_t* pool_bytes);
 int aicf_b200_plan_open_peers(aicf_plan* plan, int rank, int world, const void* handles);

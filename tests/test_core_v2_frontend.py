@@ -447,3 +447,53 @@ def test_front_end_and_executor_take_torch_dtypes_and_tensors(gpu):
     for k in h_par:
         np.testing.assert_array_equal(t_par[k].cpu().numpy(), a_par[k].numpy(), err_msg=k)
         assert not np.array_equal(t_par[k].cpu().numpy(), h_par[k]), f"{k} was not updated in place"
+
+
+# ---- AICF_WARMUP: a step that leaves the model where it is (reference exec.py:396,422-431) ---------------------------
+def test_warmup_rewrites_step_inc_and_adam_lr():
+    low = [{"op": "step_inc", "inputs": [0], "outputs": [1], "attrs": {}, "kernel_id": "step_inc_v0"},
+           {"op": "step_inc", "inputs": [2], "outputs": [2], "attrs": {}, "kernel_id": "step_inc_v0"},
+           {"op": "adam_step", "inputs": [3, 4, 5, 6, 7, 8], "outputs": [3, 5, 6], "attrs": {"lr": 0.01, "beta1": 0.9},
+            "kernel_id": "adam_step_f32_v0"},
+           {"op": "gemm", "inputs": [9, 10], "outputs": [11], "attrs": {"transB": True}, "kernel_id": "gemm_f32_naive_v0"}]
+    ir = cv.IRGraph(name="w")
+    ex = cv.PlannedExecutor(ir=ir, lowered=low, plan=cv.BindingPlan(name="w", inputs=[], params=[], statics=[], specs={}))
+    assert ex._effective_lowered(False) == low
+    w = ex._effective_lowered(True)
+    assert [it["op"] for it in w] == ["copy", "adam_step", "gemm"]  # the in-place step_inc has nothing to copy
+    assert (w[0]["inputs"], w[0]["outputs"], w[0]["kernel_id"]) == ([0], [1], "copy_i32_v0")
+    assert w[1]["attrs"] == {"lr": 0.0, "beta1": 0.9} and low[2]["attrs"]["lr"] == 0.01  # the original list is untouched
+    assert w[2] == low[3]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["run", "replay"])
+def test_warmup_mode_computes_gradients_and_moves_nothing(gpu, monkeypatch, mode):
+    from aicf_cuda.train_step import compile_train_step
+    dims, Bn = [24, 32, 8], 16
+    rng = np.random.default_rng(5)
+    batch = {"x": rng.standard_normal((Bn, dims[0])).astype(np.float32), "t": rng.standard_normal((Bn, dims[-1])).astype(np.float32)}
+
+    def one_step(warm):
+        if warm:
+            monkeypatch.setenv("AICF_WARMUP", "1")
+        else:
+            monkeypatch.delenv("AICF_WARMUP", raising=False)
+        ts = compile_train_step(dims, B=Bn, dtype="f32", optimizer="adam", lr=0.01, seed=1)
+        before = {k: v.numpy() for k, v in ts.params.items()}
+        if mode == "run":
+            ts.train_step(batch)
+        else:
+            ts.capture(batch)
+            ts.replay(1)
+        ts.sync()
+        return ts, before
+
+    warm, w_before = one_step(True)
+    real, r_before = one_step(False)
+    for k in w_before:
+        np.testing.assert_array_equal(warm.params[k].numpy(), w_before[k], err_msg=f"{k} moved in warm-up mode")
+        assert not np.array_equal(real.params[k].numpy(), r_before[k]), f"{k} did not move in a normal step"
+        np.testing.assert_array_equal(warm.value(f"d_{k}").numpy(), real.value(f"d_{k}").numpy(), err_msg=f"gradient of {k}")
+        assert np.abs(warm.value(f"opt.m.{k}").numpy()).max() > 0, "moments are still updated, as in the reference"
+    assert int(warm.value("opt.step").numpy()) == 0 and int(real.value("opt.step").numpy()) == 1

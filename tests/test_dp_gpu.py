@@ -85,3 +85,99 @@ def test_two_rank_captured_step(gpu, tmp_path, dtype, mode):
     for _ in range(2):
         oracle.run_lowered(low, env, dtypes, np.float64)
     assert (r0["loss"][0] + r1["loss"][0]) / 2 == pytest.approx(float(env[by["loss"]][0]), rel=1e-3 if dtype == "f32" else 2e-2)
+
+
+# ---- the exchange arithmetic for every world size, on ONE GPU ----------------------------------------------------------
+def _exchange_plan(shape, world_bias_len):
+    from aicf_cuda import Plan, ValueSpec
+    from aicf_cuda.plan import ROLE_PARAM, ROLE_STATIC
+    nb = world_bias_len
+    vals = [ValueSpec(0, "0.W", shape, "f32", ROLE_PARAM),
+            ValueSpec(1, "d_0.W", shape, "f32", ROLE_STATIC, persistent=True, peer_visible=True),
+            ValueSpec(2, "opt.m.0.W", shape, "f32", persistent=True), ValueSpec(3, "opt.v.0.W", shape, "f32", persistent=True),
+            ValueSpec(4, "opt.step", (1,), "i32", persistent=True),
+            ValueSpec(5, "0.W.lp", shape, "bf16", ROLE_STATIC, persistent=True, peer_visible=True),
+            ValueSpec(6, "0.b", (nb,), "f32", ROLE_PARAM, peer_visible=True),
+            ValueSpec(7, "d_0.b", (nb,), "f32", ROLE_STATIC, persistent=True, peer_visible=True),
+            ValueSpec(8, "opt.m.0.b", (nb,), "f32", persistent=True), ValueSpec(9, "opt.v.0.b", (nb,), "f32", persistent=True)]
+    hyper = {"lr": 1e-2, "beta1": 0.9, "beta2": 0.999, "eps": 1e-8, "weight_decay": 0.01}
+    low = [{"op": "dp_adam_step", "inputs": [0, 1, 2, 3, 4], "outputs": [0, 2, 3, 5], "attrs": dict(hyper, slot=0, defer_done=True),
+            "kernel_id": "dp_adam_step_f32_p2p_v0"},
+           {"op": "dp_adam_step", "inputs": [6, 7, 8, 9, 4], "outputs": [6, 8, 9], "attrs": dict(hyper, slot=1, fence_slots=2),
+            "kernel_id": "dp_adam_step_f32_p2p_v0"}]
+    return Plan("exchange_math", vals, low), hyper
+
+
+@pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (3, 1), (4, 0), (4, 3), (8, 0), (8, 5), (8, 7)])
+def test_exchange_arithmetic_of_one_rank_among_n(gpu, world, rank):
+    """One rank of an N-rank exchange run alone: the other ranks' pools are buffers on the same GPU that already
+    hold their gradients and whose flags already say "ready" and "done", so the kernel never waits and its whole data
+    path (sum of N gradient shards in rank order, Adam on the owned shard, broadcast into all N working copies, the
+    unrolled, single-packet and ragged-tail loops of every world size) is checked against the oracle."""
+    from aicf_cuda import Tensor, _C, bf16_bits_to_f32
+    shape, nb = (3001, 2003), 4099  # element counts that are no multiple of 4 x ranks: shards end on odd packets
+    n = shape[0] * shape[1]
+    plan, hyper = _exchange_plan(shape, nb)
+    pool_bytes = plan.peer_pool_bytes
+    peer_vals = ["d_0.W", "0.W.lp", "0.b", "d_0.b"]
+    base = min(plan.tensor(v).ptr for v in peer_vals) - 8192   # the pool starts with the 8 KiB control block
+    off = {v: plan.tensor(v).ptr - base for v in peer_vals}
+    pools = [None if k == rank else Tensor.zeros((pool_bytes // 4,), "f32") for k in range(world)]
+    plan.open_peers_raw(rank, world, [0 if q is None else q.ptr for q in pools])
+    at = lambda k, name, count, dt="f32": Tensor((count,), dt, ptr=(base if k == rank else pools[k].ptr) + off[name])
+
+    rng = np.random.default_rng(100 * world + rank)
+    p = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    pb = (rng.standard_normal(nb) * 0.02).astype(np.float32)
+    gW = [(rng.standard_normal(n) * 1e-3).astype(np.float32) for _ in range(world)]
+    gB = [(rng.standard_normal(nb) * 1e-3).astype(np.float32) for _ in range(world)]
+    plan.tensor("0.W").copy_from_host(p.reshape(shape))
+    plan.tensor("0.b").copy_from_host(pb)
+    for k in range(world):
+        at(k, "d_0.W", n).copy_from_host(gW[k])
+        at(k, "d_0.b", nb).copy_from_host(gB[k])
+    F = np.float32
+    m = v = mb = vb = 0.0
+    for step in (1, 2):
+        plan.tensor("opt.step").copy_from_host(np.array([step], np.int32))
+        # slots 0 and 1, phases ready and done, every rank: "arrived at epoch `step`"
+        Tensor((32,), "i32", ptr=base).copy_from_host(np.full(32, step, np.int32))
+        plan.run()
+        plan.sync()
+        assert _C.wait_status() == 0
+        for name, cnt, par0, grads, mom in (("0.W", n, p, gW, (m, v)), ("0.b", nb, pb, gB, (mb, vb))):
+            lo, hi = shard_bounds(cnt, rank, world)
+            g = grads[0][lo:hi].copy()
+            for k in range(1, world):
+                g = g + grads[k][lo:hi]   # fp32, rank order, like the kernel
+            m0 = mom[0][lo:hi] if isinstance(mom[0], np.ndarray) else 0.0
+            v0 = mom[1][lo:hi] if isinstance(mom[1], np.ndarray) else 0.0
+            wp, wm, wv = oracle.adam_step_fused(par0[lo:hi], g, m0, v0, step, F(hyper["lr"]), F(0.9), F(0.999), F(1e-8),
+                                                weight_decay=F(hyper["weight_decay"]))
+            got = plan.tensor(name).numpy().reshape(-1)
+            assert np.allclose(got[lo:hi], wp, rtol=1e-5, atol=1e-7), f"{name}: owned shard, step {step}"
+            assert np.array_equal(got[:lo], par0[:lo]) and np.array_equal(got[hi:], par0[hi:]), f"{name}: outside the shard"
+            gm = plan.tensor("opt.m." + name).numpy().reshape(-1)
+            assert np.allclose(gm[lo:hi], wm, rtol=1e-5, atol=1e-9) and not gm[:lo].any() and not gm[hi:].any()
+            for k in range(world):   # the broadcast reached every rank's copy, and only inside the shard
+                if name == "0.W":
+                    lp = bf16_bits_to_f32(at(k, "0.W.lp", cnt, "bf16").numpy())
+                    assert np.array_equal(lp[lo:hi], oracle.bf16_round(got[lo:hi])), f"working copy of rank {k}"
+                    assert not lp[:lo].any() and not lp[hi:].any()
+                elif k != rank:
+                    cp = at(k, "0.b", cnt).numpy()
+                    assert np.array_equal(cp[lo:hi], got[lo:hi]) and not cp[:lo].any() and not cp[hi:].any()
+            # carry the state of the owned shard into the next step
+            full_m, full_v = np.zeros(cnt, np.float32), np.zeros(cnt, np.float32)
+            full_m[lo:hi], full_v[lo:hi] = gm[lo:hi], plan.tensor("opt.v." + name).numpy().reshape(-1)[lo:hi]
+            new_p = par0.copy()
+            new_p[lo:hi] = got[lo:hi]
+            if name == "0.W":
+                p, m, v = new_p, full_m, full_v
+            else:
+                pb, mb, vb = new_p, full_m, full_v
+        for k in range(world):       # both phases of both slots were announced to every rank
+            if k != rank:
+                flags = Tensor((32,), "i32", ptr=pools[k].ptr).numpy().reshape(2, 2, 8)
+                assert (flags[:, :, rank] == step).all(), f"flags in rank {k}'s pool after step {step}"
+    plan.close()

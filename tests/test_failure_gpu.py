@@ -26,7 +26,8 @@ def test_dp_exchange_gives_up_when_a_rank_never_arrives(gpu):
     plan.tensor("opt.step").copy_from_host(np.array([1], np.int32))
     assert _C.wait_status(clear=True) == 0
     plan.run()
-    plan.sync()  # returns after the two bounded waits (~2 s each), not never
+    with pytest.raises(RuntimeError, match="exchange expired"):
+        plan.sync()  # returns after the two bounded waits (~2 s each), not never, and reports what happened
     status = _C.wait_status(clear=True)
     assert (status >> 17) & 3 == 1, f"status word {status:#x}: the ready-phase timeout must be reported"
     assert np.array_equal(plan.tensor("0.b").numpy(), p0), "work that depended on the missing rank must be skipped"

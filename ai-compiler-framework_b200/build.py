@@ -1,4 +1,5 @@
-"""Builds libaicf_b200.so (hand-written sm_100a kernels + registry + C ABI) in-tree with nvcc.
+"""Builds libaicf_b200.so (hand-written sm_100a kernels + registry + C ABI) in-tree with nvcc, and the Python
+extension module aicf_cuda/_C (pybind11 over that C ABI, no torch) with g++.
 
     python build.py            # incremental build into ./lib/
     python build.py --force    # rebuild everything
@@ -35,8 +36,42 @@ def nvcc() -> str:
     return exe
 
 
+BINDINGS = CSRC / "python_bindings" / "bindings.cpp"  # the extension module, not part of the library
+
+
 def sources() -> list[Path]:
-    return sorted(list(CSRC.rglob("*.cu")) + list(CSRC.rglob("*.cpp")))
+    return sorted(s for s in list(CSRC.rglob("*.cu")) + list(CSRC.rglob("*.cpp")) if s != BINDINGS)
+
+
+def extension_path() -> Path:
+    import sysconfig
+    return ROOT / "python" / "aicf_cuda" / ("_C" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_extension(force: bool = False, verbose: bool = True) -> Path:
+    """aicf_cuda/_C.<abi tag>.so: pybind11 module linked against lib/libaicf_b200.so through a run path relative to
+    the module's own location, so the package can be moved as a whole."""
+    import sysconfig
+
+    import pybind11
+    out = extension_path()
+    newest = max(BINDINGS.stat().st_mtime, (REPO / "include" / "aicf_b200.h").stat().st_mtime)
+    if not force and out.exists() and out.stat().st_mtime > newest:
+        if verbose:
+            print(f"[build] {out} is up to date")
+        return out
+    gxx = shutil.which("g++")
+    if gxx is None:
+        raise RuntimeError("g++ not found: it is needed for the aicf_cuda._C extension module")
+    cmd = [gxx, "-std=c++17", "-O2", "-shared", "-fPIC", "-fvisibility=hidden", f"-I{pybind11.get_include()}",
+           f"-I{sysconfig.get_paths()['include']}", f"-I{REPO / 'include'}", str(BINDINGS), "-o", str(out),
+           f"-L{LIB_DIR}", "-laicf_b200", "-Wl,-rpath,$ORIGIN/../../lib"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"g++ failed for {BINDINGS}:\n{r.stdout}\n{r.stderr}")
+    if verbose:
+        print(f"[build] built {out} ({out.stat().st_size >> 10} KiB)")
+    return out
 
 
 def headers_mtime() -> float:
@@ -76,6 +111,7 @@ def build(force: bool = False, verbose: bool = True) -> Path:
             print(f"[build] linked {LIB} ({LIB.stat().st_size >> 10} KiB) from {len(objs)} objects")
     elif verbose:
         print(f"[build] {LIB} is up to date")
+    build_extension(force=force, verbose=verbose)
     return LIB
 
 

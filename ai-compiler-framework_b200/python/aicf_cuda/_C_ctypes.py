@@ -1,4 +1,10 @@
-"""`aicf_cuda._C`: the binding surface of the reference's pybind/torch extension, re-done over the C ABI.
+"""The binding surface of the reference's pybind/torch extension over the C ABI, in pure Python (ctypes).
+
+`aicf_cuda._C` is normally the compiled extension module (csrc/python_bindings/bindings.cpp, built by build.py), which
+offers exactly these names. This module is the alternative for an interpreter the extension was not built for:
+AICF_BINDING=ctypes in the environment makes `aicf_cuda._C` resolve to it. Both go through the same C entry points
+(aicf_b200_op_call_traced / aicf_b200_launch_by_id_traced), so traces, error texts and results are identical; the
+compiled module only spends less host time per eager launch.
 
 Same names, argument order, defaults, trace strings and error texts as the reference module
 (src/python_bindings/bindings.cpp:372-548): OpKind, op_call, launch_by_id, trace_enable/reset/get,
@@ -49,6 +55,7 @@ class OpKind(enum.IntEnum):
 
 # pybind's export_values(): enumerators are also module attributes
 globals().update(OpKind.__members__)
+binding = "ctypes"
 
 _DTYPE_BY_NAME = {
     "f32": 1, "float32": 1, "torch.float32": 1, "torch.float": 1,

@@ -738,7 +738,7 @@ def opkind_from_name(op: str) -> int:
     k = str(op).strip().lower()
     if k not in _OP_KIND_NAMES:
         raise RuntimeError(f"[exec] unsupported lowered op '{op}' (no OpKind mapping)")
-    return int(_C.OpKind[_OP_KIND_NAMES[k]])
+    return int(getattr(_C.OpKind, _OP_KIND_NAMES[k]))
 
 
 def _canon_name(s: str) -> str:

@@ -53,7 +53,46 @@ def test_opkind_enum_values_are_abi():
     assert [int(OpKind.EltwiseAdd), int(OpKind.Gemm), int(OpKind.AdamStep), int(OpKind.GemmEpilogue)] == [0, 2, 10, 17]
     import aicf_cuda._C as m
     assert m.Gemm == OpKind.Gemm  # export_values()
-    assert OpKind(17) is OpKind.GemmEpilogue
+    assert OpKind(17) == OpKind.GemmEpilogue and int(OpKind(17)) == 17
+
+
+def test_compiled_and_ctypes_binding_modules_offer_the_same_surface():
+    """aicf_cuda._C is the compiled extension by default; _C_ctypes is its pure-Python twin over the same C ABI."""
+    import aicf_cuda
+    import aicf_cuda._C as native
+    import aicf_cuda._C_ctypes as twin
+    import os
+    expected = "ctypes" if os.environ.get("AICF_BINDING", "").lower() == "ctypes" else "pybind11"
+    assert native.binding == expected and twin.binding == "ctypes" and aicf_cuda._C is native
+    names = ["OpKind", "op_call", "launch_by_id", "trace_enable", "trace_reset", "trace_get", "graph_begin", "graph_end",
+             "graph_launch", "graph_reset", "graph_stream", "kernel_ids", "gemm_status", "wait_status", "device_sync"]
+    for n in names:
+        assert hasattr(native, n) and hasattr(twin, n), n
+    assert {k: int(v) for k, v in native.OpKind.__members__.items()} == {k: int(v) for k, v in twin.OpKind.__members__.items()}
+    assert native.kernel_ids(native.OpKind.Copy) == twin.kernel_ids(twin.OpKind.Copy)
+    # the reference's error texts, from either module, without a device
+    import pytest
+    for mod in (native, twin):
+        with pytest.raises(RuntimeError, match="graph_end called but not capturing"):
+            mod.graph_end()
+        with pytest.raises(RuntimeError, match="graph_launch called but no captured graph exists"):
+            mod.graph_launch()
+        with pytest.raises(RuntimeError, match=r"aicf_cuda call failed: kind=2 \(gemm\) status=NotImplemented \(2\) kernel_id=nope_v0"):
+            mod.launch_by_id("nope_v0", mod.OpKind.Gemm, [], [])
+
+        class Fake:
+            dtype, shape = "f64", (2, 2)
+            def data_ptr(self): return 4096
+            def stride(self): return (2, 1)
+            def is_contiguous(self): return True
+        with pytest.raises(RuntimeError, match="dtype must be float16/bfloat16/float32/int32"):
+            mod.op_call(mod.OpKind.EltwiseRelu, [Fake()], [Fake()])
+        Fake.dtype, Fake.shape = "f32", (1, 1, 1, 1, 1)
+        with pytest.raises(RuntimeError, match="rank out of range"):
+            mod.op_call(mod.OpKind.EltwiseRelu, [Fake()], [Fake()])
+        mod.trace_reset()
+        mod.trace_enable(True)
+        assert mod.trace_get() == []
 
 
 def test_null_pointer_calls_fail_cleanly_without_a_device():

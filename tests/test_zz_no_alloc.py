@@ -33,7 +33,7 @@ def test_matches_the_workspace_entry_point_on_two_calls_in_a_row(gpu):
         X = Tensor.from_numpy(x)
         want_t, got_t = Tensor.zeros((cols,)), Tensor.from_numpy(np.full(cols, np.nan, np.float32))
         need = aicf_cuda.lib.aicf_b200_query_workspace(b"reduce_sum_keep_lastdim_f32_v0", int(OpKind.ReduceSum),
-                                                       aicf_cuda._C._build_descs([X], "x")[0], 1, None)
+                                                       aicf_cuda._C_ctypes._build_descs([X], "x")[0], 1, None)
         assert 0 < need <= 512 * 1024, "the case must exercise scratch memory and fit the built-in array"
         by_id("reduce_sum_keep_lastdim_f32_v0", OpKind.ReduceSum, [X], [want_t], RSUM, struct.pack("<q", 0))
         assert noalloc(X, got_t, rows, cols) == 0, aicf_cuda.lib.aicf_b200_last_error().decode()

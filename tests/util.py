@@ -8,7 +8,8 @@ import numpy as np
 
 import aicf_cuda
 from aicf_cuda import _C, Tensor
-from aicf_cuda._C import OpKind, _blob, _build_descs
+from aicf_cuda._C import OpKind
+from aicf_cuda._C_ctypes import _blob, _build_descs
 
 
 def dev(arr, dtype=None) -> Tensor:

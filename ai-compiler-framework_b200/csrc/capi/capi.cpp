@@ -16,6 +16,8 @@ int layernorm_pipeline_status(bool clear);
 int adam_pipeline_status(bool clear);
 int gemm_tcgen05_timeline(int enable, unsigned long long* out16);
 int dp_wait_status(bool clear);
+Status stream_probe(int reads, int writes, const void* const* in, void* const* out, size_t bytes, int in_flight,
+                    int blocks_per_sm, cudaStream_t stream);
 }
 
 static_assert(sizeof(aicf_tensor_desc) == sizeof(aicf::cuda::TensorDesc), "C and C++ tensor descriptors must match");
@@ -345,6 +347,13 @@ int aicf_b200_device_info(int device, int64_t* l2_bytes, int* sm_count, int64_t*
     if (int rc = check_cuda(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties")) return rc;
     *total_bytes = static_cast<int64_t>(prop.totalGlobalMem);
   }
+  return AICF_OK;
+}
+int aicf_b200_stream_probe(int reads, int writes, const void* const* inputs, void* const* outputs, size_t bytes_each,
+                           int packets_in_flight, int blocks_per_sm, aicf_stream stream) {
+  const Status st = aicf::cuda::stream_probe(reads, writes, inputs, outputs, bytes_each, packets_in_flight, blocks_per_sm,
+                                             reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(stream)));
+  if (!aicf::cuda::ok(st)) return fail(st, std::string("stream_probe: ") + aicf::cuda::status_to_string(st));
   return AICF_OK;
 }
 int aicf_b200_malloc(void** ptr, size_t bytes) {

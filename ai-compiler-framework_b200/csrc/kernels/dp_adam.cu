@@ -227,10 +227,8 @@ __global__ void __launch_bounds__(256) dp_adam_kernel(const DpAdamArgs a) {
   __syncthreads();
 
   if (s_go) {
-    int t = a.step[0];
-    if (t < 1) t = 1;
-    const float d1 = static_cast<float>(1.0 - pow(static_cast<double>(a.h.beta1), static_cast<double>(t)));
-    const float d2 = static_cast<float>(1.0 - pow(static_cast<double>(a.h.beta2), static_cast<double>(t)));
+    float d1, d2;
+    adam_inverse_corrections(a.h, a.step[0], d1, d2);
     constexpr int kW = kWorld ? kWorld : kMaxRanks;
     const int world = kWorld ? kWorld : a.world;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;

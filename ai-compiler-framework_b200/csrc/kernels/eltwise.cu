@@ -365,3 +365,97 @@ AICF_ELTWISE_FACTORY(make_bias_add_bf16_variant, "bias_add_bf16_sm100", bias_add
 AICF_ELTWISE_FACTORY(make_cast_variant, "cast_sm100", cast_launch, cast_supported)
 
 }  // namespace aicf::cuda
+
+// ------------------------------------------------------------------------------------------------
+// Stream-mix probe (aicf_b200_stream_probe): the ceiling a streaming kernel with R input and W output arrays can
+// reach on this device. It does the least work such a kernel can do - 16-byte evict-first loads of R arrays, one add
+// per loaded word, 16-byte evict-first stores of W arrays - with the two launch choices that matter left to the
+// caller: packets per array in flight per thread (1, 2 or 4) and 256-thread blocks per SM. The best GB/s over those
+// choices is the denominator for kernels with the same stream mix (Adam: 4 reads + 3 writes; an elementwise binary
+// op: 2 + 1; a copy: 1 + 1), where a plain copy's rate is not. A measuring aid, not an op.
+// ------------------------------------------------------------------------------------------------
+namespace aicf::cuda {
+namespace {
+constexpr int kProbeMaxStreams = 8;
+struct ProbeArgs {
+  const float4* in[kProbeMaxStreams];
+  float4* out[kProbeMaxStreams];
+  int64_t packets;
+};
+template <int R, int W, int U>
+__global__ void __launch_bounds__(256) stream_probe_kernel(const ProbeArgs a) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; i + (U - 1) * stride < a.packets; i += U * stride) {
+    float4 v[U][R];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int r = 0; r < R; ++r) v[u][r] = __ldcs(a.in[r] + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float4 s = v[u][0];
+#pragma unroll
+      for (int r = 1; r < R; ++r) {
+        s.x += v[u][r].x; s.y += v[u][r].y; s.z += v[u][r].z; s.w += v[u][r].w;
+      }
+#pragma unroll
+      for (int w = 0; w < W; ++w) __stcs(a.out[w] + i + u * stride, make_float4(s.x + w, s.y, s.z, s.w));
+    }
+  }
+  for (; i < a.packets; i += stride) {
+    float4 s = __ldcs(a.in[0] + i);
+#pragma unroll
+    for (int r = 1; r < R; ++r) {
+      const float4 t = __ldcs(a.in[r] + i);
+      s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+    }
+#pragma unroll
+    for (int w = 0; w < W; ++w) __stcs(a.out[w] + i, make_float4(s.x + w, s.y, s.z, s.w));
+  }
+}
+template <int R, int W>
+Status probe_launch(const ProbeArgs& a, int in_flight, int blocks_per_sm, cudaStream_t stream) {
+  cudaGetLastError();
+  const int grid = streaming_grid(a.packets / in_flight + 1, 256, blocks_per_sm);
+  if (in_flight == 1) stream_probe_kernel<R, W, 1><<<grid, 256, 0, stream>>>(a);
+  else if (in_flight == 2) stream_probe_kernel<R, W, 2><<<grid, 256, 0, stream>>>(a);
+  else stream_probe_kernel<R, W, 4><<<grid, 256, 0, stream>>>(a);
+  return launch_status();
+}
+}  // namespace
+
+// reads in 1..4, writes in 1..3; arrays of `bytes` bytes each (multiple of 16), 16-byte aligned, all distinct;
+// in_flight in {1, 2, 4} (0 = 2), blocks_per_sm in 1..32 (0 = 8).
+Status stream_probe(int reads, int writes, const void* const* in, void* const* out, size_t bytes, int in_flight,
+                    int blocks_per_sm, cudaStream_t stream) {
+  if (reads < 1 || reads > 4 || writes < 1 || writes > 3 || !in || !out || bytes == 0 || bytes % 16 != 0) return Status::InvalidArgument;
+  if (in_flight == 0) in_flight = 2;
+  if (blocks_per_sm == 0) blocks_per_sm = 8;
+  if ((in_flight != 1 && in_flight != 2 && in_flight != 4) || blocks_per_sm < 1 || blocks_per_sm > 32) return Status::InvalidArgument;
+  ProbeArgs a{};
+  for (int r = 0; r < reads; ++r) {
+    if (!in[r] || !aligned_to(in[r], 16)) return Status::InvalidArgument;
+    a.in[r] = static_cast<const float4*>(in[r]);
+  }
+  for (int w = 0; w < writes; ++w) {
+    if (!out[w] || !aligned_to(out[w], 16)) return Status::InvalidArgument;
+    a.out[w] = static_cast<float4*>(out[w]);
+  }
+  a.packets = static_cast<int64_t>(bytes / 16);
+  switch (reads * 4 + writes) {
+    case 1 * 4 + 1: return probe_launch<1, 1>(a, in_flight, blocks_per_sm, stream);
+    case 1 * 4 + 2: return probe_launch<1, 2>(a, in_flight, blocks_per_sm, stream);
+    case 1 * 4 + 3: return probe_launch<1, 3>(a, in_flight, blocks_per_sm, stream);
+    case 2 * 4 + 1: return probe_launch<2, 1>(a, in_flight, blocks_per_sm, stream);
+    case 2 * 4 + 2: return probe_launch<2, 2>(a, in_flight, blocks_per_sm, stream);
+    case 2 * 4 + 3: return probe_launch<2, 3>(a, in_flight, blocks_per_sm, stream);
+    case 3 * 4 + 1: return probe_launch<3, 1>(a, in_flight, blocks_per_sm, stream);
+    case 3 * 4 + 2: return probe_launch<3, 2>(a, in_flight, blocks_per_sm, stream);
+    case 3 * 4 + 3: return probe_launch<3, 3>(a, in_flight, blocks_per_sm, stream);
+    case 4 * 4 + 1: return probe_launch<4, 1>(a, in_flight, blocks_per_sm, stream);
+    case 4 * 4 + 2: return probe_launch<4, 2>(a, in_flight, blocks_per_sm, stream);
+    default: return probe_launch<4, 3>(a, in_flight, blocks_per_sm, stream);
+  }
+}
+}  // namespace aicf::cuda

@@ -47,6 +47,8 @@ constexpr int kAccBufs = 2;
 constexpr int kTmemCols = 512;
 constexpr int kThreads = 192;
 constexpr int kGroupM = 16;   // tile rasterisation: 16 row-tiles share their column tiles in L2
+constexpr int kDefaultCStream = 0;  // C stores: 0 = default write-back, 1 = streaming (evict-first)
+constexpr int kDefaultAbHint = 0;   // operand loads of the paired kernel: no L2 eviction hint
 constexpr unsigned long long kWaitBudgetNs = 1000000000ull;
 
 
@@ -80,6 +82,14 @@ struct GemmParams {
   // and applies the epilogue. splits <= 1: the kernel stores C itself.
   int splits;
   float* partial;
+  // tuning (launcher defaults, AICF_GEMM_* overrides): rasterisation group in 128-row tiles, streaming (evict-first)
+  // stores of C, and L2 eviction hints on the operand loads (bit 0 / 1: A / B evict_last, bit 2 / 3: A / B evict_first)
+  int group_m;
+  int c_stream;
+  int ab_hint;
+  // paired kernel: last, partly filled round of tiles done as 256x128 half tiles (see PairItem)
+  int tail_halves;
+  uint32_t idesc_half;  // instruction descriptor with N = 128
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -177,11 +187,11 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, int mn_ma
   return static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu) | (lbo << 16) | (sbo << 32) | (1ull << 46) | (2ull << 61);
 }
 
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int* tm, int* tn) {
-  const int per_group = kGroupM * tiles_n;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int* tm, int* tn, int group_m = kGroupM) {
+  const int per_group = group_m * tiles_n;
   const int group = tile / per_group;
-  const int first_m = group * kGroupM;
-  const int rows = min(kGroupM, tiles_m - first_m);
+  const int first_m = group * group_m;
+  const int rows = min(group_m, tiles_m - first_m);
   const int in_group = tile - group * per_group;
   *tm = first_m + in_group % rows;
   *tn = in_group / rows;
@@ -281,9 +291,15 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int row, int
   if (p.c_dtype == static_cast<int>(DType::kF32)) {
     float* dst = static_cast<float*>(p.C) + off;
     if (full_chunk) {
+      if (p.c_stream) {
 #pragma unroll
-      for (int q = 0; q < 8; ++q)
-        reinterpret_cast<float4*>(dst)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        for (int q = 0; q < 8; ++q)
+          __stcs(reinterpret_cast<float4*>(dst) + q, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+      } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          reinterpret_cast<float4*>(dst)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      }
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
@@ -307,9 +323,15 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int row, int
   }
   uint16_t* dst = static_cast<uint16_t*>(p.C) + off;
   if (full_chunk) {
+    if (p.c_stream) {
 #pragma unroll
-    for (int q = 0; q < 4; ++q)
-      reinterpret_cast<uint4*>(dst)[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      for (int q = 0; q < 4; ++q)
+        __stcs(reinterpret_cast<uint4*>(dst) + q, make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]));
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        reinterpret_cast<uint4*>(dst)[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+    }
   } else {
 #pragma unroll
     for (int j = 0; j < 32; ++j)
@@ -384,7 +406,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool first = true;
       for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
         int tm, tn;
-        tile_coords(tile / splits, tiles_m, tiles_n, &tm, &tn);
+        tile_coords(tile / splits, tiles_m, tiles_n, &tm, &tn, p.group_m);
         const int m0 = tm * kTileM, n0 = tn * TN;
         const int kb_lo = (tile % splits) * kb_per_split, kb_hi = min(kb_lo + kb_per_split, k_blocks_all);
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
@@ -480,7 +502,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
       int tm, tn;
-      tile_coords(tile / splits, tiles_m, tiles_n, &tm, &tn);
+      tile_coords(tile / splits, tiles_m, tiles_n, &tm, &tn, p.group_m);
       const int row = tm * kTileM + sub * 32 + lane;
       const int n0 = tn * TN;
       if (splits > 1) q.C = p.partial + static_cast<int64_t>(tile % splits) * p.M * p.N;
@@ -594,6 +616,25 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar_cluster)
       : "memory");
 }
+// Same load with an L2 eviction policy (from createpolicy) attached.
+__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster,
+                                                      uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar_cluster), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
@@ -617,8 +658,8 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
                : "memory");
 }
 
-__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m2, int tiles_n, int* tm, int* tn) {
-  constexpr int kGroup = kGroupM / 2;  // 8 pair-rows = 16 row tiles of 128
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m2, int tiles_n, int* tm, int* tn, int group_m) {
+  const int kGroup = max(group_m / 2, 1);  // default 8 pair-rows = 16 row tiles of 128
   const int per_group = kGroup * tiles_n;
   const int group = tile / per_group;
   const int first_m = group * kGroup;
@@ -628,9 +669,34 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m2, int til
   *tn = in_group / rows;
 }
 
+// Work items of the paired kernel. Clusters take items round-robin, so `num_tiles` tiles on `num_clusters` clusters
+// run in ceil(num_tiles / num_clusters) rounds and the last round may be mostly empty (4096^3: 256 tiles on 74
+// clusters = 3 full rounds + 34 tiles). When the left-over tiles number at most half the clusters, each of them is
+// split into its two 256x128 column halves: twice as many items, each about half as long, still one round - the
+// tail costs half a round instead of a whole one. Items [0, full) are whole tiles, the rest are halves.
+struct PairItem {
+  int tile;    // 256x256 tile index (rasterised by pair_tile_coords)
+  int half;    // 0 / 1: column half, when `width` is 128
+  int width;   // 256 or 128 columns
+};
+struct PairSchedule {
+  int full, items;
+  __device__ __forceinline__ PairSchedule(int num_tiles, int num_clusters, int tail_halves) {
+    const int rem = num_tiles % num_clusters;
+    const bool halve = tail_halves != 0 && rem > 0 && 2 * rem <= num_clusters;
+    full = halve ? num_tiles - rem : num_tiles;
+    items = full + (halve ? 2 * rem : 0);
+  }
+  __device__ __forceinline__ PairItem at(int w) const {
+    if (w < full) return PairItem{w, 0, kTileN};
+    const int h = w - full;
+    return PairItem{full + (h >> 1), h & 1, kTileN / 2};
+  }
+};
+
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                             const GemmParams p) {
+                             const __grid_constant__ CUtensorMap tmap_b_half, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -651,6 +717,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int tiles_m2 = (p.M + 2 * kTileM - 1) / (2 * kTileM), tiles_n = (p.N + kTileN - 1) / kTileN;
   const int num_tiles = tiles_m2 * tiles_n;
   const int k_blocks = (p.K + kTileK - 1) / kTileK;
+  const PairSchedule sched(num_tiles, num_clusters, p.tail_halves);
 
   const bool tl = g_gemm_timeline_on != 0 && blockIdx.x == 0;
   if (tl && threadIdx.x == 0) g_gemm_timeline[0] = global_ns();
@@ -682,11 +749,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool alive = true;
       unsigned long long waited = 0;
       bool first = true;
-      for (int tile = cluster; tile < num_tiles && alive; tile += num_clusters) {
+      const bool hint_a = (p.ab_hint & 5) != 0, hint_b = (p.ab_hint & 10) != 0;
+      const uint64_t pol_a = (p.ab_hint & 1) ? l2_policy_evict_last() : l2_policy_evict_first();
+      const uint64_t pol_b = (p.ab_hint & 2) ? l2_policy_evict_last() : l2_policy_evict_first();
+      for (int w = cluster; w < sched.items && alive; w += num_clusters) {
+        const PairItem it = sched.at(w);
         int tm, tn;
-        pair_tile_coords(tile, tiles_m2, tiles_n, &tm, &tn);
+        pair_tile_coords(it.tile, tiles_m2, tiles_n, &tm, &tn, p.group_m);
         const int m0 = tm * 2 * kTileM + static_cast<int>(rank) * kTileM;
-        const int nb0 = tn * kTileN + static_cast<int>(rank) * k2HalfN;
+        const bool is_half = it.width != kTileN;
+        const int b_cols = it.width / 2;  // B columns this CTA holds: 128, or 64 for a half tile
+        const int nb0 = tn * kTileN + it.half * (kTileN / 2) + static_cast<int>(rank) * b_cols;
+        const uint32_t stage_tx = static_cast<uint32_t>(k2AStageBytes + b_cols * kTileK * 2);
         for (int kb = 0; kb < k_blocks; ++kb) {
           const unsigned long long w0 = tl ? global_ns() : 0;
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1)) { alive = false; break; }
@@ -697,18 +771,29 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint32_t full_leader = map_to_cta(bar_full + 8 * stage, 0);
           const uint32_t sa = base + stage * k2StageBytes, sb = sa + k2AStageBytes;
           const int k0 = kb * kTileK;
-          if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * k2StageBytes);
+          if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * stage_tx);
+          auto load_a = [&](uint32_t dst, int c0, int c1) {
+            if (hint_a) tma_load_2d_pair_hint(dst, &tmap_a, c0, c1, full_leader, pol_a);
+            else tma_load_2d_pair(dst, &tmap_a, c0, c1, full_leader);
+          };
+          // K-major B comes in one box of b_cols rows (the half tile has a tensor map of its own, box 64 x 64);
+          // N-major B comes in 64 x 64 boxes from the same map, one or two of them
+          const CUtensorMap* mb = (is_half && !p.b_mn_major) ? &tmap_b_half : &tmap_b;
+          auto load_b = [&](uint32_t dst, int c0, int c1) {
+            if (hint_b) tma_load_2d_pair_hint(dst, mb, c0, c1, full_leader, pol_b);
+            else tma_load_2d_pair(dst, mb, c0, c1, full_leader);
+          };
           if (p.a_mn_major) {
-            tma_load_2d_pair(sa, &tmap_a, m0, k0, full_leader);
-            tma_load_2d_pair(sa + kChunkBytes, &tmap_a, m0 + 64, k0, full_leader);
+            load_a(sa, m0, k0);
+            load_a(sa + kChunkBytes, m0 + 64, k0);
           } else {
-            tma_load_2d_pair(sa, &tmap_a, k0, m0, full_leader);
+            load_a(sa, k0, m0);
           }
           if (p.b_mn_major) {
-            tma_load_2d_pair(sb, &tmap_b, nb0, k0, full_leader);
-            tma_load_2d_pair(sb + kChunkBytes, &tmap_b, nb0 + 64, k0, full_leader);
+            load_b(sb, nb0, k0);
+            if (!is_half) load_b(sb + kChunkBytes, nb0 + 64, k0);
           } else {
-            tma_load_2d_pair(sb, &tmap_b, k0, nb0, full_leader);
+            load_b(sb, k0, nb0);
           }
           if (++stage == k2Stages) { stage = 0; phase ^= 1u; }
         }
@@ -728,7 +813,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t b_step = p.b_mn_major ? (2 * 1024) >> 4 : (kUmmaK * 2) >> 4;
       unsigned long long wait_data = 0, wait_acc = 0;
       bool first = true, first_tile = true;
-      for (int tile = cluster; tile < num_tiles && alive; tile += num_clusters) {
+      for (int w = cluster; w < sched.items && alive; w += num_clusters) {
+        const uint32_t idesc = sched.at(w).width == kTileN ? p.idesc : p.idesc_half;
         unsigned long long w0 = tl ? global_ns() : 0;
         if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, 2)) { alive = false; break; }
         if (tl) wait_acc += global_ns() - w0;
@@ -747,7 +833,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint64_t bdesc = make_smem_desc(sb, p.b_mn_major);
 #pragma unroll
           for (int k = 0; k < kTileK / kUmmaK; ++k)
-            umma_f16_pair(tmem_d, adesc + k * a_step, bdesc + k * b_step, p.idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_pair(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc, (kb | k) != 0 ? 1u : 0u);
           umma_commit_pair(bar_empty + 8 * stage);  // frees the stage in both CTAs
           if (++stage == k2Stages) { stage = 0; phase ^= 1u; }
         }
@@ -767,11 +853,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool alive = true;
     const bool tle = tl && warp == 2 && lane == 0;
     unsigned long long e_wait = 0, e_busy = 0, e_tiles = 0;
-    for (int tile = cluster; tile < num_tiles && alive; tile += num_clusters) {
+    for (int w = cluster; w < sched.items && alive; w += num_clusters) {
+      const PairItem it = sched.at(w);
       int tm, tn;
-      pair_tile_coords(tile, tiles_m2, tiles_n, &tm, &tn);
+      pair_tile_coords(it.tile, tiles_m2, tiles_n, &tm, &tn, p.group_m);
       const int row = tm * 2 * kTileM + static_cast<int>(rank) * kTileM + sub * 32 + lane;
-      const int n0 = tn * kTileN;
+      const int n0 = tn * kTileN + it.half * (kTileN / 2);
+      const int chunks = it.width / 32;
       const unsigned long long e0 = tle ? global_ns() : 0;
       if (!__all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, 4))) { alive = false; break; }
       tc_fence_after();
@@ -782,14 +870,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * kTileN;
       float* bs = bias_smem + (warp - 2) * kTileN;
-#pragma unroll
-      for (int h = 0; h < kTileN / 32; ++h) {
+#pragma unroll 1
+      for (int h = 0; h < chunks; ++h) {
         const int col = n0 + lane + 32 * h;
         bs[lane + 32 * h] = (p.bias_dtype != 0 && col < p.N) ? bias_at(p, col) : 0.0f;
       }
       __syncwarp();
 #pragma unroll 1
-      for (int c = 0; c < kTileN / 32; c += 2) {
+      for (int c = 0; c < chunks; c += 2) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;
         uint32_t r[64];
@@ -1142,6 +1230,10 @@ struct GemmEnvOverrides {
   int tile_n = 0;
   bool splitk_set = false;
   int splitk = 0;
+  int group_m = 0;    // AICF_GEMM_GROUP_M: rasterisation group in 128-row tiles (0 = default)
+  int c_stream = -1;  // AICF_GEMM_C_STREAM: 0 / 1 (-1 = default)
+  int ab_hint = -1;   // AICF_GEMM_AB_HINT: bit mask, see GemmParams (-1 = default)
+  int tail_halves = -1;  // AICF_GEMM_TAIL_HALVES: 0 / 1 (-1 = default, on)
 };
 const GemmEnvOverrides& gemm_env_overrides() {
   static const GemmEnvOverrides env = [] {
@@ -1149,6 +1241,10 @@ const GemmEnvOverrides& gemm_env_overrides() {
     if (const char* s = std::getenv("AICF_GEMM_CTA_GROUP")) e.cta_group = s[0] == '1' ? 1 : s[0] == '2' ? 2 : 0;
     if (const char* s = std::getenv("AICF_GEMM_TILE_N")) e.tile_n = std::atoi(s);
     if (const char* s = std::getenv("AICF_GEMM_SPLITK")) e.splitk_set = true, e.splitk = std::atoi(s);
+    if (const char* s = std::getenv("AICF_GEMM_GROUP_M")) e.group_m = std::atoi(s);
+    if (const char* s = std::getenv("AICF_GEMM_C_STREAM")) e.c_stream = std::atoi(s);
+    if (const char* s = std::getenv("AICF_GEMM_AB_HINT")) e.ab_hint = std::atoi(s);
+    if (const char* s = std::getenv("AICF_GEMM_TAIL_HALVES")) e.tail_halves = std::atoi(s);
     return e;
   }();
   return env;
@@ -1319,6 +1415,10 @@ Status gemm_tcgen05_run(const GemmProblem& p, void* ws, size_t ws_bytes, cudaStr
   ok_maps = ok_maps && (b_major == 0 ? encode_operand(&tb, p.B.data, p.B.dtype, p.K, p.N, p.B.cs, kTileK, b_rows)
                                      : encode_operand(&tb, p.B.data, p.B.dtype, p.N, p.K, p.B.rs, 64, kTileK));
   if (!ok_maps) return Status::Internal;
+  // the paired kernel's half tiles take K-major B in boxes of 64 rows
+  CUtensorMap tb_half = tb;
+  if (pair && b_major == 0 && !encode_operand(&tb_half, p.B.data, p.B.dtype, p.K, p.N, p.B.cs, kTileK, k2HalfN / 2))
+    return Status::Internal;
 
   GemmParams g{};
   g.C = const_cast<void*>(p.C.data);
@@ -1342,10 +1442,18 @@ Status gemm_tcgen05_run(const GemmProblem& p, void* ws, size_t ws_bytes, cudaStr
   g.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(a_major) << 15) |
             (static_cast<uint32_t>(b_major) << 16) | (static_cast<uint32_t>((pair ? kTileN : tn) >> 3) << 17) |
             (static_cast<uint32_t>((pair ? 2 * kTileM : kTileM) >> 4) << 24);
+  g.idesc_half = (g.idesc & ~(0x3Fu << 17)) | (static_cast<uint32_t>((kTileN / 2) >> 3) << 17);
   const int c_elem = dtype_size_bytes(p.C.dtype);
   g.c_vec_ok = aligned_to(p.C.data, 16) && ((p.C.rs * c_elem) % 16 == 0);
   g.splits = choice.splits;
   g.partial = choice.splits > 1 ? static_cast<float*>(ws) : nullptr;
+  {
+    const GemmEnvOverrides& env = gemm_env_overrides();
+    g.group_m = env.group_m >= 2 ? env.group_m : kGroupM;
+    g.c_stream = env.c_stream >= 0 ? (env.c_stream ? 1 : 0) : kDefaultCStream;
+    g.ab_hint = env.ab_hint >= 0 ? (env.ab_hint & 15) : kDefaultAbHint;
+    g.tail_halves = env.tail_halves >= 0 ? (env.tail_halves ? 1 : 0) : 1;
+  }
 
   const int dev = device_slot();  // -1: a device beyond the per-device tables, set up again on every call
   cudaGetLastError();
@@ -1381,7 +1489,7 @@ Status gemm_tcgen05_run(const GemmProblem& p, void* ws, size_t ws_bytes, cudaStr
     const int64_t pair_tiles = ((p.M + 2 * kTileM - 1) / (2 * kTileM)) * ((p.N + kTileN - 1) / kTileN);
     const int clusters = static_cast<int>(pair_tiles < device_clusters ? pair_tiles : device_clusters);
     cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters));
-    if (cudaLaunchKernelEx(&cfg, gemm_tcgen05_2cta_kernel, ta, tb, g) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, gemm_tcgen05_2cta_kernel, ta, tb, tb_half, g) != cudaSuccess) {
       cudaGetLastError();
       return Status::Internal;
     }

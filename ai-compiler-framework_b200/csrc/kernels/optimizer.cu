@@ -66,12 +66,7 @@ __global__ void __launch_bounds__(256) adam_kernel(AdamArgs a) {
     d1 = a.bc1[0];
     d2 = a.bc2[0];
   } else {
-    // 1 - beta^t cancels badly in fp32 for beta close to 1; two double pow() per thread are free
-    // next to the memory traffic and give correctly rounded divisors.
-    int t = a.step[0];
-    if (t < 1) t = 1;
-    d1 = static_cast<float>(1.0 - pow(static_cast<double>(a.h.beta1), static_cast<double>(t)));
-    d2 = static_cast<float>(1.0 - pow(static_cast<double>(a.h.beta2), static_cast<double>(t)));
+    adam_inverse_corrections(a.h, a.step[0], d1, d2);  // multipliers in the fused contract (see adam_one)
   }
   using V4 = Pack16<float>;
   const V4* P = reinterpret_cast<const V4*>(a.p);
@@ -156,10 +151,7 @@ __global__ void __launch_bounds__(kBulkThreads) adam_bulk_kernel(AdamArgs a, int
     d1 = a.bc1[0];
     d2 = a.bc2[0];
   } else {
-    int t = a.step[0];
-    if (t < 1) t = 1;
-    d1 = static_cast<float>(1.0 - pow(static_cast<double>(a.h.beta1), static_cast<double>(t)));
-    d2 = static_cast<float>(1.0 - pow(static_cast<double>(a.h.beta2), static_cast<double>(t)));
+    adam_inverse_corrections(a.h, a.step[0], d1, d2);
   }
   using V4 = Pack16<float>;
   const uint32_t buf0 = sm100::smem_addr(ring);
@@ -352,6 +344,228 @@ Status adam_v1_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, con
   return out[3].dtype == DType::kBF16 ? launch_adam<false, 1>(a, stream) : launch_adam<false, 2>(a, stream);
 }
 
+// ---------------------------------------------------------------- adam_step_f32_multi_v1
+// One launch for the whole optimizer step of a model: up to kMultiMax parameter tensors, each updated in place with
+// the fused contract above. inputs [P0,G0,M0,V0, P1,G1,M1,V1, ..., step(i32 scalar)] -> outputs, per tensor,
+// [Pt,Mt,Vt] followed by the tensor's 16-bit working copy when bit t of `lp_mask` is set. 'ADAM' payload
+// <ffff fI> + <II> tensor count, lp_mask. The reference launches one kernel per tensor
+// (ops/adam_step/launcher.cu:188-243); a plan is free to batch them: a model's biases and small matrices are
+// launch-bound on their own and cannot fill the machine, and ten tails of ten grids add up.
+//
+// The grid walks one list of 16 KiB chunks over all tensors with the bulk-copy ring of adam_bulk_kernel; what is left
+// of each tensor past its whole chunks (and tensors smaller than a chunk) is finished by one block per tensor with
+// per-thread loads.
+constexpr int kMultiMax = 16;
+struct AdamMultiArgs {
+  float* p[kMultiMax];
+  const float* g[kMultiMax];
+  float* m[kMultiMax];
+  float* v[kMultiMax];
+  void* lp[kMultiMax];             // nullptr = no working copy
+  int64_t n[kMultiMax];
+  int64_t chunk_begin[kMultiMax + 1];  // whole chunks of tensors [0, t) come before tensor t's
+  int lp_kind[kMultiMax];          // 0 none, 1 bf16, 2 f16
+  int count;
+  const int32_t* step;
+  AdamHyper h;
+};
+
+__device__ __forceinline__ void adam_multi_store(const AdamMultiArgs& a, int t, int64_t packet, const Pack16<float>& po,
+                                                 const Pack16<float>& mo, const Pack16<float>& vo) {
+  using V4 = Pack16<float>;
+  st_stream(reinterpret_cast<V4*>(a.m[t]) + packet, mo);
+  st_stream(reinterpret_cast<V4*>(a.v[t]) + packet, vo);
+  st_stream(reinterpret_cast<V4*>(a.p[t]) + packet, po);
+  if (a.lp_kind[t] == 1) store_lp_x4<1>(a.lp[t], packet, po);
+  if (a.lp_kind[t] == 2) store_lp_x4<2>(a.lp[t], packet, po);
+}
+
+__global__ void __launch_bounds__(kBulkThreads) adam_multi_kernel(const AdamMultiArgs a) {
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ int wait_failed;
+  float d1, d2;
+  adam_inverse_corrections(a.h, a.step[0], d1, d2);
+  using V4 = Pack16<float>;
+  const int64_t nchunks = a.chunk_begin[a.count];
+  const uint32_t buf0 = sm100::smem_addr(ring);
+  const uint32_t bar0 = buf0 + kBulkStages * 4 * kBulkArrayBytes;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kBulkStages; ++s) sm100::mbar_init(bar0 + 8u * s, 1);
+    sm100::mbar_init_fence();
+    wait_failed = 0;
+  }
+  __syncthreads();
+  auto tensor_of = [&](int64_t chunk) {  // the tensor whose chunk range holds `chunk` (at most kMultiMax steps)
+    int t = 0;
+    while (t + 1 < a.count && chunk >= a.chunk_begin[t + 1]) ++t;
+    return t;
+  };
+  auto fetch = [&](int64_t chunk, int slot) {  // thread 0 only
+    const int t = tensor_of(chunk);
+    const int64_t off = (chunk - a.chunk_begin[t]) * kBulkChunk;
+    const uint32_t bar = bar0 + 8u * slot, buf = buf0 + static_cast<uint32_t>(slot) * 4 * kBulkArrayBytes;
+    sm100::mbar_expect_tx(bar, 4 * kBulkArrayBytes);
+    sm100::bulk_copy_g2s(buf, a.p[t] + off, kBulkArrayBytes, bar);
+    sm100::bulk_copy_g2s(buf + kBulkArrayBytes, a.g[t] + off, kBulkArrayBytes, bar);
+    sm100::bulk_copy_g2s(buf + 2 * kBulkArrayBytes, a.m[t] + off, kBulkArrayBytes, bar);
+    sm100::bulk_copy_g2s(buf + 3 * kBulkArrayBytes, a.v[t] + off, kBulkArrayBytes, bar);
+  };
+  if (threadIdx.x == 0)
+    for (int s = 0; s < kBulkStages; ++s) {
+      const int64_t c = blockIdx.x + static_cast<int64_t>(s) * gridDim.x;
+      if (c < nchunks) fetch(c, s);
+    }
+  int slot = 0;
+  uint32_t parity = 0;
+  for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+    if (!sm100::mbar_wait_bounded(bar0 + 8u * slot, parity, kBulkWaitBudgetNs)) wait_failed = 1;
+    const V4* sp = reinterpret_cast<const V4*>(ring + static_cast<size_t>(slot) * 4 * kBulkArrayBytes);
+    V4 p[kBulkPackets], g[kBulkPackets], m[kBulkPackets], v[kBulkPackets];
+#pragma unroll
+    for (int u = 0; u < kBulkPackets; ++u) {
+      const int j = threadIdx.x + u * kBulkThreads;
+      p[u] = sp[j];
+      g[u] = sp[kBulkChunk / 4 + j];
+      m[u] = sp[2 * (kBulkChunk / 4) + j];
+      v[u] = sp[3 * (kBulkChunk / 4) + j];
+    }
+    __syncthreads();  // every thread holds its packets: the slot may be refilled; the flag is seen by all
+    if (wait_failed) {
+      if (threadIdx.x == 0) atomicExch(&g_adam_status, 1);
+      break;
+    }
+    if (threadIdx.x == 0) {
+      const int64_t ahead = c + static_cast<int64_t>(kBulkStages) * gridDim.x;
+      if (ahead < nchunks) {
+        sm100::fence_generic_to_async_smem();
+        fetch(ahead, slot);
+      }
+    }
+    const int t = tensor_of(c);
+    const int64_t base = (c - a.chunk_begin[t]) * (kBulkChunk / 4);
+#pragma unroll
+    for (int u = 0; u < kBulkPackets; ++u) {
+      V4 po, mo, vo;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        adam_one<false>(p[u].v[e], g[u].v[e], m[u].v[e], v[u].v[e], a.h, d1, d2, po.v[e], mo.v[e], vo.v[e]);
+      adam_multi_store(a, t, base + threadIdx.x + u * kBulkThreads, po, mo, vo);
+    }
+    if (++slot == kBulkStages) {
+      slot = 0;
+      parity ^= 1u;
+    }
+  }
+  // what the whole chunks leave over, one block per tensor
+  for (int t = blockIdx.x; t < a.count; t += gridDim.x) {
+    const int64_t done = (a.chunk_begin[t + 1] - a.chunk_begin[t]) * kBulkChunk;
+    const int64_t left = a.n[t] - done;
+    const int64_t pk0 = done >> 2, pk1 = pk0 + (left >> 2);
+    for (int64_t j = pk0 + threadIdx.x; j < pk1; j += kBulkThreads) {
+      const V4 p = ld_stream(reinterpret_cast<const V4*>(a.p[t]) + j), g = ld_stream(reinterpret_cast<const V4*>(a.g[t]) + j),
+               m = ld_stream(reinterpret_cast<const V4*>(a.m[t]) + j), v = ld_stream(reinterpret_cast<const V4*>(a.v[t]) + j);
+      V4 po, mo, vo;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) adam_one<false>(p.v[e], g.v[e], m.v[e], v.v[e], a.h, d1, d2, po.v[e], mo.v[e], vo.v[e]);
+      adam_multi_store(a, t, j, po, mo, vo);
+    }
+    for (int64_t k = (pk1 << 2) + threadIdx.x; k < a.n[t]; k += kBulkThreads) {
+      float po, mo, vo;
+      adam_one<false>(a.p[t][k], a.g[t][k], a.m[t][k], a.v[t][k], a.h, d1, d2, po, mo, vo);
+      a.m[t][k] = mo;
+      a.v[t][k] = vo;
+      a.p[t][k] = po;
+      if (a.lp_kind[t] == 1) store_lp_x1<1>(a.lp[t], k, po);
+      if (a.lp_kind[t] == 2) store_lp_x1<2>(a.lp[t], k, po);
+    }
+  }
+}
+
+struct AdamMultiAttrs {
+  AdamHyper h;
+  uint32_t count;
+  uint32_t lp_mask;
+};
+bool read_adam_multi(const void* attr, AdamMultiAttrs* out) {
+  const AttrBlob& b = blob_of(attr);
+  if (b.schema_id != schema::kAdam || !b.data || b.bytes < 32) return false;
+  std::memcpy(&out->h, b.data, 24);
+  std::memcpy(&out->count, static_cast<const uint8_t*>(b.data) + 24, 4);
+  std::memcpy(&out->lp_mask, static_cast<const uint8_t*>(b.data) + 28, 4);
+  return out->count >= 1 && out->count <= static_cast<uint32_t>(kMultiMax) && (out->lp_mask >> out->count) == 0;
+}
+bool adam_multi_check(const TensorDesc* in, int ni, const TensorDesc* out, int no, const void* attr, AdamMultiAttrs* at) {
+  if (!in || !out || !read_adam_multi(attr, at)) return false;
+  const int T = static_cast<int>(at->count);
+  int lp_count = 0;
+  for (int t = 0; t < T; ++t) lp_count += (at->lp_mask >> t) & 1u;
+  if (ni != 4 * T + 1 || no != 3 * T + lp_count) return false;
+  if (!i32_scalar(in[4 * T])) return false;
+  int o = 0;
+  for (int t = 0; t < T; ++t) {
+    const TensorDesc* q = in + 4 * t;
+    for (int i = 0; i < 4; ++i) {
+      if (!f32_contig_rank1p(q[i]) || !same_shape(q[0], q[i]) || !aligned_to(q[i].data, 16)) return false;
+      for (int j = 0; j < i; ++j)
+        if (same_ptr(q[i], q[j])) return false;
+    }
+    // in place only: outputs are the parameter and its two moments themselves
+    if (!same_ptr(out[o], q[0]) || !same_ptr(out[o + 1], q[2]) || !same_ptr(out[o + 2], q[3])) return false;
+    for (int i = 0; i < 3; ++i)
+      if (!f32_contig_rank1p(out[o + i]) || !same_shape(q[0], out[o + i])) return false;
+    o += 3;
+    if ((at->lp_mask >> t) & 1u) {
+      const TensorDesc& lp = out[o++];
+      if ((lp.dtype != DType::kBF16 && lp.dtype != DType::kF16) || !lp.contiguous || !same_shape(q[0], lp) || !aligned_to(lp.data, 8))
+        return false;
+    }
+  }
+  return true;
+}
+bool adam_multi_supported(const TensorDesc* in, int ni, const TensorDesc* out, int no, const void* attr) {
+  AdamMultiAttrs at;
+  return adam_multi_check(in, ni, out, no, attr, &at);
+}
+Status adam_multi_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, const void* attr, void*, size_t,
+                         cudaStream_t stream) {
+  AdamMultiAttrs at;
+  if (!adam_multi_check(in, ni, out, no, attr, &at)) return Status::InvalidArgument;
+  AdamMultiArgs a{};
+  a.count = static_cast<int>(at.count);
+  a.h = at.h;
+  a.step = static_cast<const int32_t*>(in[4 * a.count].data);
+  int o = 0;
+  a.chunk_begin[0] = 0;
+  for (int t = 0; t < a.count; ++t) {
+    a.p[t] = static_cast<float*>(in[4 * t].data);
+    a.g[t] = static_cast<const float*>(in[4 * t + 1].data);
+    a.m[t] = static_cast<float*>(in[4 * t + 2].data);
+    a.v[t] = static_cast<float*>(in[4 * t + 3].data);
+    a.n[t] = numel_raw(in[4 * t]);
+    a.chunk_begin[t + 1] = a.chunk_begin[t] + a.n[t] / kBulkChunk;
+    o += 3;
+    if ((at.lp_mask >> t) & 1u) {
+      a.lp[t] = out[o].data;
+      a.lp_kind[t] = out[o].dtype == DType::kBF16 ? 1 : 2;
+      ++o;
+    }
+  }
+  static PerDeviceOnce smem_opt_in;
+  if (!smem_opt_in.run([] {
+        return cudaFuncSetAttribute(adam_multi_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(kBulkSmem)) == cudaSuccess;
+      })) {
+    cudaGetLastError();
+    return Status::Internal;
+  }
+  const int per_sm = static_cast<int>((227 * 1024) / (kBulkSmem + 1024));
+  const int64_t work = a.chunk_begin[a.count] > a.count ? a.chunk_begin[a.count] : a.count;
+  const int grid = streaming_grid(work, 1, per_sm);
+  cudaGetLastError();
+  adam_multi_kernel<<<grid, kBulkThreads, kBulkSmem, stream>>>(a);
+  return launch_status();
+}
+
 // ---------------------------------------------------------------- step_inc
 // Contract (ops/step_inc/launcher.cu:92-144): int32, same shape, rank 0 allowed. The reference
 // increments the OUTPUT buffer and never reads the input, so out-of-place use relies on the caller
@@ -504,6 +718,7 @@ int adam_pipeline_status(bool clear) {
 
 KernelVariant make_adam_step_f32_variant() { return make("adam_step_f32_sm100", schema::kAdam, adam_v0_launch, adam_v0_supported); }
 KernelVariant make_adam_step_f32_fused_variant() { return make("adam_step_f32_fused_sm100", schema::kAdam, adam_v1_launch, adam_v1_supported); }
+KernelVariant make_adam_step_f32_multi_variant() { return make("adam_step_f32_multi_sm100", schema::kAdam, adam_multi_launch, adam_multi_supported); }
 KernelVariant make_step_inc_variant() { return make("step_inc_i32_sm100", 0, step_inc_launch, step_inc_supported); }
 KernelVariant make_biascorr_variant() { return make("bias_corr_f32_sm100", schema::kBiasCorr, bias_corr_launch, bias_corr_supported); }
 KernelVariant make_sgd_step_f32_variant() { return make("sgd_step_f32_sm100", 0, sgd_launch<DType::kF32, float>, sgd_supported<DType::kF32>); }

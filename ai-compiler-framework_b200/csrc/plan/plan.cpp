@@ -17,6 +17,7 @@
 #include <vector>
 
 #include "../capi/capi_internal.hpp"
+#include "aicf/backends/cuda/nvtx.hpp"
 
 using aicf::cuda::AttrBlob;
 using aicf::cuda::DType;
@@ -107,6 +108,7 @@ struct aicf_plan {
   size_t peer_pool_bytes = 0;
   std::vector<void*> peer_mapped;  // other ranks' pools opened through IPC handles
   bool peers_open = false;
+  std::vector<void*> peer_bases;   // every rank's pool as seen from this device (own entry = peer_pool)
   int peer_world = 1;
   cudaStream_t stream = nullptr, comm_stream = nullptr;
   cudaGraph_t graph = nullptr;
@@ -250,6 +252,7 @@ int enqueue_all(aicf_plan* p, cudaStream_t main, std::vector<cudaEvent_t>* marks
       if (int rc = check_cuda(cudaStreamWaitEvent(p->comm_stream, op.ev_ready, 0), "cudaStreamWaitEvent(fork)")) return rc;
       s = p->comm_stream;
     }
+    AICF_NVTX_RANGE(op.variant->kernel_id);  // eager: the launch; under capture: the recording of the op's node
     const Status st = op.variant->launch(op.in_desc.data(), static_cast<int>(op.in_desc.size()), op.out_desc.data(),
                                          static_cast<int>(op.out_desc.size()), &op.blob, op.ws_bytes ? p->ws : nullptr,
                                          op.ws_bytes ? p->ws_bytes : 0, s);
@@ -428,6 +431,7 @@ int aicf_b200_plan_open_peers(aicf_plan* p, int rank, int world, const void* han
     return fail(Status::Internal, "plan_open_peers: pool registration failed");
   p->peers_open = true;
   p->peer_world = world;
+  p->peer_bases = bases;
   return AICF_OK;
 }
 
@@ -444,6 +448,7 @@ int aicf_b200_plan_open_peers_raw(aicf_plan* p, int rank, int world, void* const
     return fail(Status::Internal, "plan_open_peers_raw: pool registration failed");
   p->peers_open = true;
   p->peer_world = world;
+  p->peer_bases = b;
   return AICF_OK;
 }
 
@@ -620,6 +625,11 @@ int64_t aicf_b200_plan_value_arena_offset(aicf_plan* p, int vid) {
   return (q >= base && q < base + p->pooled_bytes) ? static_cast<int64_t>(q - base) : -1;
 }
 size_t aicf_b200_plan_peer_pool_bytes(aicf_plan* p) { return p ? p->peer_pool_bytes : 0; }
+void* aicf_b200_plan_peer_pool_base(aicf_plan* p, int rank) {
+  if (!p || rank < 0) return nullptr;
+  if (!p->peers_open) return rank == 0 ? p->peer_pool : nullptr;
+  return static_cast<size_t>(rank) < p->peer_bases.size() ? p->peer_bases[static_cast<size_t>(rank)] : nullptr;
+}
 size_t aicf_b200_plan_arena_bytes(aicf_plan* p) { return p ? p->arena_bytes : 0; }
 size_t aicf_b200_plan_arena_bytes_no_reuse(aicf_plan* p) { return p ? p->no_reuse_bytes : 0; }
 int aicf_b200_plan_num_ops(aicf_plan* p) { return p ? static_cast<int>(p->ops.size()) : 0; }

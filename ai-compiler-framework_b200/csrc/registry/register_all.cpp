@@ -17,6 +17,7 @@ namespace aicf::cuda {
 // optimizer.cu
 KernelVariant make_adam_step_f32_variant();
 KernelVariant make_adam_step_f32_fused_variant();
+KernelVariant make_adam_step_f32_multi_variant();
 KernelVariant make_step_inc_variant();
 KernelVariant make_biascorr_variant();
 KernelVariant make_sgd_step_f32_variant();
@@ -179,6 +180,7 @@ extern "C" void aicf_cuda_register_all_kernels() {
       {K::Copy, make_copy_bf16_variant, 15, "copy_bf16_v0"},
       {K::Copy, make_copy_i32_variant, 10, "copy_i32_v0"},
       {K::AdamStep, make_adam_step_f32_fused_variant, -10, "adam_step_f32_fused_v1"},
+      {K::AdamStep, make_adam_step_f32_multi_variant, -20, "adam_step_f32_multi_v1"},
       {K::Softmax, make_softmax_lastdim_f32_variant, 0, "softmax_lastdim_f32_v0"},
       {K::Softmax, make_softmax_lastdim_bf16_variant, 0, "softmax_lastdim_bf16_v0"},
       {K::Softmax, make_softmax_lastdim_f16_variant, 0, "softmax_lastdim_f16_v0"},

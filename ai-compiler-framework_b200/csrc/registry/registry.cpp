@@ -12,6 +12,7 @@
 #include <atomic>
 #include <cstdio>
 
+#include "aicf/backends/cuda/nvtx.hpp"
 #include "aicf/backends/cuda/registry/attr_blob.hpp"
 #include "aicf/backends/cuda/registry/dispatch.hpp"
 #include "aicf/backends/cuda/registry/register_all.hpp"
@@ -106,6 +107,7 @@ bool call_is_sane(const OpCall& c) {
 }
 
 Status run_variant(const KernelVariant* v, const OpCall& c, const AttrBlob* attrs) {
+  AICF_NVTX_RANGE(v->kernel_id);  // one range per dispatched launch, named by the kernel id (AICF_ENABLE_NVTX=1)
   void* ws = nullptr;
   size_t ws_bytes = 0;
   if (v->query_workspace) {

@@ -81,6 +81,7 @@ PROTOTYPES = {
     "aicf_b200_device_count": (_i, []),
     "aicf_b200_set_device": (_i, [_i]),
     "aicf_b200_device_info": (_i, [_i, _P(C.c_int64), _P(C.c_int), _P(C.c_int64)]),
+    "aicf_b200_stream_probe": (_i, [_i, _i, _P(_vp), _P(_vp), _sz, _i, _i, _u64]),
     "aicf_b200_malloc": (_i, [_P(_vp), _sz]),
     "aicf_b200_free": (_i, [_vp]),
     "aicf_b200_host_alloc_pinned": (_i, [_P(_vp), _sz]),
@@ -110,6 +111,7 @@ PROTOTYPES = {
     "aicf_b200_plan_open_peers": (_i, [_vp, _i, _i, _vp]),
     "aicf_b200_plan_open_peers_raw": (_i, [_vp, _i, _i, _P(_vp)]),
     "aicf_b200_plan_peer_pool_bytes": (_sz, [_vp]),
+    "aicf_b200_plan_peer_pool_base": (_vp, [_vp, _i]),
     "aicf_b200_plan_finalize": (_i, [_vp]),
     "aicf_b200_plan_value_ptr": (_vp, [_vp, _i]),
     "aicf_b200_plan_value_bytes": (_sz, [_vp, _i]),

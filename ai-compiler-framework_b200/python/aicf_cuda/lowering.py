@@ -24,7 +24,7 @@ def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str 
                          lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
                          weight_decay: float = 0.0, data_parallel=False, with_argmax: bool = False,
                          input_f32: bool = True, fuse_relu_bwd: bool = True,
-                         fp32_gemm: str = "exact") -> Tuple[List[ValueSpec], List[Dict[str, Any]]]:
+                         fp32_gemm: str = "exact", fuse_adam: bool = True) -> Tuple[List[ValueSpec], List[Dict[str, Any]]]:
     """dims = [in, hidden..., out]. Every Linear but the last is followed by ReLU.
 
     compute_dtype 'f32': GEMMs run on fp32 parameters directly.
@@ -36,6 +36,9 @@ def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str 
     fp32_gemm (compute_dtype 'f32' only): 'exact' pins the fp32 FMA kernels (bit-identical to the reference's);
     '3xtf32' pins the tensor-core ids that form every product from three TF32 products (~6x faster on large layers,
     normwise error ~2e-6 instead of ~4e-7).
+
+    fuse_adam: the whole optimizer step is one `adam_step` op over all parameter tensors (kernel
+    adam_step_f32_multi_v1) instead of one op per tensor; the arithmetic per element is the same.
 
     data_parallel: False - single device; True / "nccl" - an all_reduce op per gradient tensor, then the
     ordinary fused Adam; "fused" - one dp_adam_step op per parameter that exchanges the gradient over peer
@@ -168,6 +171,17 @@ def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str 
 
     # ---- optimizer ---------------------------------------------------------------------------------
     op("step_inc", [step], [step], None, "step_inc_v0")
+    if fuse_adam and 2 * L <= 16:
+        # one launch for all 2L parameter tensors: inputs [P,G,M,V] per tensor then the step counter; outputs
+        # [P,M,V(,working copy)] per tensor
+        ins, outs, mask = [], [], 0
+        for t, (P, G, Mo, Vo, lp) in enumerate([(W[i], dW[i], mW[i], vW[i], Wlp[i] if mixed else None) for i in range(L)] +
+                                               [(b[i], db[i], mb[i], vb[i], None) for i in range(L)]):
+            ins += [P, G, Mo, Vo]
+            outs += [P, Mo, Vo] + ([lp] if lp is not None else [])
+            mask |= (1 << t) if lp is not None else 0
+        op("adam_step", ins + [step], outs, dict(hyper, count=2 * L, lp_mask=mask), "adam_step_f32_multi_v1")
+        return vals, ops
     for i in range(L):
         outs = [W[i], mW[i], vW[i]] + ([Wlp[i]] if mixed else [])
         op("adam_step", [W[i], dW[i], mW[i], vW[i], step], outs, hyper, "adam_step_f32_fused_v1")

@@ -62,8 +62,10 @@ def pack_attrs(op: str, attrs: Optional[Dict[str, Any]]) -> Tuple[int, bytes]:
     if op == "adam_step":
         payload = struct.pack("<ffff", float(a.get("lr", 1e-3)), float(a.get("beta1", 0.9)),
                               float(a.get("beta2", 0.999)), float(a.get("eps", 1e-8)))
-        if "weight_decay" in a or "decoupled" in a:
+        if "weight_decay" in a or "decoupled" in a or "count" in a:
             payload += struct.pack("<fI", float(a.get("weight_decay", 0.0)), 1 if a.get("decoupled", False) else 0)
+        if "count" in a:  # multi-tensor form (adam_step_f32_multi_v1): tensor count and which tensors have a 16-bit copy
+            payload += struct.pack("<II", int(a["count"]), int(a.get("lp_mask", 0)))
         return SCHEMA_ADAM, payload
     if op == "dp_adam_step":
         payload = struct.pack("<fffffIi", float(a.get("lr", 1e-3)), float(a.get("beta1", 0.9)),
@@ -268,6 +270,10 @@ class Plan:
     @property
     def peer_pool_bytes(self) -> int:
         return int(lib.aicf_b200_plan_peer_pool_bytes(self._h))
+
+    def peer_pool_base(self, rank: int) -> int:
+        """Device address of rank `rank`'s pool as mapped into this process (0 if not mapped)."""
+        return int(lib.aicf_b200_plan_peer_pool_base(self._h, int(rank)) or 0)
 
     def open_peers_raw(self, rank: int, world: int, bases: Sequence[int]) -> None:
         """Like open_peers, from device addresses of the other ranks' pools (bases[rank] is ignored)."""

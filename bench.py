@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the op backend + captured-plan hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload mlp|mlp_c1|gemm|gemm_f32|softmax|ce|reduce|adam]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload mlp|mlp_c1|gemm|gemm_f32|gemm_tf32x3|softmax|ce|reduce|adam|ln_fwd|ln_bwd|stream_mix]
                     [--impl reference] [--small] [--no-check] [--no-kernels]
 
 Default workload `mlp`: the data-parallel captured MLP train step (4x Linear(8192->8192)+ReLU ->
@@ -295,7 +295,7 @@ class CpuMlpSample:
     def __init__(self, dims, b, gbatch):
         import oracle
         self.oracle, self.b, self.gbatch = oracle, b, gbatch
-        vals, low = host_lowering().build_mlp_train_step(b, dims, compute_dtype="bf16", global_batch=gbatch, **ADAM)
+        vals, low = host_lowering().build_mlp_train_step(b, dims, compute_dtype="bf16", global_batch=gbatch, fuse_adam=False, **ADAM)
         params = oracle.mlp_params(dims, seed=4)
         x, y = oracle.mlp_batch(b, dims[0], dims[-1], seed=4)
         self.dtypes = {v.vid: v.dtype for v in vals}
@@ -536,6 +536,70 @@ def run_mlp_reference(args, world: int):
             "note": "ms_per_step is the sample step scaled to the full 65536-row step (seconds_per_sample_step x 65536 / rows)"}
 
 
+def run_p2p_probe(args, dist: Dist):
+    """Measured ceiling of the peer links for the exchange kernel: the stream probe (16-byte loads / stores, no
+    arithmetic to speak of) reading from, and writing to, another rank's memory through the same IPC mappings the
+    plans use. Every rank does the same thing at the same time (rank r talks to rank r+1), so each GPU carries one
+    stream in and one stream out, as in the exchange. Reports GB/s per GPU and direction, max time over ranks."""
+    import ctypes as C
+    import aicf_cuda
+    from aicf_cuda import Plan, Tensor, ValueSpec, dp
+    from aicf_cuda.plan import ROLE_STATIC
+    lib = aicf_cuda.lib
+    rank, local_rank, world = dist.rank, dist_env()[1], dist.world
+    if world < 2:
+        raise SystemExit("p2p_probe needs at least 2 ranks (torchrun)")
+    aicf_cuda._lib.check(lib.aicf_b200_set_device(local_rank), "set_device")
+    n = 1 << 26  # 256 MiB per buffer
+    vals = [ValueSpec(0, "window", (n,), "f32", ROLE_STATIC, persistent=True, peer_visible=True),
+            ValueSpec(1, "scratch", (4,), "f32", ROLE_STATIC, persistent=True)]
+    plan = Plan("p2p_probe", vals, [{"op": "grad_zero", "inputs": [1], "outputs": [1], "attrs": {}, "kernel_id": "grad_zero_v0"}])
+    dp.connect_plans([plan], rank, world, dist.allgather)
+    off = plan.tensor("window").ptr - plan.peer_pool_base(rank)
+    window_of = lambda k: plan.peer_pool_base(k) + off
+    local = [Tensor.zeros((n,)) for _ in range(2)]
+    ev = Events(lib)
+
+    def timed(reads, writes, ins, outs, in_flight, blocks):
+        a = (C.c_void_p * reads)(*ins)
+        b = (C.c_void_p * writes)(*outs)
+        launch = lambda: aicf_cuda._lib.check(lib.aicf_b200_stream_probe(reads, writes, a, b, 4 * n, in_flight, blocks, 0), "stream_probe")
+        for _ in range(3):
+            launch()
+        lib.aicf_b200_device_sync()
+        dist.barrier()
+        reps = 20
+        ev.start(0)
+        for _ in range(reps):
+            launch()
+        ms = dist.max_float(ev.stop_ms(0)) / reps
+        dist.barrier()
+        return ms
+
+    right = (rank + 1) % world
+    others = [(rank + j) % world for j in range(1, min(world, 5))]
+    res = {}
+    for in_flight, blocks in ((2, 8), (4, 8), (4, 16)):
+        tag = f"inflight{in_flight}_blocks{blocks}"
+        ms = timed(1, 1, [window_of(right)], [local[0].ptr], in_flight, blocks)
+        res[f"pull_from_one_peer_{tag}"] = 4 * n / ms / 1e6
+        ms = timed(1, 1, [local[0].ptr], [window_of(right)], in_flight, blocks)
+        res[f"push_to_one_peer_{tag}"] = 4 * n / ms / 1e6
+        ms = timed(len(others), 1, [window_of(k) for k in others], [local[0].ptr], in_flight, blocks)
+        res[f"pull_from_{len(others)}_peers_{tag}"] = 4 * n * len(others) / ms / 1e6
+        ms = timed(1, 1, [local[1].ptr], [local[0].ptr], in_flight, blocks)
+        res[f"local_copy_{tag}"] = 2 * 4 * n / ms / 1e6
+    plan.close()
+    if rank != 0:
+        return None
+    best = max(v for k, v in res.items() if k.startswith("pull_from"))
+    return {"metric": "peer-memory probe GB/s per GPU and direction (NVLink)", "value": best, "unit": "GB/s", "n_gpus": world,
+            "steps": 20, "warmup": 3, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": {"workload": "p2p_probe", "bytes_per_buffer": 4 * n,
+                                                               "pattern": "every rank reads from / writes to rank+1 at the same time"},
+            "gb_per_s": {k: round(v, 1) for k, v in res.items()}, "gpu_launches": 20 * 12}
+
+
 def run_mlp_c1(args):
     """BASELINE config 1: fp32 MLP 784->256->10, batch 64, captured replay (launch/latency-bound; reports us/step)."""
     import aicf_cuda
@@ -599,7 +663,8 @@ def _verdict(what, err, tol):
     return {"what": what, "max_err": float(err), "tolerance": float(tol), "ok": bool(err <= tol)}
 
 
-def kernel_case(w, *, small=False, size=0, rows=0, cols=0, dtype="f32", reduce_kind="sum", transb=False, want_check=True):
+def kernel_case(w, *, small=False, size=0, rows=0, cols=0, dtype="f32", reduce_kind="sum", transb=False, want_check=True,
+                probe=(0, 0)):
     """One single-kernel workload on a benchmark shape: device buffers, the launch closure `fn(stream)`, its algorithmic
     work, and `check()`, which reads a sample of the output back and compares it with the oracle (never timed)."""
     import oracle
@@ -773,6 +838,22 @@ def kernel_case(w, *, small=False, size=0, rows=0, cols=0, dtype="f32", reduce_k
                     worst = max(worst, float(np.max(np.abs(got - wnt) / (np.abs(wnt) + atol / 1e-5))))
             return _verdict(f"first step (t = 1): {len(starts)} slices of 4096 elements of p, m, v against the fp64 oracle, relative", worst, 1e-5)
         case["before"] = check_first_launch
+    elif w == "stream_mix":
+        # the ceiling for a streaming kernel with R input and W output arrays (rows = R, cols = W; default 4 + 3 = Adam's mix)
+        import ctypes as C
+        import aicf_cuda
+        R, Wn = rows or 4, cols or 3
+        n = (1 << 24) if small else (1 << 28)
+        bufs = [Tensor.zeros((n,)) for _ in range(R + Wn)]
+        ins = (C.c_void_p * R)(*[b.ptr for b in bufs[:R]])
+        outs = (C.c_void_p * Wn)(*[b.ptr for b in bufs[R:]])
+
+        def fn(st):
+            aicf_cuda._lib.check(aicf_cuda.lib.aicf_b200_stream_probe(R, Wn, ins, outs, 4 * n, probe[0], probe[1], st), "stream_probe")
+        case.update(work=4.0 * n * (R + Wn), unit="GB/s", bound="hbm", peak=peaks["hbm_gbs"],
+                    metric=f"stream-mix probe: {R} arrays read, {Wn} written, HBM GB/s", keep=bufs,
+                    cfg={"workload": f"stream_mix_{R}r{Wn}w_f32", "elements": n, "packets_in_flight": probe[0] or 2,
+                         "blocks_per_sm": probe[1] or 8, "l2": f"{R + Wn} streams of {4 * n >> 20} MiB exceed L2"})
     else:
         raise SystemExit(f"unknown workload {w}")
     case["fn"] = fn
@@ -824,7 +905,8 @@ def run_kernel_workload(args):
     from aicf_cuda import _C
     peaks = measured_peaks()
     case = kernel_case(args.workload, small=args.small, size=args.size, rows=args.rows, cols=args.cols, dtype=args.dtype,
-                       reduce_kind=args.reduce_kind, transb=args.transb, want_check=not args.no_check)
+                       reduce_kind=args.reduce_kind, transb=args.transb, want_check=not args.no_check,
+                       probe=(args.probe_in_flight, args.probe_blocks))
     r = time_case(case, args.steps, args.warmup)
     cfg = dict(case["cfg"], launches_per_timed_graph=r["reps"])
     out = {"metric": case["metric"], "value": r["achieved"], "unit": case["unit"], "n_gpus": 1, "steps": args.steps,
@@ -842,7 +924,9 @@ def run_kernel_workload(args):
 KERNEL_SUITE = [("gemm_8192_bf16", "gemm", dict(size=8192)), ("gemm_4096_bf16", "gemm", dict(size=4096)),
                 ("gemm_1024_bf16", "gemm", dict(size=1024)), ("softmax_f32", "softmax", dict(dtype="f32")),
                 ("softmax_bf16", "softmax", dict(dtype="bf16")), ("softmax_ce_f32", "ce", {}),
-                ("reduce_sum_f32", "reduce", dict(dtype="f32", reduce_kind="sum")), ("adam_f32_2p28", "adam", {})]
+                ("reduce_sum_f32", "reduce", dict(dtype="f32", reduce_kind="sum")), ("adam_f32_2p28", "adam", {}),
+                # measured ceilings for the stream mixes above: 4 arrays read + 3 written (Adam), 1 + 1 (softmax, CE)
+                ("ceiling_4_reads_3_writes", "stream_mix", dict(rows=4, cols=3)), ("ceiling_1_read_1_write", "stream_mix", dict(rows=1, cols=1))]
 
 
 def run_kernel_suite(args):
@@ -875,6 +959,8 @@ def main():
     ap.add_argument("--dtype", default="f32")
     ap.add_argument("--reduce-kind", default="sum")
     ap.add_argument("--transb", action="store_true")
+    ap.add_argument("--probe-in-flight", type=int, default=0, help="stream_mix: 16-byte packets per array in flight per thread (1, 2, 4)")
+    ap.add_argument("--probe-blocks", type=int, default=0, help="stream_mix: 256-thread blocks per SM (1-32)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed NumPy baseline")
     ap.add_argument("--no-check", action="store_true", help="skip the oracle comparison of read-back samples (never timed)")
     ap.add_argument("--no-kernels", action="store_true", help="N = 1 MLP line without the single-kernel measurements")
@@ -895,12 +981,12 @@ def main():
     if args.workload == "mlp_c1":
         print(json.dumps(run_mlp_c1(args)), flush=True)
         return
-    if args.workload != "mlp":
+    if args.workload not in ("mlp", "p2p_probe"):
         print(json.dumps(run_kernel_workload(args)), flush=True)
         return
     dist = Dist(world)
     try:
-        out = run_mlp(args, dist)
+        out = run_p2p_probe(args, dist) if args.workload == "p2p_probe" else run_mlp(args, dist)
         if out is not None:
             print(json.dumps(out), flush=True)
     finally:

@@ -156,6 +156,14 @@ int aicf_b200_set_device(int device);
 /* Facts about a device that sizing decisions and benchmark reports need: L2 cache bytes, SM count, total global
  * memory bytes (any pointer may be NULL). What a torch user reads from torch.cuda.get_device_properties. */
 int aicf_b200_device_info(int device, int64_t* l2_bytes, int* sm_count, int64_t* total_bytes);
+/* Measuring aid: a minimal streaming kernel that reads `reads` (1-4) arrays and writes `writes` (1-3) arrays of
+ * bytes_each bytes (16-byte aligned, multiple of 16) with 16-byte evict-first accesses - the bandwidth ceiling of this
+ * device for a kernel with that mix of input and output streams (fused Adam: 4 + 3), which a plain copy's rate
+ * overstates. packets_in_flight (1, 2 or 4; 0 = 2) is the number of 16-byte packets per array each thread has in
+ * flight, blocks_per_sm (1-32; 0 = 8) the number of 256-thread blocks per SM: the ceiling is the best rate over
+ * those choices. No counterpart in the reference. */
+int aicf_b200_stream_probe(int reads, int writes, const void* const* inputs, void* const* outputs, size_t bytes_each,
+                           int packets_in_flight, int blocks_per_sm, aicf_stream stream);
 int aicf_b200_malloc(void** ptr, size_t bytes);
 int aicf_b200_free(void* ptr);
 int aicf_b200_host_alloc_pinned(void** ptr, size_t bytes);
@@ -223,6 +231,10 @@ int aicf_b200_plan_open_peers(aicf_plan* plan, int rank, int world, const void* 
  * bases[k] = address of rank k's pool as seen from this device; bases[rank] is ignored. */
 int aicf_b200_plan_open_peers_raw(aicf_plan* plan, int rank, int world, void* const* bases);
 size_t aicf_b200_plan_peer_pool_bytes(aicf_plan* plan);
+/* Address, as seen from this device, of rank `rank`'s pool once the peers are open (the own rank: the plan's own
+ * pool; before open_peers only rank 0 = the own pool answers). NULL otherwise. The first 8 KiB of a pool are the
+ * exchange's control block. For tools that measure the peer links with the plan's own mappings. */
+void* aicf_b200_plan_peer_pool_base(aicf_plan* plan, int rank);
 /* Allocates the arena and every unbound value, resolves variants. No ops may be added afterwards. */
 int aicf_b200_plan_finalize(aicf_plan* plan);
 void* aicf_b200_plan_value_ptr(aicf_plan* plan, int vid);

@@ -96,6 +96,17 @@ def run_lowered(lowered: Sequence[Dict[str, Any]], env: Dict[int, np.ndarray], d
             store(o[0], O.add(i[0], i[1], dt))
         elif op == "adam_step":
             kw = dict(lr=a.get("lr", 1e-3), beta1=a.get("beta1", 0.9), beta2=a.get("beta2", 0.999), eps=a.get("eps", 1e-8))
+            if len(i) > 6:   # multi-tensor form: [P,G,M,V] per tensor, then the step counter; in place
+                T, step_now, k = (len(i) - 1) // 4, int(np.ravel(i[-1])[0]), 0
+                for q in range(T):
+                    p, m, v = O.adam_step_fused(i[4 * q], i[4 * q + 1], i[4 * q + 2], i[4 * q + 3], step_now,
+                                                weight_decay=a.get("weight_decay", 0.0), decoupled=a.get("decoupled", False), dt=dt, **kw)
+                    store(o[k], p), store(o[k + 1], m), store(o[k + 2], v)
+                    k += 3
+                    if (int(a.get("lp_mask", 0)) >> q) & 1:
+                        store(o[k], p)  # low-precision working copy of the new parameter
+                        k += 1
+                continue
             if len(i) == 6:  # reference contract: divisor scalars
                 p, m, v = O.adam_step_v0(i[0], i[1], i[2], i[3], float(np.ravel(i[4])[0]), float(np.ravel(i[5])[0]), dt=dt, **kw)
             else:            # fused contract: device step counter

@@ -338,3 +338,81 @@ def test_softmax_ce_ties_and_out_of_range_labels(gpu):
     assert list(A.numpy()) == [5, 63, 0, 0] == list(wa)
     assert_close_f32(host(L), wl, atol=1e-6)
     assert_close_f32(host(D), wd, atol=1e-9)
+
+
+# ------------------------------------------------------------------ multi-tensor Adam (one launch for a whole model)
+def _multi_adam(sizes, lp_kinds, step_value, wd, dec, seed=0):
+    """Launches adam_step_f32_multi_v1 over tensors of `sizes`; returns per tensor (device results, oracle results)."""
+    rng = np.random.default_rng(seed)
+    host_in, dev_in, outs, mask = [], [], [], 0
+    for t, (n, lpk) in enumerate(zip(sizes, lp_kinds)):
+        p = (rng.standard_normal(n) * 0.02).astype(np.float32)
+        g = (rng.standard_normal(n) * 1e-3).astype(np.float32)
+        m = (rng.standard_normal(n) * 1e-3).astype(np.float32)
+        v = np.abs(rng.standard_normal(n) * 1e-6).astype(np.float32)
+        host_in.append((p, g, m, v))
+        P, G, M, V = dev(p), dev(g), dev(m), dev(v)
+        dev_in += [P, G, M, V]
+        outs += [P, M, V]
+        if lpk:
+            outs.append(Tensor.empty((n,), lpk))
+            mask |= 1 << t
+    step = Tensor.from_numpy(np.array([step_value], np.int32))
+    pay = struct.pack("<fffffIII", 3e-4, 0.9, 0.999, 1e-8, wd, dec, len(sizes), mask)
+    by_id("adam_step_f32_multi_v1", OpKind.AdamStep, dev_in + [step], outs, ADAM, pay)
+    assert _C.wait_status() == 0
+    res, k = [], 0
+    for t, (n, lpk) in enumerate(zip(sizes, lp_kinds)):
+        p, g, m, v = host_in[t]
+        want = oracle.adam_step_fused(p, g, m, v, step_value, F(3e-4), F(0.9), F(0.999), F(1e-8), weight_decay=F(wd), decoupled=bool(dec))
+        got = [host(outs[k]), host(outs[k + 1]), host(outs[k + 2])]
+        k += 3
+        lp = None
+        if lpk:
+            lp = (host(outs[k]), lpk)
+            k += 1
+        res.append((got, want, lp))
+    return res
+
+
+@pytest.mark.parametrize("wd,dec", [(0.0, 0), (0.01, 0), (0.01, 1)])
+def test_adam_multi_tensor_one_launch(gpu, wd, dec):
+    # whole 16 KiB chunks, tails of every kind (packets + odd elements), tensors smaller than a chunk, one element
+    sizes = [4096 * 37 + 1001, 1000, 8192, 1, 4096 * 5, 4099, 3, 4096 * 301 + 2]
+    lps = ["bf16", None, "f16", None, "bf16", "bf16", "f16", None]
+    for (got, want, lp), n in zip(_multi_adam(sizes, lps, 7, wd, dec), sizes):
+        assert_close_f32(got[0], want[0], what=f"p[{n}]")
+        assert_close_f32(got[1], want[1], atol=1e-9, what=f"m[{n}]")
+        assert_close_f32(got[2], want[2], atol=1e-13, what=f"v[{n}]")
+        if lp:
+            assert np.array_equal(lp[0], _round(got[0], lp[1])), f"working copy of the tensor of {n} elements"
+
+
+def test_adam_multi_tensor_equals_per_tensor_launches_and_checks_its_contract(gpu):
+    sizes, lps = [4096 * 9 + 17, 513, 4096 * 2], ["bf16", None, None]
+    multi = _multi_adam(sizes, lps, 3, 0.01, 0, seed=5)
+    rng = np.random.default_rng(5)
+    for (got, _, lp), n, lpk in zip(multi, sizes, lps):  # same draws, one fused launch per tensor: identical bits
+        p, g = (rng.standard_normal(n) * 0.02).astype(np.float32), (rng.standard_normal(n) * 1e-3).astype(np.float32)
+        m, v = (rng.standard_normal(n) * 1e-3).astype(np.float32), np.abs(rng.standard_normal(n) * 1e-6).astype(np.float32)
+        P, G, M, V = dev(p), dev(g), dev(m), dev(v)
+        outs = [P, M, V] + ([Tensor.empty((n,), lpk)] if lpk else [])
+        by_id("adam_step_f32_fused_v1", OpKind.AdamStep, [P, G, M, V, Tensor.from_numpy(np.array([3], np.int32))], outs, ADAM,
+              struct.pack("<fffffI", 3e-4, 0.9, 0.999, 1e-8, 0.01, 0))
+        for a, b in zip(got, outs[:3]):
+            assert np.array_equal(a, host(b))
+        if lpk:
+            assert np.array_equal(lp[0], host(outs[3]))
+    # contract: in place only, count must match the operand lists, at most 16 tensors
+    P, G, M, V = (dev(rnd((64,), i)) for i in range(4))
+    step = Tensor.from_numpy(np.array([1], np.int32))
+    pay = lambda count, mask: struct.pack("<fffffIII", 1e-3, 0.9, 0.999, 1e-8, 0.0, 0, count, mask)
+    with pytest.raises(RuntimeError, match="InvalidArgument"):   # out of place
+        by_id("adam_step_f32_multi_v1", OpKind.AdamStep, [P, G, M, V, step], [Tensor.empty((64,)), M, V], ADAM, pay(1, 0))
+    with pytest.raises(RuntimeError, match="InvalidArgument"):   # count says two tensors, one is given
+        by_id("adam_step_f32_multi_v1", OpKind.AdamStep, [P, G, M, V, step], [P, M, V], ADAM, pay(2, 0))
+    with pytest.raises(RuntimeError, match="InvalidArgument"):   # a working copy is announced but not passed
+        by_id("adam_step_f32_multi_v1", OpKind.AdamStep, [P, G, M, V, step], [P, M, V], ADAM, pay(1, 1))
+    with pytest.raises(RuntimeError, match="InvalidArgument"):   # the plain fused payload is not enough
+        by_id("adam_step_f32_multi_v1", OpKind.AdamStep, [P, G, M, V, step], [P, M, V], ADAM,
+              struct.pack("<fffffI", 1e-3, 0.9, 0.999, 1e-8, 0.0, 0))

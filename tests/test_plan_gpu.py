@@ -300,3 +300,29 @@ def test_small_batch_plan_with_gemms_split_over_k(gpu, monkeypatch):
         eager.close()
         graphed.close()
     assert results["split"] == pytest.approx(results["unsplit"], rel=2e-3)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_one_launch_optimizer_equals_one_launch_per_tensor(gpu, dtype):
+    """The plan's optimizer as a single multi-tensor Adam launch against the per-tensor form: same parameters, moments
+    and working copies, bit for bit, eagerly and replayed; and fewer kernels in the captured graph."""
+    dims, batch = [96, 160, 64, 24], 32
+    fused, *_ = make_plan(batch, dims, dtype, seed=2, fuse_adam=True)
+    split, *_ = make_plan(batch, dims, dtype, seed=2, fuse_adam=False)
+    assert "adam_step_f32_multi_v1" in fused.kernel_ids() and "adam_step_f32_multi_v1" not in split.kernel_ids()
+    for plan in (fused, split):
+        plan.run()
+        plan.capture()
+        plan.replay(3)
+        plan.sync()
+    names = [f"{2 * i}.{p}" for i in range(len(dims) - 1) for p in ("W", "b")]
+    names += ["opt.m." + n for n in names] + ["opt.v." + n for n in names[:len(names)]]
+    if dtype != "f32":
+        names += [f"{2 * i}.W.lp" for i in range(len(dims) - 1)]
+    for n in names:
+        assert np.array_equal(fused.tensor(n).numpy(), split.tensor(n).numpy()), n
+    assert int(fused.tensor("opt.step").numpy()[0]) == 4
+    assert fused.graph_kernel_nodes == split.graph_kernel_nodes - (2 * (len(dims) - 1) - 1)
+    assert _C.wait_status() == 0
+    fused.close()
+    split.close()

@@ -275,7 +275,8 @@ __global__ void __launch_bounds__(256) dp_adam_kernel(const DpAdamArgs a) {
 }
 
 // 'DPAD' payload: the Adam payload <ffff fI> followed by <i> slot (index of this op's flag block) and, optionally,
-// <ii> defer_done (1: leave the done-phase wait to the step's fence), fence_slots (> 0: this op is the fence).
+// <ii> flags (bit 0 defer_done: leave the done-phase wait to the step's fence; bit 1 solo: no other kernel runs beside
+// this op, take two CTAs per SM), fence_slots (> 0: this op is the fence).
 constexpr uint32_t kSchemaDpAdam = 0x44415044u;  // 'DPAD' little-endian
 struct DpAttrs {
   AdamHyper h;
@@ -356,8 +357,9 @@ Status dp_adam_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, con
     a.flags_base = reinterpret_cast<const uint32_t*>(gp->mine);
     a.epoch_base = reinterpret_cast<const uint32_t*>(gp->mine + kFlagsBytes);
   }
-  a.defer_done = at.defer_done != 0 ? 1 : 0;
+  a.defer_done = (at.defer_done & 1) ? 1 : 0;
   a.fence_slots = at.fence_slots;
+  const bool solo = (at.defer_done & 2) != 0;  // nothing runs beside this op: no need to leave room for GEMM CTAs
   const void* must_align[] = {in[0].data, in[1].data, in[2].data, in[3].data, bcast_mine};
   for (const void* q : must_align)
     if (!aligned_to(q, 16)) return Status::InvalidArgument;
@@ -373,7 +375,9 @@ Status dp_adam_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, con
   a.end = std::min<int64_t>(n, (packets * (a.rank + 1) / a.world) * 4);
   // One CTA per SM at most: 256 threads x (at most) 144 registers fit beside a persistent GEMM CTA (192 x 136), two
   // would not, and a GEMM launched while this kernel is resident must still find room on every SM.
-  const int grid = streaming_grid((a.end - a.begin) / 4 + 1, 256, 1);
+  // An op marked `solo` (the step's last exchange, which has no GEMM left to overlap with) takes two CTAs per SM, all
+  // the register file allows: twice the peer loads in flight, which is what bounds a kernel that waits on NVLink.
+  const int grid = streaming_grid((a.end - a.begin) / 4 + 1, 256, solo ? 2 : 1);
   // The SM's L1/shared split is one setting for all resident CTAs. The GEMMs run with the largest shared-memory
   // split; asking for the same split here lets these CTAs and GEMM CTAs join each other's SMs in either order
   // (with the default split, a GEMM CTA would have to wait for the SM to drain first).

@@ -161,9 +161,10 @@ def build_mlp_train_step(batch: int, dims: Sequence[int], *, compute_dtype: str 
             # No exchange waits for its peers' "done" words by itself: nothing later in the step reads a working
             # copy or rewrites a gradient, so the last exchange of the step (layer 0's bias) is the one fence for all.
             outs = [W[i], mW[i], vW[i]] + ([Wlp[i]] if mixed else [])
-            op("dp_adam_step", [W[i], dW[i], mW[i], vW[i], step], outs, dict(hyper, slot=2 * i, defer_done=True),
+            # layer 0's exchange is the last work of the step: no GEMM is left to share the SMs with ("solo")
+            op("dp_adam_step", [W[i], dW[i], mW[i], vW[i], step], outs, dict(hyper, slot=2 * i, defer_done=True, solo=(i == 0)),
                "dp_adam_step_f32_p2p_v0")
-            fence = {"fence_slots": 2 * L} if i == 0 else {"defer_done": True}
+            fence = {"fence_slots": 2 * L, "solo": True} if i == 0 else {"defer_done": True}
             op("dp_adam_step", [b[i], db[i], mb[i], vb[i], step], [b[i], mb[i], vb[i]], dict(hyper, slot=2 * i + 1, **fence),
                "dp_adam_step_f32_p2p_v0")
     if fused_dp:

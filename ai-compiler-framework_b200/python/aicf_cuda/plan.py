@@ -71,10 +71,11 @@ def pack_attrs(op: str, attrs: Optional[Dict[str, Any]]) -> Tuple[int, bytes]:
         payload = struct.pack("<fffffIi", float(a.get("lr", 1e-3)), float(a.get("beta1", 0.9)),
                               float(a.get("beta2", 0.999)), float(a.get("eps", 1e-8)),
                               float(a.get("weight_decay", 0.0)), 1 if a.get("decoupled", False) else 0, int(a["slot"]))
-        if a.get("defer_done") or a.get("fence_slots"):
+        if a.get("defer_done") or a.get("fence_slots") or a.get("solo"):
             # defer_done: this op does not wait for the peers' "done" words; fence_slots = n: this op (the last
-            # exchange of the step) waits for the done words of slots [0, n) before it finishes
-            payload += struct.pack("<ii", 1 if a.get("defer_done") else 0, int(a.get("fence_slots", 0)))
+            # exchange of the step) waits for the done words of slots [0, n) before it finishes; solo: nothing runs
+            # beside this op, so it may fill the SMs instead of leaving room for GEMM CTAs
+            payload += struct.pack("<ii", (1 if a.get("defer_done") else 0) | (2 if a.get("solo") else 0), int(a.get("fence_slots", 0)))
         return SCHEMA_DP_ADAM, payload
     if op == "bias_corr":
         return SCHEMA_BIAS_CORR, struct.pack("<ff", float(a.get("beta1", 0.9)), float(a.get("beta2", 0.999)))

@@ -218,9 +218,11 @@ int aicf_b200_plan_bind(aicf_plan* plan, int vid, void* device_ptr);
  * (handles = world x 64 bytes in rank order; the own entry is ignored). One process per GPU.
  * Attrs of a dp_adam_step op: schema 'DPAD' (0x44415044), payload <fffffIi> lr, beta1, beta2, eps, weight_decay,
  * decoupled, slot (index of the op's flag block, unique per op of a plan, < 60), optionally followed by <ii>
- * defer_done, fence_slots. defer_done = 1: the op does not wait for the other ranks' "my stores into your memory are
- * done" words; the plan must then end the step with a dp_adam_step op carrying fence_slots = n, which waits for
- * those words of slots [0, n) before it completes. Without the two optional fields every op waits for itself.
+ * flags, fence_slots. flags bit 0 (defer_done): the op does not wait for the other ranks' "my stores into your memory
+ * are done" words; the plan must then end the step with a dp_adam_step op carrying fence_slots = n, which waits for
+ * those words of slots [0, n) before it completes. flags bit 1 (solo): no other kernel runs beside this op, so it
+ * may take two CTAs per SM instead of leaving room for a co-resident GEMM. Without the two optional fields every op
+ * waits for itself and leaves that room.
  * After a non-zero aicf_b200_wait_status (bits 17-18) the replicas are no longer known to agree: restore the model
  * and optimizer state from a checkpoint before training on. */
 int aicf_b200_plan_set_peer_visible(aicf_plan* plan, int vid);

@@ -121,3 +121,36 @@ def test_sharding_rule_and_lowering_shape():
     assert ce["attrs"]["scale"] == 1.0 / 65536
     params = sum(int(np.prod(v.shape)) for v in vals if v.role == 1)
     assert params == 276_661_224
+
+
+# ---- bench.py host logic: every N trains on the same global batch; the host arm is a fraction of one step ----------------
+def test_bench_shards_are_slices_of_one_global_batch():
+    import bench
+    gb, d, classes = 64, 24, 10
+    full_x, full_y = np.empty((gb, d), np.float32), np.empty(gb, np.int32)
+    bench.fill_global_batch_rows(full_x, full_y, 0, gb, classes)
+    assert full_y.min() >= 0 and full_y.max() < classes and abs(float(full_x.mean())) < 0.2
+    for world in (2, 4, 8):
+        b = gb // world
+        for r in range(world):
+            x, y = np.empty((b, d), np.float32), np.empty(b, np.int32)
+            bench.fill_global_batch_rows(x, y, r * b, gb, classes)
+            assert np.array_equal(x, full_x[r * b:(r + 1) * b]) and np.array_equal(y, full_y[r * b:(r + 1) * b]), (world, r)
+
+
+def test_bench_host_arm_runs_a_fraction_of_a_step_without_the_cuda_library():
+    import subprocess
+    import sys
+    code = (
+        "import sys, json; sys.argv=['bench.py']; import bench\n"
+        "bench.MLP_DIMS, bench.MLP_GLOBAL_BATCH = [32, 48, 16], 4096\n"
+        "s = bench.CpuMlpSample(bench.MLP_DIMS, 512, bench.MLP_GLOBAL_BATCH)\n"
+        "t = s.step(); assert t > 0\n"
+        "want = sum(max(1, round(r * 512 / 4096)) * c for r, c in ((48, 32), (16, 48))) + sum(max(1, round(n * 512 / 4096)) for n in (48, 16))\n"
+        "assert s.opt_elements == want, (s.opt_elements, want)\n"
+        "assert not [l for l in open('/proc/self/maps') if 'libaicf_b200' in l], 'the host arm must not map the CUDA library'\n"
+        "a, b = bench.mlp_config([8, 4], 64, 2, 'fused', False), bench.mlp_config([8, 4], 64, 2, 'fused', False)\n"
+        "assert a == b and a['per_gpu_batch'] == 32\n"
+        "print('HOST_ARM_OK')\n")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=str(REPO), timeout=300)
+    assert r.returncode == 0 and "HOST_ARM_OK" in r.stdout, r.stdout + r.stderr

@@ -55,16 +55,21 @@ int dtype_code_from_name(const std::string& n) {
   return it == kByName.end() ? 0 : it->second;
 }
 
-// dtype objects seen so far (torch dtypes are singletons, aicf_cuda.Tensor carries interned short strings): the
-// string conversion happens once per object. The cache holds a reference, so an address is never reused while cached.
+// dtype objects seen so far (torch dtypes are singletons, aicf_cuda.Tensor carries short strings): the string
+// conversion happens once per object. The cache holds a reference, so an address is never reused while cached; the
+// map itself is never destroyed, because static destructors run after the interpreter is gone and dropping a
+// reference then would touch freed memory.
 int dtype_code(const py::handle& dtype) {
-  static std::unordered_map<PyObject*, std::pair<py::object, int>> cache;
-  auto it = cache.find(dtype.ptr());
-  if (it != cache.end()) return it->second.second;
+  static auto* cache = new std::unordered_map<PyObject*, int>();
+  auto it = cache->find(dtype.ptr());
+  if (it != cache->end()) return it->second;
   const std::string name = py::str(dtype);
   const int code = dtype_code_from_name(name);
   if (code == 0) throw std::runtime_error("dtype must be float16/bfloat16/float32/int32. got: dtype=" + name);
-  if (cache.size() < 64) cache.emplace(dtype.ptr(), std::make_pair(py::reinterpret_borrow<py::object>(dtype), code));
+  if (cache->size() < 64) {
+    Py_INCREF(dtype.ptr());  // kept for the life of the process
+    cache->emplace(dtype.ptr(), code);
+  }
   return code;
 }
 

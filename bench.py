@@ -926,7 +926,9 @@ KERNEL_SUITE = [("gemm_8192_bf16", "gemm", dict(size=8192)), ("gemm_4096_bf16", 
                 ("softmax_bf16", "softmax", dict(dtype="bf16")), ("softmax_ce_f32", "ce", {}),
                 ("reduce_sum_f32", "reduce", dict(dtype="f32", reduce_kind="sum")), ("adam_f32_2p28", "adam", {}),
                 # measured ceilings for the stream mixes above: 4 arrays read + 3 written (Adam), 1 + 1 (softmax, CE)
-                ("ceiling_4_reads_3_writes", "stream_mix", dict(rows=4, cols=3)), ("ceiling_1_read_1_write", "stream_mix", dict(rows=1, cols=1))]
+                # (launch shapes that measured best in a sweep of 1 / 2 / 4 packets in flight x 4 / 8 / 16 / 32 blocks per SM)
+                ("ceiling_4_reads_3_writes", "stream_mix", dict(rows=4, cols=3, probe=(1, 32))),
+                ("ceiling_1_read_1_write", "stream_mix", dict(rows=1, cols=1, probe=(4, 32)))]
 
 
 def run_kernel_suite(args):

@@ -108,3 +108,26 @@ def test_null_pointer_calls_fail_cleanly_without_a_device():
     assert lib.aicf_b200_last_error().decode() == "graph_end called but not capturing"
     assert lib.aicf_b200_graph_launch() == 1
     assert lib.aicf_b200_last_error().decode() == "graph_launch called but no captured graph exists"
+
+
+def test_binding_survives_interpreter_exit_with_cached_runtime_dtype_objects():
+    """The compiled module caches dtype objects it has seen. A dtype that is an ordinary run-time string (not an
+    interned constant) must not be released from a C++ static destructor after the interpreter is gone."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    repo = Path(__file__).resolve().parents[1]
+    code = (
+        "import sys; sys.path.insert(0, 'ai-compiler-framework_b200/python')\n"
+        "from aicf_cuda import _C\n"
+        "class T:\n"
+        "    def __init__(s, dt): s.dtype, s.shape = dt, (2, 2)\n"
+        "    def data_ptr(s): return 4096\n"
+        "    def stride(s): return (2, 1)\n"
+        "    def is_contiguous(s): return True\n"
+        "for dt in [''.join(['f', '3', '2']), ''.join(['b', 'f', '1', '6'])]:\n"
+        "    try: _C.launch_by_id('nope_v0', _C.OpKind.EltwiseRelu, [T(dt)], [T(dt)])\n"
+        "    except RuntimeError: pass\n"
+        "print('DONE')\n")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=str(repo), timeout=120)
+    assert r.returncode == 0 and "DONE" in r.stdout, f"exit code {r.returncode}\n{r.stderr[-500:]}"

@@ -7,6 +7,7 @@
 #include <atomic>
 #include <cstdint>
 #include <cstring>
+#include <type_traits>
 
 #include "aicf/backends/cuda/registry/attr_blob.hpp"
 #include "aicf/backends/cuda/registry/kernel_variant.hpp"
@@ -148,6 +149,48 @@ template <typename T> struct alignas(16) Pack16 {
   static constexpr int kN = 16 / sizeof(T);
   T v[kN];
 };
+
+// A packet to / from its kN floats. Same values as converting element by element (round to nearest even), but the
+// 16-bit types convert two elements per instruction: bf16 -> f32 is a shift or a mask of the 32-bit word,
+// f32 -> bf16 / f16 one cvt.rn.{bf16x2,f16x2}.f32 per pair. The 16-bit row kernels are bound by instruction issue,
+// not by HBM, so the conversions are where their time goes.
+template <typename T>
+__device__ __forceinline__ void unpack16(const Pack16<T>& p, float (&f)[Pack16<T>::kN]) {
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int e = 0; e < Pack16<T>::kN; ++e) f[e] = Cvt<T>::to_f(p.v[e]);
+  } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+  } else {
+    const __half2* h = reinterpret_cast<const __half2*>(&p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 t = __half22float2(h[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+}
+template <typename T>
+__device__ __forceinline__ void pack16(Pack16<T>& o, const float (&f)[Pack16<T>::kN]) {
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int e = 0; e < Pack16<T>::kN; ++e) o.v[e] = Cvt<T>::from_f(f[e]);
+  } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    __nv_bfloat162* w = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  } else {
+    __half2* w = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+  }
+}
 
 // Streaming (evict-first) 16-byte global accesses: data touched once should not displace L2 lines.
 template <typename T>

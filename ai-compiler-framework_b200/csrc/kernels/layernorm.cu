@@ -92,12 +92,9 @@ __global__ void __launch_bounds__(1024)
     for (int q = 0; q < kPackets; ++q) {
       const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
       if (pi < np) {
-        const PK p = srow[pi];
+        unpack16(srow[pi], f[q]);
 #pragma unroll
-        for (int e = 0; e < kN; ++e) {
-          f[q][e] = Cvt<T>::to_f(p.v[e]);
-          s += f[q][e];
-        }
+        for (int e = 0; e < kN; ++e) s += f[q][e];
       } else {
 #pragma unroll
         for (int e = 0; e < kN; ++e) f[q][e] = 0.0f;
@@ -139,14 +136,18 @@ __global__ void __launch_bounds__(1024)
       const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
       if (pi < np) {
         PK o;
+        float r[kN];
         if constexpr (kAffine) {
-          const PK g = ld_param(gamma, pi), b = ld_param(beta, pi);
+          float g[kN], b[kN];
+          unpack16(ld_param(gamma, pi), g);
+          unpack16(ld_param(beta, pi), b);
 #pragma unroll
-          for (int e = 0; e < kN; ++e) o.v[e] = Cvt<T>::from_f(fmaf(f[q][e] * rs, Cvt<T>::to_f(g.v[e]), Cvt<T>::to_f(b.v[e])));
+          for (int e = 0; e < kN; ++e) r[e] = fmaf(f[q][e] * rs, g[e], b[e]);
         } else {
 #pragma unroll
-          for (int e = 0; e < kN; ++e) o.v[e] = Cvt<T>::from_f(f[q][e] * rs);
+          for (int e = 0; e < kN; ++e) r[e] = f[q][e] * rs;
         }
+        pack16(o, r);
         st_stream(yr + pi, o);
       }
     }
@@ -429,13 +430,15 @@ bool ln_fwd_supported(const TensorDesc* in, int ni, const TensorDesc* out, int n
 }
 
 template <typename T, int kPackets>
-Status ln_fwd_go(bool affine, int grid, int threads, size_t smem, cudaStream_t stream, const T* x, const T* g, const T* b,
-                 T* y, float* mean, float* rstd, int64_t M, int64_t N, float eps) {
+Status ln_fwd_go(bool affine, int threads, size_t smem, cudaStream_t stream, const T* x, const T* g, const T* b, T* y,
+                 float* mean, float* rstd, int64_t M, int64_t N, float eps) {
   if (affine) {
     if (!allow_smem(ln_fwd_regs_kernel<T, kPackets, true>, smem)) return Status::Internal;
+    const int grid = streaming_grid(M, 1, row_blocks_per_sm(ln_fwd_regs_kernel<T, kPackets, true>, threads, smem));
     ln_fwd_regs_kernel<T, kPackets, true><<<grid, threads, smem, stream>>>(x, g, b, y, mean, rstd, M, N, eps);
   } else {
     if (!allow_smem(ln_fwd_regs_kernel<T, kPackets, false>, smem)) return Status::Internal;
+    const int grid = streaming_grid(M, 1, row_blocks_per_sm(ln_fwd_regs_kernel<T, kPackets, false>, threads, smem));
     ln_fwd_regs_kernel<T, kPackets, false><<<grid, threads, smem, stream>>>(x, g, b, y, mean, rstd, M, N, eps);
   }
   return launch_status();
@@ -464,12 +467,11 @@ Status ln_fwd_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, cons
     ln_fwd_multipass_kernel<T><<<streaming_grid(M, 1, 8), 256, 0, stream>>>(x, g, b, y, mean, rstd, M, N, eps);
     return launch_status();
   }
-  const int grid = streaming_grid(M, 1, row_pipe_blocks_per_sm(c.threads, smem));
   switch (c.packets) {
-    case 1: return ln_fwd_go<T, 1>(affine, grid, c.threads, smem, stream, x, g, b, y, mean, rstd, M, N, eps);
-    case 2: return ln_fwd_go<T, 2>(affine, grid, c.threads, smem, stream, x, g, b, y, mean, rstd, M, N, eps);
-    case 4: return ln_fwd_go<T, 4>(affine, grid, c.threads, smem, stream, x, g, b, y, mean, rstd, M, N, eps);
-    default: return ln_fwd_go<T, kMaxPk>(affine, grid, c.threads, smem, stream, x, g, b, y, mean, rstd, M, N, eps);
+    case 1: return ln_fwd_go<T, 1>(affine, c.threads, smem, stream, x, g, b, y, mean, rstd, M, N, eps);
+    case 2: return ln_fwd_go<T, 2>(affine, c.threads, smem, stream, x, g, b, y, mean, rstd, M, N, eps);
+    case 4: return ln_fwd_go<T, 4>(affine, c.threads, smem, stream, x, g, b, y, mean, rstd, M, N, eps);
+    default: return ln_fwd_go<T, kMaxPk>(affine, c.threads, smem, stream, x, g, b, y, mean, rstd, M, N, eps);
   }
 }
 

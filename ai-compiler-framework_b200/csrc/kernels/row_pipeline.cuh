@@ -1,6 +1,8 @@
 #pragma once
 // Building blocks of the row kernels (softmax, softmax cross-entropy, layer norm): a block owns one row at a
 // time, keeps it in registers, and prefetches its next row into shared memory with one bulk asynchronous copy.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "sm100_async.cuh"
 
@@ -124,6 +126,32 @@ inline int row_pipe_blocks_per_sm(int threads, size_t smem) {
 template <typename K>
 bool allow_smem(K kernel, size_t smem) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) == cudaSuccess;
+}
+
+// Blocks per SM the grid-stride row kernels are launched with. The default is the estimate above, which ignores
+// registers and therefore over-subscribes some shapes (a 256-thread block at 46 registers fits five times, not
+// eight): measured on [32768,4096] and [65536,1024], a grid of exactly the resident blocks was slower than the
+// over-subscribed one (bf16 softmax 5736 against 6425 GB/s, f32 cross-entropy on 1024 columns 5679 against 6376),
+// because blocks that start late run out of step with the first wave and smooth its read-then-write bursts.
+// AICF_ROW_BLOCKS_PER_SM (tuning, read once per process): a number forces that many, "occ" asks the runtime for the
+// resident count of this kernel at this block size and shared memory.
+template <typename K>
+int row_blocks_per_sm(K kernel, int threads, size_t smem) {
+  static const int forced = [] {
+    const char* e = std::getenv("AICF_ROW_BLOCKS_PER_SM");
+    if (e == nullptr || e[0] == 0) return 0;
+    if (e[0] == 'o') return -1;
+    const int v = std::atoi(e);
+    return v < 1 ? 0 : (v > 32 ? 32 : v);
+  }();
+  if (forced > 0) return forced;
+  if (forced == 0) return row_pipe_blocks_per_sm(threads, smem);
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem) != cudaSuccess || n < 1) {
+    cudaGetLastError();
+    return row_pipe_blocks_per_sm(threads, smem);
+  }
+  return n > 32 ? 32 : n;
 }
 
 }  // namespace aicf::cuda::rowk

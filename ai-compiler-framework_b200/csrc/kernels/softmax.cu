@@ -9,6 +9,8 @@
 // deterministic.
 // Rows wider than 32768 elements, or rows that are not 16-byte aligned, take a three-read fallback
 // kernel.
+#include <cstdlib>
+
 #include "row_pipeline.cuh"
 
 namespace aicf::cuda {
@@ -17,10 +19,20 @@ namespace {
 
 using namespace rowk;
 
-// exp for arguments <= 0: one multiply and one MUFU.EX2. Relative error <= |x| * 2^-24 + 2^-22, i.e. below
-// 1e-5 for every argument whose result is not already flushed to zero (x > -100); the accurate expf costs ~20
-// instructions per element, which for a 32000-wide row is more time than its HBM traffic.
-__device__ __forceinline__ float fast_exp(float x) { return __expf(x); }
+// exp(v - mx) for v <= mx: a subtraction, a multiply by log2(e) and one MUFU.EX2. Relative error <= |v - mx| * 2^-24
+// + 2^-22, i.e. below 1e-5 for every argument whose result is not already flushed to zero; the accurate expf costs
+// ~20 instructions per element, which for a 32000-wide row is more time than its HBM traffic. The subtraction comes
+// first on purpose: the row maximum itself then gives exp2(0) = 1 exactly, which a loss of the order of 1e-6 (a
+// confident, correct prediction: sum = 1 + a few e-6) depends on. Folding the shift into one fused multiply-add
+// (2^(v * log2(e) - mx * log2(e))) saves an instruction but puts the rounding of mx * log2(e), up to 1e-6, into
+// log(sum).
+constexpr float kLog2e = 1.4426950408889634f;
+__device__ __forceinline__ float exp2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float exp_shifted(float v, float mx) { return exp2_approx((v - mx) * kLog2e); }
 
 struct ArgMax {
   float v;
@@ -61,28 +73,38 @@ __device__ __forceinline__ ArgMax block_argmax(ArgMax a, float* sv /*[kMaxWarps 
   return ArgMax{sv[kMaxWarps], si[kMaxWarps]};
 }
 
-// Two-barrier form; the same alternation rule as block_reduce_2b applies to (sv, si).
-__device__ __forceinline__ ArgMax block_argmax_2b(ArgMax a, float* sv /*[kMaxWarps + 1]*/, int* si /*[kMaxWarps + 1]*/) {
+__device__ int g_row_pipeline_status = 0;  // non-zero: a bounded wait of the row pipeline expired
+
+// Block-wide sum of `s` and minimum of `idx` in one trip through shared memory. kLeadingBarrier as in block_reduce
+// (areas possibly still being read by the previous call) against block_reduce_2b (caller alternates areas).
+struct SumMin {
+  float sum;
+  int idx;
+};
+template <bool kLeadingBarrier>
+__device__ __forceinline__ SumMin block_sum_min(float s, int idx, float* sv /*[kMaxWarps + 1]*/, int* si /*[kMaxWarps + 1]*/) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  a = warp_argmax(a);
+  s = warp_sum(s);
+  idx = __reduce_min_sync(0xffffffffu, idx);
+  if (kLeadingBarrier) __syncthreads();
   if (lane == 0) {
-    sv[warp] = a.v;
-    si[warp] = a.idx;
+    sv[warp] = s;
+    si[warp] = idx;
   }
   __syncthreads();
   if (warp == 0) {
-    ArgMax r{lane < nwarps ? sv[lane] : -INFINITY, lane < nwarps ? si[lane] : 0x7fffffff};
-    r = warp_argmax(r);
+    float r = lane < nwarps ? sv[lane] : 0.0f;
+    int j = lane < nwarps ? si[lane] : 0x7fffffff;
+    r = warp_sum(r);
+    j = __reduce_min_sync(0xffffffffu, j);
     if (lane == 0) {
-      sv[kMaxWarps] = r.v;
-      si[kMaxWarps] = r.idx;
+      sv[kMaxWarps] = r;
+      si[kMaxWarps] = j;
     }
   }
   __syncthreads();
-  return ArgMax{sv[kMaxWarps], si[kMaxWarps]};
+  return SumMin{sv[kMaxWarps], si[kMaxWarps]};
 }
-
-__device__ int g_row_pipeline_status = 0;  // non-zero: a bounded wait of the row pipeline expired
 
 // ------------------------------------------------------------------ softmax, row in registers
 template <typename T, int kPackets>
@@ -109,12 +131,9 @@ __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict_
     for (int q = 0; q < kPackets; ++q) {
       const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
       if (pi < np) {
-        const PK p = srow[pi];
+        unpack16(srow[pi], f[q]);
 #pragma unroll
-        for (int e = 0; e < kN; ++e) {
-          f[q][e] = Cvt<T>::to_f(p.v[e]);
-          mx = fmaxf(mx, f[q][e]);
-        }
+        for (int e = 0; e < kN; ++e) mx = fmaxf(mx, f[q][e]);
       } else {
 #pragma unroll
         for (int e = 0; e < kN; ++e) f[q][e] = -INFINITY;
@@ -136,7 +155,7 @@ __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict_
     for (int q = 0; q < kPackets; ++q)
 #pragma unroll
       for (int e = 0; e < kN; ++e) {
-        f[q][e] = fast_exp(f[q][e] - mx);  // exp(-inf) == 0 for the padding
+        f[q][e] = exp_shifted(f[q][e], mx);  // exp(-inf) == 0 for the padding
         sum += f[q][e];
       }
     sum = block_reduce_2b<false>(sum, red[1]);
@@ -146,8 +165,10 @@ __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict_
       const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
       if (pi < np) {
         PK o;
+        float r[kN];
 #pragma unroll
-        for (int e = 0; e < kN; ++e) o.v[e] = Cvt<T>::from_f(f[q][e] * inv);
+        for (int e = 0; e < kN; ++e) r[e] = f[q][e] * inv;
+        pack16(o, r);
         st_stream(yr + pi, o);
       }
     }
@@ -185,11 +206,11 @@ Status softmax_run(const T* x, T* y, int64_t M, int64_t N, cudaStream_t stream) 
     softmax_multipass_kernel<T><<<streaming_grid(M, 1, 8), 256, 0, stream>>>(x, y, M, N);
     return launch_status();
   }
-  const int grid = streaming_grid(M, 1, row_pipe_blocks_per_sm(c.threads, smem));
   bool ok_attr = true;
-#define AICF_SM_LAUNCH(PK)                                           \
-  if ((ok_attr = allow_smem(softmax_regs_kernel<T, PK>, smem)))      \
-    softmax_regs_kernel<T, PK><<<grid, c.threads, smem, stream>>>(x, y, M, N)
+#define AICF_SM_LAUNCH(PK)                                                                                        \
+  if ((ok_attr = allow_smem(softmax_regs_kernel<T, PK>, smem)))                                                   \
+    softmax_regs_kernel<T, PK><<<streaming_grid(M, 1, row_blocks_per_sm(softmax_regs_kernel<T, PK>, c.threads, smem)), \
+                                 c.threads, smem, stream>>>(x, y, M, N)
   switch (c.packets) {
     case 1: AICF_SM_LAUNCH(1); break;
     case 2: AICF_SM_LAUNCH(2); break;
@@ -244,9 +265,11 @@ Status softmax_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, con
 // outputs [dlogits (B,C) same dtype, loss_row (B,) f32, argmax (B,) i32]   (argmax optional)
 //   loss_row = logsumexp(z) - z[label];  dlogits = (softmax(z) - onehot(label)) * scale
 // scale: 'SMCE' <f>, default 1/B. A label outside [0,C) contributes no one-hot term and a zero loss.
-// kLockstep: the wait for the row ends in a barrier and the reductions keep their leading barrier. With a single
-// 1024-thread block per SM (rows of tens of thousands of fp32 logits) that is measurably faster than the
-// two-barrier form, which wins whenever several blocks share an SM.
+// kLockstep: the wait for the row ends in a barrier and the reductions keep their leading barrier (an alternative
+// form kept for tuning, see the launcher; the two-barrier form is what runs).
+// Per element the loops only take a maximum, an exponential and a product: the arg-max index is looked up afterwards
+// by the few threads that hold the row maximum and reduced together with the sum, and the one-hot term is patched in
+// by the one thread that owns the label's column.
 template <typename T, int kPackets, bool kLockstep>
 __global__ void __launch_bounds__(1024)
     softmax_ce_regs_kernel(const T* __restrict__ z, const int32_t* __restrict__ labels, T* __restrict__ dz,
@@ -274,24 +297,22 @@ __global__ void __launch_bounds__(1024)
     PK* dr = reinterpret_cast<PK*>(dz + row * C);
     const int label = labels[row];
     const bool label_ok = label >= 0 && label < C;
-    float z_label = 0.0f;  // only thread 0 needs it
-    if (threadIdx.x == 0 && label_ok) z_label = Cvt<T>::to_f(reinterpret_cast<const T*>(row_smem)[label]);
+    // The thread whose packets hold column `label` patches the one-hot term after its stores (same thread, same
+    // address: ordered), so the element loops carry no per-element column compare. It and thread 0 (loss) read the
+    // label's logit while the row is still in shared memory.
+    const int owner = label_ok ? static_cast<int>((label / kN) % static_cast<int>(blockDim.x)) : -1;
+    float z_label = 0.0f;
+    if (label_ok && (threadIdx.x == 0 || static_cast<int>(threadIdx.x) == owner))
+      z_label = Cvt<T>::to_f(reinterpret_cast<const T*>(row_smem)[label]);
     float f[kPackets][kN];
-    ArgMax am{-INFINITY, 0x7fffffff};
+    float tmax = -INFINITY;
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
       const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
       if (pi < np) {
-        const PK p = srow[pi];
+        unpack16(srow[pi], f[q]);
 #pragma unroll
-        for (int e = 0; e < kN; ++e) {
-          const float v = Cvt<T>::to_f(p.v[e]);
-          f[q][e] = v;
-          if (v > am.v) {  // columns are visited in increasing order per thread: strict > keeps the lowest
-            am.v = v;
-            am.idx = static_cast<int>(pi) * kN + e;
-          }
-        }
+        for (int e = 0; e < kN; ++e) tmax = fmaxf(tmax, f[q][e]);
       } else {
 #pragma unroll
         for (int e = 0; e < kN; ++e) f[q][e] = -INFINITY;
@@ -299,7 +320,7 @@ __global__ void __launch_bounds__(1024)
     }
     // past the barriers of the reduction every thread holds its part of the row (the buffer may be refilled), and a
     // wait that ran out is seen by all threads
-    am = kLockstep ? block_argmax(am, red[0], redi) : block_argmax_2b(am, red[0], redi);
+    const float mx = kLockstep ? block_reduce<true>(tmax, red[0]) : block_reduce_2b<true>(tmax, red[0]);
     if (wait_failed) {
       if (threadIdx.x == 0) atomicExch(&g_row_pipeline_status, 1);
       break;
@@ -308,35 +329,50 @@ __global__ void __launch_bounds__(1024)
       sm100::fence_generic_to_async_smem();
       pipe.fetch(z + (row + gridDim.x) * C, row_bytes);
     }
-    const float mx = am.v;
+    // arg-max: only the (few) threads that hold the row maximum look for its lowest column among their elements;
+    // the block-wide minimum of those candidates rides along with the sum reduction below
+    int cand = 0x7fffffff;
+    if (tmax == mx) {
+#pragma unroll
+      for (int q = kPackets - 1; q >= 0; --q) {
+        const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
+        if (pi < np) {
+#pragma unroll
+          for (int e = kN - 1; e >= 0; --e)
+            if (f[q][e] == mx) cand = static_cast<int>(pi) * kN + e;  // descending order: the lowest column stays
+        }
+      }
+    }
     float sum = 0.0f;
 #pragma unroll
     for (int q = 0; q < kPackets; ++q)
 #pragma unroll
       for (int e = 0; e < kN; ++e) {
-        f[q][e] = fast_exp(f[q][e] - mx);
+        f[q][e] = exp_shifted(f[q][e], mx);
         sum += f[q][e];
       }
-    sum = kLockstep ? block_reduce<false>(sum, red[1]) : block_reduce_2b<false>(sum, red[1]);
+    const SumMin sm = block_sum_min<kLockstep>(sum, cand, red[1], redi);
+    sum = sm.sum;
     const float k = scale / sum;
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
       const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
       if (pi < np) {
         PK o;
+        float r[kN];
 #pragma unroll
-        for (int e = 0; e < kN; ++e) {
-          const int col = static_cast<int>(pi) * kN + e;
-          float g = f[q][e] * k;
-          if (col == label) g -= scale;
-          o.v[e] = Cvt<T>::from_f(g);
-        }
+        for (int e = 0; e < kN; ++e) r[e] = f[q][e] * k;
+        pack16(o, r);
         st_stream(dr + pi, o);
       }
     }
+    if (static_cast<int>(threadIdx.x) == owner) {
+      const float g = exp_shifted(z_label, mx) * k - scale;  // the same bits the loop above produced, minus the one-hot term
+      dz[row * C + label] = Cvt<T>::from_f(g);
+    }
     if (threadIdx.x == 0) {
       loss_row[row] = label_ok ? (logf(sum) + mx - z_label) : 0.0f;
-      if (argmax_out) argmax_out[row] = am.idx;
+      if (argmax_out) argmax_out[row] = sm.idx;
     }
   }
 }
@@ -422,12 +458,18 @@ Status softmax_ce_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, 
     return launch_status();
   }
   bool ok_attr = true;
-  const int per_sm = row_pipe_blocks_per_sm(c.threads, smem);
-  const bool lockstep = per_sm == 1;
-  const int grid = streaming_grid(B, 1, per_sm);
-#define AICF_CE_LAUNCH_M(PK, LS)                                                                          \
-  if ((ok_attr = allow_smem(softmax_ce_regs_kernel<T, PK, LS>, smem)))                                    \
-    softmax_ce_regs_kernel<T, PK, LS><<<grid, c.threads, smem, stream>>>(z, lab, dz, loss, am, B, C, scale)
+  // The two-barrier form is the default everywhere. AICF_CE_LOCKSTEP=1 selects the lockstep form (tuning; read once
+  // per process): it used to win for one 1024-thread block per SM, and lost that once the per-element arg-max and
+  // one-hot work left the loops ([8192,32000] f32: 6396 GB/s against 5612 in lockstep).
+  static const bool lockstep = [] {
+    const char* e = std::getenv("AICF_CE_LOCKSTEP");
+    return e != nullptr && e[0] == '1';
+  }();
+#define AICF_CE_LAUNCH_M(PK, LS)                                                                                     \
+  if ((ok_attr = allow_smem(softmax_ce_regs_kernel<T, PK, LS>, smem)))                                               \
+    softmax_ce_regs_kernel<T, PK, LS>                                                                                \
+        <<<streaming_grid(B, 1, row_blocks_per_sm(softmax_ce_regs_kernel<T, PK, LS>, c.threads, smem)), c.threads, \
+           smem, stream>>>(z, lab, dz, loss, am, B, C, scale)
 #define AICF_CE_LAUNCH(PK)                          \
   if (lockstep) { AICF_CE_LAUNCH_M(PK, true); }     \
   else { AICF_CE_LAUNCH_M(PK, false); }

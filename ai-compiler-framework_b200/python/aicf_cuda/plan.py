@@ -8,9 +8,7 @@ CUDA graph live in C++: Python only describes the lowered-op list once.
 from __future__ import annotations
 
 import ctypes as C
-import re
 import struct
-from dataclasses import dataclass, field
 from typing import Any, Dict, Iterable, List, Optional, Sequence, Tuple
 
 from ._lib import check, lib

@@ -349,6 +349,10 @@ int aicf_b200_device_info(int device, int64_t* l2_bytes, int* sm_count, int64_t*
   }
   return AICF_OK;
 }
+int aicf_b200_device_pci_bus_id(int device, char* out, int capacity) {
+  if (!out || capacity < 13) return fail(Status::InvalidArgument, "device_pci_bus_id: need a buffer of at least 13 bytes");
+  return check_cuda(cudaDeviceGetPCIBusId(out, capacity, device), "cudaDeviceGetPCIBusId");
+}
 int aicf_b200_stream_probe(int reads, int writes, const void* const* inputs, void* const* outputs, size_t bytes_each,
                            int packets_in_flight, int blocks_per_sm, aicf_stream stream) {
   const Status st = aicf::cuda::stream_probe(reads, writes, inputs, outputs, bytes_each, packets_in_flight, blocks_per_sm,

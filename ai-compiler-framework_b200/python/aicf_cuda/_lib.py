@@ -80,6 +80,7 @@ PROTOTYPES = {
     "aicf_b200_graph_stream": (_u64, []),
     "aicf_b200_device_count": (_i, []),
     "aicf_b200_set_device": (_i, [_i]),
+    "aicf_b200_device_pci_bus_id": (_i, [_i, C.c_char_p, _i]),
     "aicf_b200_device_info": (_i, [_i, _P(C.c_int64), _P(C.c_int), _P(C.c_int64)]),
     "aicf_b200_stream_probe": (_i, [_i, _i, _P(_vp), _P(_vp), _sz, _i, _i, _u64]),
     "aicf_b200_malloc": (_i, [_P(_vp), _sz]),

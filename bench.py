@@ -361,6 +361,12 @@ def run_mlp(args, dist: Dist):
     gbatch = SMALL_MLP_BATCH if args.small else MLP_GLOBAL_BATCH
     batch = gbatch // world
     aicf_cuda._lib.check(lib.aicf_b200_set_device(local_rank), "set_device")
+    # N > 1: this rank's threads, and the pinned staging buffers allocated below, stay on the NUMA node of its GPU.
+    # At N = 1 the process keeps every core (the host arm of the same run uses them all).
+    host_affinity = None
+    if world > 1:
+        from aicf_cuda import hostmem
+        host_affinity = hostmem.bind_to_device_node(local_rank)
     if world > 1 and args.dp_mode == "nccl":
         from aicf_cuda import dp
         # NCCL prints its version banner on stdout at communicator creation; stdout carries the one JSON line only,
@@ -482,7 +488,8 @@ def run_mlp(args, dist: Dist):
             "e2e": {"value": gbatch / (e2e_ms / e2e_steps * 1e-3), "unit": "samples/s",
                     "h2d_bytes_per_step": int(x_host.nbytes + y_host.nbytes), "d2h_bytes_per_step": 4, "steps": e2e_steps,
                     "note": "every step: pinned host X (fp32) + labels copied in on a copy stream (double-buffered, overlaps the "
-                            "previous replay), one graph replay, loss copied out and read by the host"},
+                            "previous replay), one graph replay, loss copied out and read by the host",
+                    "host_affinity": host_affinity},
             "gpu_launches": graph_kernels * args.steps,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None,

@@ -156,6 +156,10 @@ int aicf_b200_set_device(int device);
 /* Facts about a device that sizing decisions and benchmark reports need: L2 cache bytes, SM count, total global
  * memory bytes (any pointer may be NULL). What a torch user reads from torch.cuda.get_device_properties. */
 int aicf_b200_device_info(int device, int64_t* l2_bytes, int* sm_count, int64_t* total_bytes);
+/* PCI address of a device as "dddd:bb:dd.f" (NUL-terminated; capacity >= 13). A one-process-per-GPU job uses it to
+ * find the host NUMA node the device hangs off (sysfs numa_node of that address) and to keep its pinned staging
+ * buffers and copy-issuing threads there. No counterpart in the reference (single device, torch owns host memory). */
+int aicf_b200_device_pci_bus_id(int device, char* out, int capacity);
 /* Measuring aid: a minimal streaming kernel that reads `reads` (1-4) arrays and writes `writes` (1-3) arrays of
  * bytes_each bytes (16-byte aligned, multiple of 16) with 16-byte evict-first accesses - the bandwidth ceiling of this
  * device for a kernel with that mix of input and output streams (fused Adam: 4 + 3), which a plain copy's rate

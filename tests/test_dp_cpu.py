@@ -154,3 +154,55 @@ def test_bench_host_arm_runs_a_fraction_of_a_step_without_the_cuda_library():
         "print('HOST_ARM_OK')\n")
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=str(REPO), timeout=300)
     assert r.returncode == 0 and "HOST_ARM_OK" in r.stdout, r.stdout + r.stderr
+
+
+# ------------------------------------------------------------------ host placement (fake sysfs, no GPU)
+def _fake_sysfs(tmp_path, bus_id="0000:1b:00.0", node="1", cpulists=("0-3", "4-7")):
+    d = tmp_path / "bus" / "pci" / "devices" / bus_id
+    d.mkdir(parents=True)
+    (d / "numa_node").write_text(node + "\n")
+    for i, cl in enumerate(cpulists):
+        n = tmp_path / "devices" / "system" / "node" / f"node{i}"
+        n.mkdir(parents=True)
+        (n / "cpulist").write_text(cl + "\n")
+    return tmp_path
+
+
+def test_cpulist_parsing():
+    from aicf_cuda import hostmem
+    assert hostmem.parse_cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    assert hostmem.parse_cpulist("") == []
+    assert hostmem.parse_cpulist("5") == [5]
+    with pytest.raises(ValueError):
+        hostmem.parse_cpulist("7-3")
+
+
+def test_rank_is_bound_to_the_cpus_of_its_gpus_node(tmp_path, monkeypatch):
+    from aicf_cuda import hostmem
+    monkeypatch.delenv("AICF_HOST_AFFINITY", raising=False)
+    sysfs = _fake_sysfs(tmp_path)
+    calls = []
+    info = hostmem.bind_to_device_node(3, bus_id="0000:1B:00.0", sysfs=sysfs, setaffinity=lambda pid, cpus: calls.append((pid, list(cpus))),
+                                       allowed={0, 1, 4, 5, 6})
+    assert info["bound"] and info["numa_node"] == 1 and info["cpus"] == 3
+    assert calls == [(0, [4, 5, 6])]  # node 1's CPUs, minus the one the process may not use
+
+
+def test_binding_declines_and_says_why(tmp_path, monkeypatch):
+    from aicf_cuda import hostmem
+    monkeypatch.delenv("AICF_HOST_AFFINITY", raising=False)
+    never = lambda pid, cpus: pytest.fail("must not bind")
+    # the host reports no node (-1)
+    info = hostmem.bind_to_device_node(0, bus_id="0000:1b:00.0", sysfs=_fake_sysfs(tmp_path / "a", node="-1"), setaffinity=never,
+                                       allowed={0, 1})
+    assert not info["bound"] and "no NUMA node" in info["why_not"]
+    # unknown device address
+    info = hostmem.bind_to_device_node(0, bus_id="0000:ff:00.0", sysfs=_fake_sysfs(tmp_path / "b"), setaffinity=never, allowed={0})
+    assert not info["bound"] and "no NUMA node" in info["why_not"]
+    # none of the node's CPUs is allowed (a container's cpuset)
+    info = hostmem.bind_to_device_node(0, bus_id="0000:1b:00.0", sysfs=_fake_sysfs(tmp_path / "c"), setaffinity=never, allowed={0, 1})
+    assert not info["bound"] and "no CPU" in info["why_not"]
+    # switched off
+    monkeypatch.setenv("AICF_HOST_AFFINITY", "0")
+    info = hostmem.bind_to_device_node(0, bus_id="0000:1b:00.0", sysfs=_fake_sysfs(tmp_path / "d"), setaffinity=never, allowed={4})
+    assert not info["bound"] and info["why_not"] == "AICF_HOST_AFFINITY=0"

@@ -15,6 +15,7 @@ int row_pipeline_status(bool clear);
 int layernorm_pipeline_status(bool clear);
 int adam_pipeline_status(bool clear);
 int gemm_tcgen05_timeline(int enable, unsigned long long* out16);
+void gemm_reload_env_overrides();
 int dp_wait_status(bool clear);
 Status stream_probe(int reads, int writes, const void* const* in, void* const* out, size_t bytes, int in_flight,
                     int blocks_per_sm, cudaStream_t stream);
@@ -237,6 +238,10 @@ const char* aicf_b200_kernel_id(int op_kind, int index) {
   return v[static_cast<size_t>(index)]->kernel_id;  // string literals: stable for the process lifetime
 }
 
+int aicf_b200_gemm_reload_tuning(void) {
+  aicf::cuda::gemm_reload_env_overrides();
+  return AICF_OK;
+}
 int aicf_b200_gemm_status(int clear) { return aicf::cuda::gemm_tcgen05_status(clear != 0); }
 int aicf_b200_gemm_timeline(int enable, uint64_t* out16) {
   return aicf::cuda::gemm_tcgen05_timeline(enable, reinterpret_cast<unsigned long long*>(out16)) == 0 ? AICF_OK : AICF_INTERNAL;

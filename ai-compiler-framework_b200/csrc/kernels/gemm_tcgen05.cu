@@ -1224,7 +1224,8 @@ struct GemmChoice {
 // added in split order by splitk_finish_kernel (deterministic). Considered only when it is predicted to win and each
 // part keeps at least 8 k blocks.
 // AICF_GEMM_CTA_GROUP=1|2, AICF_GEMM_TILE_N=256|128|64 and AICF_GEMM_SPLITK=<n> (0 or 1 = off) override the choice
-// (tuning and tests). The environment is read once, at the first GEMM of the process.
+// (tuning and tests). The environment is read at the first GEMM of the process, not on every launch;
+// gemm_reload_env_overrides() reads it again (a test or a sweep that changes a setting inside one process).
 struct GemmEnvOverrides {
   int cta_group = 0;  // 0 = no override
   int tile_n = 0;
@@ -1235,8 +1236,8 @@ struct GemmEnvOverrides {
   int ab_hint = -1;   // AICF_GEMM_AB_HINT: bit mask, see GemmParams (-1 = default)
   int tail_halves = -1;  // AICF_GEMM_TAIL_HALVES: 0 / 1 (-1 = default, on)
 };
-const GemmEnvOverrides& gemm_env_overrides() {
-  static const GemmEnvOverrides env = [] {
+GemmEnvOverrides read_gemm_env() {
+  {
     GemmEnvOverrides e;
     if (const char* s = std::getenv("AICF_GEMM_CTA_GROUP")) e.cta_group = s[0] == '1' ? 1 : s[0] == '2' ? 2 : 0;
     if (const char* s = std::getenv("AICF_GEMM_TILE_N")) e.tile_n = std::atoi(s);
@@ -1246,8 +1247,19 @@ const GemmEnvOverrides& gemm_env_overrides() {
     if (const char* s = std::getenv("AICF_GEMM_AB_HINT")) e.ab_hint = std::atoi(s);
     if (const char* s = std::getenv("AICF_GEMM_TAIL_HALVES")) e.tail_halves = std::atoi(s);
     return e;
-  }();
-  return env;
+  }
+}
+// The current settings. A reload publishes a new object and leaves the old one allocated: a launch on another thread
+// may still be reading it, and reloads happen a handful of times in a test run.
+std::atomic<const GemmEnvOverrides*> g_gemm_env{nullptr};
+const GemmEnvOverrides& gemm_env_overrides() {
+  const GemmEnvOverrides* e = g_gemm_env.load(std::memory_order_acquire);
+  if (e == nullptr) {
+    const GemmEnvOverrides* fresh = new GemmEnvOverrides(read_gemm_env());
+    if (g_gemm_env.compare_exchange_strong(e, fresh, std::memory_order_acq_rel)) return *fresh;
+    delete fresh;  // another thread published first
+  }
+  return *e;
 }
 
 GemmChoice choose_gemm(const GemmProblem& p) {
@@ -1609,6 +1621,10 @@ Status gemm_tf32x3_run(const GemmProblem& p, void* ws, size_t ws_bytes, cudaStre
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
   gemm_tf32x3_kernel<<<grid, kThreads, k3SmemBytes, stream>>>(mahi, malo, mbhi, mblo, g);
   return launch_status();
+}
+
+void gemm_reload_env_overrides() {
+  g_gemm_env.store(new GemmEnvOverrides(read_gemm_env()), std::memory_order_release);
 }
 
 // Reads (and optionally clears) the device status word written by a GEMM that gave up waiting.

@@ -64,6 +64,7 @@ PROTOTYPES = {
     "aicf_b200_kernel_id": (_cp, [_i, _i]),
     "aicf_b200_num_op_kinds": (_i, []),
     "aicf_b200_gemm_status": (_i, [_i]),
+    "aicf_b200_gemm_reload_tuning": (_i, []),
     "aicf_b200_wait_status": (_i, [_i]),
     "aicf_b200_gemm_timeline": (_i, [_i, _P(C.c_uint64)]),
     "aicf_b200_colsum_f32_noalloc": (_i, [_vp, _vp, C.c_int64, C.c_int64, _u64]),

@@ -104,6 +104,10 @@ int aicf_b200_wait_status(int clear);
  * end, then wait and busy totals per role and the tile count), then switches recording on or off. out16 may be NULL.
  * Synchronises the device. No counterpart in the reference. */
 int aicf_b200_gemm_timeline(int enable, uint64_t* out16);
+/* The tcgen05 GEMM reads its tuning overrides (environment variables AICF_GEMM_CTA_GROUP, _TILE_N, _SPLITK, _GROUP_M,
+ * _C_STREAM, _AB_HINT, _TAIL_HALVES) at the first GEMM of the process, not on every launch. This reads them again: for a
+ * test or a tuning sweep that changes a setting inside one process. No counterpart in the reference. */
+int aicf_b200_gemm_reload_tuning(void);
 
 /* Column sum [rows, cols] -> [cols] (fp32, row-major, contiguous) for callers that must not allocate
  * device memory: a host that was given a fixed memory budget up front, or code that runs where the

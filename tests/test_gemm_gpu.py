@@ -10,7 +10,7 @@ import pytest
 import oracle
 from aicf_cuda import _C, Tensor
 from aicf_cuda._C import OpKind
-from util import by_id, dev, host, op_call, rel_err
+from util import by_id, dev, gemm_tuning, host, op_call, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -36,14 +36,12 @@ EPI_KID = {("bf16", "bf16"): "gemm_bias_relu_bf16_tcgen05_out_bf16_v0", ("bf16",
 TOL = {"bf16": 2e-2, "f16": 2e-2, "f32": 1e-5}
 
 @pytest.fixture(params=["1:256", "1:128", "1:64", "2"], ids=["cta1_n256", "cta1_n128", "cta1_n64", "cta2"])
-def cta_group(request, monkeypatch):
+def cta_group(request):
     """Runs a test with one CTA per tile at each tile width (256, 128, 64 columns) and with CTA pairs (tcgen05
     cta_group::2); without the overrides the launcher picks by tile count."""
     group, _, width = request.param.partition(":")
-    monkeypatch.setenv("AICF_GEMM_CTA_GROUP", group)
-    if width:
-        monkeypatch.setenv("AICF_GEMM_TILE_N", width)
-    return request.param
+    with gemm_tuning(cta_group=group, tile_n=width or None):
+        yield request.param
 
 
 SHAPES = [(64, 80, 48), (128, 256, 64), (256, 512, 128), (200, 304, 136), (1, 8, 8), (129, 257, 72), (384, 1000, 512),
@@ -230,17 +228,16 @@ def test_gemm_f32_3xtf32_4096_sampled_rows(gpu):
 
 # ------------------------------------------------------------------ split-K (few tiles, long K)
 @pytest.fixture(params=["auto", "3", "8"], ids=["split_auto", "split3", "split8"])
-def splitk(request, monkeypatch):
+def splitk(request):
     """The launcher's own choice, and forced part counts (3 leaves a ragged last part)."""
-    if request.param != "auto":
-        monkeypatch.setenv("AICF_GEMM_SPLITK", request.param)
-    return request.param
+    with gemm_tuning(splitk=None if request.param == "auto" else request.param):
+        yield request.param
 
 
 @pytest.mark.parametrize("M,N,K", [(16, 512, 4096), (128, 1024, 8192), (200, 768, 4104), (64, 1000, 5000), (1, 256, 4096)])
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
 @pytest.mark.parametrize("dt,out", [("bf16", "bf16"), ("bf16", "f32"), ("f16", "f16")])
-def test_gemm_split_over_k(gpu, splitk, monkeypatch, M, N, K, ta, tb, dt, out):
+def test_gemm_split_over_k(gpu, splitk, M, N, K, ta, tb, dt, out):
     if ta and M % 8:
         pytest.skip("a transposed A needs 16-byte aligned columns on the tensor-core path")
     A, B, bias, sa, sb = _operands(M, N, K, ta, tb, dt)
@@ -255,26 +252,95 @@ def test_gemm_split_over_k(gpu, splitk, monkeypatch, M, N, K, ta, tb, dt, out):
             by_id(EPI_KID[(dt, out)], OpKind.GemmEpilogue, [X, W, Bv], [C], GPEL, struct.pack("<iii", ta, tb, relu))
             assert rel_err(host(C), oracle.gemm_epilogue(A, B, bias, False, False, bool(relu))) <= TOL[dt]
     # the unsplit kernel on the same operands: same product up to the order of the fp32 additions
-    monkeypatch.setenv("AICF_GEMM_SPLITK", "0")
-    by_id(GEMM_KID[(dt, out)], OpKind.Gemm, [X, W], [C], GEMM, struct.pack("<ii", ta, tb))
+    with gemm_tuning(splitk="0"):
+        by_id(GEMM_KID[(dt, out)], OpKind.Gemm, [X, W], [C], GEMM, struct.pack("<ii", ta, tb))
     scale = float(np.abs(want).max())
     assert np.abs(host(C) - split_result).max() <= (2e-5 if out == "f32" else 1e-2) * scale
     assert _C.gemm_status() == 0
 
 
-def test_gemm_split_over_k_with_relu_backward_mask_and_determinism(gpu, monkeypatch):
+def test_gemm_split_over_k_with_relu_backward_mask_and_determinism(gpu):
     M, N, K = 96, 512, 4096
     A, B, bias, sa, sb = _operands(M, N, K, 0, 0, "bf16")
     Y = oracle.bf16_round(np.random.default_rng(5).standard_normal((M, N)).astype(np.float32))
     want = oracle.gemm_relu_bwd(A, B, Y)
     outs = []
     for force in ("4", "4", "0"):
-        monkeypatch.setenv("AICF_GEMM_SPLITK", force)
         C = Tensor.zeros((M, N), "bf16")
-        by_id("gemm_relu_bwd_bf16_tcgen05_out_bf16_v0", OpKind.GemmReluBwd, [dev(sa, "bf16"), dev(sb, "bf16"), dev(Y, "bf16")], [C],
-              GEMM, struct.pack("<ii", 0, 0))
+        with gemm_tuning(splitk=force):
+            by_id("gemm_relu_bwd_bf16_tcgen05_out_bf16_v0", OpKind.GemmReluBwd, [dev(sa, "bf16"), dev(sb, "bf16"), dev(Y, "bf16")],
+                  [C], GEMM, struct.pack("<ii", 0, 0))
         assert rel_err(host(C), want) <= TOL["bf16"]
         assert np.array_equal(host(C) == 0, ~(Y > 0) | (host(C) == 0))
         outs.append(host(C))
     assert np.array_equal(outs[0], outs[1]), "parts are added in a fixed order"
     assert _C.gemm_status() == 0
+
+
+# ------------------------------------------------------------------ last round of the paired kernel
+def _sm_count():
+    import ctypes as C
+    import aicf_cuda
+    sms = C.c_int(0)
+    assert aicf_cuda.lib.aicf_b200_device_info(0, None, C.byref(sms), None) == 0
+    return sms.value
+
+
+def _gemm_workspace(kid, kind, ins, payload, schema):
+    import aicf_cuda
+    from aicf_cuda._C_ctypes import _blob, _build_descs
+    descs = _build_descs(ins, "x")[0]
+    blob, _keep = _blob(schema, payload)
+    return aicf_cuda.lib.aicf_b200_query_workspace(kid.encode(), int(kind), descs, len(ins), blob)
+
+
+def test_tuning_overrides_are_live_after_a_reload(gpu):
+    """The launcher reads AICF_GEMM_* once per process; the tests' overrides only mean something because
+    gemm_tuning() asks for a re-read. Observable through the workspace a shape asks for: a small batch against a long K
+    is split over K (workspace for the parts) unless the split is switched off."""
+    X, W = Tensor.empty((64, 4096), "bf16"), Tensor.empty((4096, 1024), "bf16")
+    args = ("gemm_bf16_tcgen05_out_bf16_v0", OpKind.Gemm, [X, W], struct.pack("<ii", 0, 0), GEMM)
+    assert _gemm_workspace(*args) > 0
+    with gemm_tuning(splitk="0"):
+        assert _gemm_workspace(*args) == 0
+        with gemm_tuning(splitk="4", cta_group="1", tile_n="256"):
+            assert _gemm_workspace(*args) == 4 * 64 * 1024 * 4
+        assert _gemm_workspace(*args) == 0
+    assert _gemm_workspace(*args) > 0
+
+
+@pytest.mark.parametrize("rows_cut,cols_cut", [(0, 0), (60, 24)], ids=["whole_tiles", "ragged_edges"])
+@pytest.mark.parametrize("K,tb", [(256, 1), (1088, 1), (1088, 0)])
+def test_pair_kernel_tail_round_as_column_halves(gpu, K, tb, rows_cut, cols_cut):
+    """One more round than the clusters can fill, with at most half of them busy: each left-over 256x256 tile is done as
+    two 256x128 column halves on two clusters. Against fp64, and bit for bit against the same launch with the tail
+    tiles left whole (every output element is still one accumulator over the same k order)."""
+    clusters = _sm_count() // 2
+    extra = max(1, min(6, clusters // 2))
+    total = clusters + extra
+    cols_t = 8 if total % 8 == 0 else 4 if total % 4 == 0 else 2 if total % 2 == 0 else 1
+    M, N = total // cols_t * 256 - rows_cut, cols_t * 256 - cols_cut
+    A, B, bias, sa, sb = _operands(M, N, K, 0, tb, "bf16", seed=11)
+    X, W, Bv = dev(sa, "bf16"), dev(sb, "bf16"), dev(bias)
+    kid, payload = "gemm_bias_relu_bf16_tcgen05_out_bf16_v0", struct.pack("<iii", 0, tb, 1)
+    want = oracle.gemm_epilogue(A, B, bias, relu=True)
+    outs = {}
+    for mode, halves in [("halves", "1"), ("whole", "0")]:
+        with gemm_tuning(cta_group="2", tail_halves=halves):
+            C = dev(np.full((M, N), np.nan, np.float32), "bf16")  # an element nobody stores stays NaN
+            by_id(kid, OpKind.GemmEpilogue, [X, W, Bv], [C], GPEL, payload)
+            assert _C.gemm_status() == 0
+            outs[mode] = host(C)
+        assert rel_err(outs[mode], want) <= TOL["bf16"], mode
+    assert np.array_equal(outs["halves"], outs["whole"])
+    Y = oracle.bf16_round(np.random.default_rng(5).standard_normal((M, N)).astype(np.float32))
+    with gemm_tuning(cta_group="2", tail_halves="1"):
+        C32 = Tensor.zeros((M, N), "f32")
+        by_id("gemm_bf16_tcgen05_out_f32_v0", OpKind.Gemm, [X, W], [C32], GEMM, struct.pack("<ii", 0, tb))
+        Cm = Tensor.zeros((M, N), "bf16")
+        by_id("gemm_relu_bwd_bf16_tcgen05_out_bf16_v0", OpKind.GemmReluBwd, [X, W, dev(Y, "bf16")], [Cm], GEMM, struct.pack("<ii", 0, tb))
+        assert _C.gemm_status() == 0
+    assert rel_err(host(C32), oracle.gemm(A, B)) <= 1e-4
+    got = host(Cm)
+    assert rel_err(got, oracle.gemm_relu_bwd(A, B, Y)) <= TOL["bf16"]
+    assert not got[~(Y > 0)].any()

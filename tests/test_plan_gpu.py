@@ -8,6 +8,7 @@ import pytest
 import oracle
 from aicf_cuda import _C, DoubleBufferedStep, Plan, Tensor, build_mlp_train_step, f32_to_bf16_bits
 from aicf_cuda._C import OpKind
+from util import gemm_tuning
 
 pytestmark = pytest.mark.gpu
 
@@ -271,16 +272,13 @@ def test_fp32_mlp_on_the_tensor_cores_tracks_the_exact_plan(gpu):
     fast.close()
 
 
-def test_small_batch_plan_with_gemms_split_over_k(gpu, monkeypatch):
+def test_small_batch_plan_with_gemms_split_over_k(gpu):
     """A small batch against wide layers: the forward and dX GEMMs (M = 64, K = 4096) are split over K by the launcher,
     with the parts in the plan's one workspace buffer. The captured replay equals the eager run bit for bit, and both
     follow the oracle; with the split switched off the plan needs no GEMM workspace and gives the same loss to GEMM
     tolerance."""
     dims, batch = [4096, 4096, 16], 64
-    results = {}
-    for mode in ("split", "unsplit"):
-        if mode == "unsplit":
-            monkeypatch.setenv("AICF_GEMM_SPLITK", "0")
+    def two_steps(mode):
         eager, vals, low, env, dtypes = make_plan(batch, dims, "bf16", seed=6, lr=1e-3)
         graphed, *_ = make_plan(batch, dims, "bf16", seed=6, lr=1e-3)
         by = eager.by_name
@@ -295,10 +293,15 @@ def test_small_batch_plan_with_gemms_split_over_k(gpu, monkeypatch):
             assert eager.tensor("loss").numpy()[0] == graphed.tensor("loss").numpy()[0], (mode, step)
         for name in ("0.W", "2.W", "0.b"):
             assert np.array_equal(eager.tensor(name).numpy(), graphed.tensor(name).numpy()), (mode, name)
-        results[mode] = float(eager.tensor("loss").numpy()[0])
+        loss = float(eager.tensor("loss").numpy()[0])
         assert _C.gemm_status() == 0
         eager.close()
         graphed.close()
+        return loss
+
+    results = {"split": two_steps("split")}
+    with gemm_tuning(splitk="0"):
+        results["unsplit"] = two_steps("unsplit")
     assert results["split"] == pytest.approx(results["unsplit"], rel=2e-3)
 
 

@@ -1,7 +1,9 @@
 """Helpers shared by the GPU parity tests: call ops through the binding on aicf_cuda.Tensor buffers."""
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
+import os
 import struct
 
 import numpy as np
@@ -57,3 +59,25 @@ def assert_close_f32(got, want, rtol=1e-5, atol=1e-7, what=""):
 
 GEMM = struct.Struct("<ii")
 GEPL = struct.Struct("<iii")
+
+
+@contextlib.contextmanager
+def gemm_tuning(**settings):
+    """Runs the body with AICF_GEMM_<NAME>=value overrides in force (None removes a variable). The GEMM launcher reads
+    its environment once per process, so every change is followed by a reload, and so is the restore."""
+    names = {f"AICF_GEMM_{k.upper()}": v for k, v in settings.items()}
+    saved = {n: os.environ.get(n) for n in names}
+
+    def apply(values):
+        for n, v in values.items():
+            if v is None:
+                os.environ.pop(n, None)
+            else:
+                os.environ[n] = str(v)
+        aicf_cuda._lib.check(aicf_cuda.lib.aicf_b200_gemm_reload_tuning(), "gemm_reload_tuning")
+
+    apply(names)
+    try:
+        yield
+    finally:
+        apply(saved)

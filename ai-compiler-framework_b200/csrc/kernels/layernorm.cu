@@ -18,6 +18,8 @@
 // row's mean / rstd one iteration early.
 // Rows that do not fit the register path (N not a multiple of the 16-byte packet, unaligned pointers, N beyond the
 // per-thread element budget) take multi-pass kernels that accept anything.
+#include <cstdlib>
+
 #include "row_pipeline.cuh"
 
 namespace aicf::cuda {
@@ -67,7 +69,10 @@ __device__ __forceinline__ Pack16<T> ld_param(const T* p, int64_t packet) {  // 
 }
 
 // ------------------------------------------------------------------ forward, row in registers
-template <typename T, int kPackets, bool kAffine>
+// kFull: the row is exactly kPackets packets for every thread of the block, so no packet needs a range check. The
+// checks (a compare, a branch and a reconvergence point per packet and loop, and zero-fill of the unused registers)
+// were a quarter of the instructions of the 16-bit kernels, which are bound by instruction issue.
+template <typename T, int kPackets, bool kAffine, bool kFull>
 __global__ void __launch_bounds__(1024)
     ln_fwd_regs_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
                        float* __restrict__ mean, float* __restrict__ rstd, int64_t M, int64_t N, float eps) {
@@ -76,7 +81,8 @@ __global__ void __launch_bounds__(1024)
   extern __shared__ __align__(16) uint8_t row_smem[];
   __shared__ float red[2][kMaxWarps + 1];
   __shared__ int wait_failed;
-  const int64_t np = N / kN;
+  using Idx = typename RowIdx<T>::type;
+  const Idx np = static_cast<Idx>(N / kN);
   const uint32_t row_bytes = static_cast<uint32_t>(N * sizeof(T));
   const float inv_n = 1.0f / static_cast<float>(N);
   RowPipe pipe;
@@ -90,12 +96,12 @@ __global__ void __launch_bounds__(1024)
     float s = 0.0f;
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
-      const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
-      if (pi < np) {
+      const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
+      if (kFull || pi < np) {
         unpack16(srow[pi], f[q]);
 #pragma unroll
         for (int e = 0; e < kN; ++e) s += f[q][e];
-      } else {
+      } else {  // never read again (every later use sits behind the same range check); keeps the registers defined
 #pragma unroll
         for (int e = 0; e < kN; ++e) f[q][e] = 0.0f;
       }
@@ -115,8 +121,8 @@ __global__ void __launch_bounds__(1024)
     float d2 = 0.0f;
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
-      const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
-      if (pi < np) {
+      const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
+      if (kFull || pi < np) {
 #pragma unroll
         for (int e = 0; e < kN; ++e) {
           f[q][e] -= mu;
@@ -133,8 +139,8 @@ __global__ void __launch_bounds__(1024)
     PK* yr = reinterpret_cast<PK*>(y + row * N);
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
-      const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
-      if (pi < np) {
+      const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
+      if (kFull || pi < np) {
         PK o;
         float r[kN];
         if constexpr (kAffine) {
@@ -192,7 +198,7 @@ __global__ void __launch_bounds__(256)
 // taken its part of the current pair into registers, so up to `stages` row pairs per block are in flight or
 // waiting in shared memory while one is being worked on.
 // partial: [gridDim.x][2][N] floats (dgamma partials, then dbeta partials), written only when kAffine.
-template <typename T, int kPackets, bool kAffine>
+template <typename T, int kPackets, bool kAffine, bool kFull>
 __global__ void __launch_bounds__((kPackets * (16 / sizeof(T)) > 8) ? 512 : 1024)
     ln_bwd_regs_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ gamma,
                        const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
@@ -202,7 +208,8 @@ __global__ void __launch_bounds__((kPackets * (16 / sizeof(T)) > 8) ? 512 : 1024
   extern __shared__ __align__(16) uint8_t row_smem[];
   __shared__ float red[2][kSum2Floats];
   __shared__ int wait_failed;
-  const int64_t np = N / kN;
+  using Idx = typename RowIdx<T>::type;
+  const Idx np = static_cast<Idx>(N / kN);
   const uint32_t row_bytes = static_cast<uint32_t>(N * sizeof(T));
   const uint32_t slot_bytes = 2 * row_bytes;
   const float n_f = static_cast<float>(N), inv_n = 1.0f / n_f;
@@ -236,11 +243,11 @@ __global__ void __launch_bounds__((kPackets * (16 / sizeof(T)) > 8) ? 512 : 1024
   float gam[kPackets][kN];
 #pragma unroll
   for (int q = 0; q < kPackets; ++q) {
-    const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
+    const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
     PK pg;
-    if (kAffine && pi < np) pg = ld_param(gamma, pi);
+    if (kAffine && (kFull || pi < np)) pg = ld_param(gamma, pi);
 #pragma unroll
-    for (int e = 0; e < kN; ++e) gam[q][e] = (kAffine && pi < np) ? Cvt<T>::to_f(pg.v[e]) : 1.0f;
+    for (int e = 0; e < kN; ++e) gam[q][e] = (kAffine && (kFull || pi < np)) ? Cvt<T>::to_f(pg.v[e]) : 1.0f;
   }
   int slot = 0, it = 0;
   uint32_t parity = 0;
@@ -259,14 +266,15 @@ __global__ void __launch_bounds__((kPackets * (16 / sizeof(T)) > 8) ? 512 : 1024
     const PK* sdy = reinterpret_cast<const PK*>(row_smem + static_cast<size_t>(slot) * slot_bytes + row_bytes);
     float xh[kPackets][kN], g[kPackets][kN];
     float s1 = 0.0f, s2 = 0.0f;
+    const float neg_mu_rs = -mu * rs;  // x-hat = x * rstd - mean * rstd: one fused multiply-add per element
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
-      const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
-      if (pi < np) {
+      const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
+      if (kFull || pi < np) {
         const PK px = sx[pi], pd = sdy[pi];
 #pragma unroll
         for (int e = 0; e < kN; ++e) {
-          xh[q][e] = (Cvt<T>::to_f(px.v[e]) - mu) * rs;
+          xh[q][e] = fmaf(Cvt<T>::to_f(px.v[e]), rs, neg_mu_rs);
           float d = Cvt<T>::to_f(pd.v[e]);
           if constexpr (kAffine) {
             acc_b[q][e] += d;
@@ -294,15 +302,19 @@ __global__ void __launch_bounds__((kPackets * (16 / sizeof(T)) > 8) ? 512 : 1024
         fetch2(ahead, slot);
       }
     }
+    // dx = (N g - s1 - x-hat s2) rstd / N, with the three row constants folded: two fused multiply-adds per element
     const float k = rs * inv_n;
+    const float c_g = n_f * k, c_1 = -s1 * k, c_x = -s2 * k;
     PK* dxr = reinterpret_cast<PK*>(dx + row * N);
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
-      const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
-      if (pi < np) {
+      const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
+      if (kFull || pi < np) {
         PK o;
+        float r[kN];
 #pragma unroll
-        for (int e = 0; e < kN; ++e) o.v[e] = Cvt<T>::from_f((n_f * g[q][e] - s1 - xh[q][e] * s2) * k);
+        for (int e = 0; e < kN; ++e) r[e] = fmaf(g[q][e], c_g, fmaf(xh[q][e], c_x, c_1));
+        pack16(o, r);
         st_stream(dxr + pi, o);
       }
     }
@@ -316,12 +328,12 @@ __global__ void __launch_bounds__((kPackets * (16 / sizeof(T)) > 8) ? 512 : 1024
     float* pb = pg + N;
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
-      const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
-      if (pi < np) {
+      const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
+      if (kFull || pi < np) {
 #pragma unroll
         for (int e = 0; e < kN; ++e) {
-          pg[pi * kN + e] = acc_g[q][e];
-          pb[pi * kN + e] = acc_b[q][e];
+          pg[static_cast<int64_t>(pi) * kN + e] = acc_g[q][e];
+          pb[static_cast<int64_t>(pi) * kN + e] = acc_b[q][e];
         }
       }
     }
@@ -429,19 +441,24 @@ bool ln_fwd_supported(const TensorDesc* in, int ni, const TensorDesc* out, int n
   return ln_fwd_check<kDt>(in, ni, out, no, &M, &N);
 }
 
+template <typename T, int kPackets, bool kAffine, bool kFull>
+Status ln_fwd_go2(int threads, size_t smem, cudaStream_t stream, const T* x, const T* g, const T* b, T* y, float* mean,
+                  float* rstd, int64_t M, int64_t N, float eps) {
+  auto kernel = ln_fwd_regs_kernel<T, kPackets, kAffine, kFull>;
+  if (!allow_smem(kernel, smem)) return Status::Internal;
+  const int grid = streaming_grid(M, 1, row_blocks_per_sm(kernel, threads, smem));
+  kernel<<<grid, threads, smem, stream>>>(x, g, b, y, mean, rstd, M, N, eps);
+  return launch_status();
+}
 template <typename T, int kPackets>
 Status ln_fwd_go(bool affine, int threads, size_t smem, cudaStream_t stream, const T* x, const T* g, const T* b, T* y,
                  float* mean, float* rstd, int64_t M, int64_t N, float eps) {
-  if (affine) {
-    if (!allow_smem(ln_fwd_regs_kernel<T, kPackets, true>, smem)) return Status::Internal;
-    const int grid = streaming_grid(M, 1, row_blocks_per_sm(ln_fwd_regs_kernel<T, kPackets, true>, threads, smem));
-    ln_fwd_regs_kernel<T, kPackets, true><<<grid, threads, smem, stream>>>(x, g, b, y, mean, rstd, M, N, eps);
-  } else {
-    if (!allow_smem(ln_fwd_regs_kernel<T, kPackets, false>, smem)) return Status::Internal;
-    const int grid = streaming_grid(M, 1, row_blocks_per_sm(ln_fwd_regs_kernel<T, kPackets, false>, threads, smem));
-    ln_fwd_regs_kernel<T, kPackets, false><<<grid, threads, smem, stream>>>(x, g, b, y, mean, rstd, M, N, eps);
-  }
-  return launch_status();
+  const bool full = use_full_rows(N / Pack16<T>::kN == static_cast<int64_t>(threads) * kPackets, sizeof(T));
+  if (affine)
+    return full ? ln_fwd_go2<T, kPackets, true, true>(threads, smem, stream, x, g, b, y, mean, rstd, M, N, eps)
+                : ln_fwd_go2<T, kPackets, true, false>(threads, smem, stream, x, g, b, y, mean, rstd, M, N, eps);
+  return full ? ln_fwd_go2<T, kPackets, false, true>(threads, smem, stream, x, g, b, y, mean, rstd, M, N, eps)
+              : ln_fwd_go2<T, kPackets, false, false>(threads, smem, stream, x, g, b, y, mean, rstd, M, N, eps);
 }
 
 template <DType kDt, typename T>
@@ -490,11 +507,18 @@ struct BwdGeom {
 BwdGeom bwd_geom(int64_t M, int64_t N, size_t elem, bool vec_ok) {
   BwdGeom g;
   const int kn = static_cast<int>(16 / elem);
-  // 16-bit rows of 4096 elements and more take 16 elements per thread (two packets, ~107 registers, 512-thread
+  // 16-bit rows of 512 elements and more take 16 elements per thread (two packets, ~110-120 registers, 512-thread
   // blocks at most): these kernels are bound by instruction issue, and the per-row overhead (barriers, shuffles, loop
-  // control) is then spread over twice the elements (4096 columns: 0.67 -> 0.78 of the copy rate). Narrower rows
-  // lose more from the halved number of resident blocks than they gain.
-  const bool wide = elem == 2 && N % kn == 0 && N / kn >= 512;
+  // control) is then spread over twice the elements. Fraction of the copy rate with 8 / 16 elements per thread, bf16:
+  // 512 columns 0.57 / 0.77, 1024 0.67 / 0.79, 2048 0.69 / 0.81, 4096 0.78 / 0.92. Below 512 columns a warp would be left
+  // with less than one packet pair per thread.
+  // AICF_LN_BWD_WIDE_MIN (tuning, read once per process): the row length in packets from which the wide form is taken.
+  static const int64_t wide_min = [] {
+    const char* e = std::getenv("AICF_LN_BWD_WIDE_MIN");
+    const long v = e ? std::atol(e) : 0;
+    return static_cast<int64_t>(v > 0 ? v : 64);
+  }();
+  const bool wide = elem == 2 && N % kn == 0 && N / kn >= wide_min;
   const int max_packets = wide ? 2 : 8 / kn;
   const int64_t col_blocks = (N + 127) / 128;
   int64_t sl = (static_cast<int64_t>(sm_count()) * 8) / col_blocks;
@@ -552,17 +576,23 @@ size_t ln_bwd_workspace(const TensorDesc* in, int ni, const void*) {
   return static_cast<size_t>(slots) * 2 * static_cast<size_t>(N) * sizeof(float);
 }
 
+template <typename T, int kPackets, bool kAffine, bool kFull>
+Status ln_bwd_go2(const BwdGeom& g, cudaStream_t stream, const T* x, const T* dy, const T* gamma, const float* mean,
+                  const float* rstd, T* dx, float* partial, int64_t M, int64_t N) {
+  auto kernel = ln_bwd_regs_kernel<T, kPackets, kAffine, kFull>;
+  if (!allow_smem(kernel, g.smem)) return Status::Internal;
+  kernel<<<g.grid, g.threads, g.smem, stream>>>(x, dy, gamma, mean, rstd, dx, partial, M, N, g.stages);
+  return launch_status();
+}
 template <typename T, int kPackets>
 Status ln_bwd_go(bool affine, const BwdGeom& g, cudaStream_t stream, const T* x, const T* dy, const T* gamma, const float* mean,
                  const float* rstd, T* dx, float* partial, int64_t M, int64_t N) {
-  if (affine) {
-    if (!allow_smem(ln_bwd_regs_kernel<T, kPackets, true>, g.smem)) return Status::Internal;
-    ln_bwd_regs_kernel<T, kPackets, true><<<g.grid, g.threads, g.smem, stream>>>(x, dy, gamma, mean, rstd, dx, partial, M, N, g.stages);
-  } else {
-    if (!allow_smem(ln_bwd_regs_kernel<T, kPackets, false>, g.smem)) return Status::Internal;
-    ln_bwd_regs_kernel<T, kPackets, false><<<g.grid, g.threads, g.smem, stream>>>(x, dy, gamma, mean, rstd, dx, partial, M, N, g.stages);
-  }
-  return launch_status();
+  const bool full = use_full_rows(N / Pack16<T>::kN == static_cast<int64_t>(g.threads) * kPackets, sizeof(T));
+  if (affine)
+    return full ? ln_bwd_go2<T, kPackets, true, true>(g, stream, x, dy, gamma, mean, rstd, dx, partial, M, N)
+                : ln_bwd_go2<T, kPackets, true, false>(g, stream, x, dy, gamma, mean, rstd, dx, partial, M, N);
+  return full ? ln_bwd_go2<T, kPackets, false, true>(g, stream, x, dy, gamma, mean, rstd, dx, partial, M, N)
+              : ln_bwd_go2<T, kPackets, false, false>(g, stream, x, dy, gamma, mean, rstd, dx, partial, M, N);
 }
 
 template <DType kDt, typename T>

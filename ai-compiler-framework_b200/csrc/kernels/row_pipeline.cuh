@@ -2,6 +2,7 @@
 // Building blocks of the row kernels (softmax, softmax cross-entropy, layer norm): a block owns one row at a
 // time, keeps it in registers, and prefetches its next row into shared memory with one bulk asynchronous copy.
 #include <cstdlib>
+#include <type_traits>
 
 #include "common.cuh"
 #include "sm100_async.cuh"
@@ -122,6 +123,31 @@ inline int row_pipe_blocks_per_sm(int threads, size_t smem) {
   int b = by_threads < by_smem ? by_threads : by_smem;
   return b < 1 ? 1 : (b > 32 ? 32 : b);
 }
+
+// Whether a row that fills every thread's packets exactly takes the kernel variant without per-packet range checks.
+// AICF_ROW_FULL (tuning, read once per process): 0 = never, 1 = always, unset = by element size (see use_full_rows).
+inline int row_full_override() {
+  static const int v = [] {
+    const char* e = std::getenv("AICF_ROW_FULL");
+    return (e == nullptr || e[0] == 0) ? -1 : (e[0] == '0' ? 0 : 1);
+  }();
+  return v;
+}
+inline bool use_full_rows(bool exact_fit, size_t elem_bytes) {
+  if (!exact_fit) return false;
+  const int o = row_full_override();
+  if (o >= 0) return o != 0;
+  return elem_bytes < 4;
+}
+// Type of a thread's packet index. The 16-bit kernels are bound by instruction issue: 32-bit indices and no range
+// checks took a quarter of their instructions away (layer norm [32768,4096] bf16: forward 5650 -> 6258 GB/s, backward
+// 5392 -> 6035). The fp32 kernels are bound by HBM and measured slower with the leaner code (layer norm backward f32
+// 6739 -> 5800 GB/s, softmax f32 6239 -> 5953): there the timing of the loads and stores decides, not the instruction
+// count, so they keep the 64-bit index arithmetic and the checks they were tuned with.
+template <typename T>
+struct RowIdx {
+  using type = std::conditional_t<sizeof(T) == 4, int64_t, int>;
+};
 
 template <typename K>
 bool allow_smem(K kernel, size_t smem) {

@@ -107,7 +107,9 @@ __device__ __forceinline__ SumMin block_sum_min(float s, int idx, float* sv /*[k
 }
 
 // ------------------------------------------------------------------ softmax, row in registers
-template <typename T, int kPackets>
+// kFull: the row is exactly kPackets packets for every thread, so no packet needs a range check (a compare, a branch and a
+// reconvergence point per packet and loop otherwise: a sizeable share of the instructions of the 16-bit kernels).
+template <typename T, int kPackets, bool kFull>
 __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M,
                                                            int64_t N) {
   using PK = Pack16<T>;
@@ -115,7 +117,8 @@ __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict_
   extern __shared__ __align__(16) uint8_t row_smem[];
   __shared__ float red[2][kMaxWarps + 1];
   __shared__ int wait_failed;
-  const int64_t np = N / kN;  // N % kN == 0 on this path
+  using Idx = typename RowIdx<T>::type;
+  const Idx np = static_cast<Idx>(N / kN);  // N % kN == 0 on this path
   const uint32_t row_bytes = static_cast<uint32_t>(N * sizeof(T));
   RowPipe pipe;
   pipe.init(row_smem, row_bytes, &wait_failed);
@@ -129,8 +132,8 @@ __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict_
     float mx = -INFINITY;
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
-      const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
-      if (pi < np) {
+      const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
+      if (kFull || pi < np) {
         unpack16(srow[pi], f[q]);
 #pragma unroll
         for (int e = 0; e < kN; ++e) mx = fmaxf(mx, f[q][e]);
@@ -162,8 +165,8 @@ __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict_
     const float inv = 1.0f / sum;
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
-      const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
-      if (pi < np) {
+      const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
+      if (kFull || pi < np) {
         PK o;
         float r[kN];
 #pragma unroll
@@ -207,10 +210,15 @@ Status softmax_run(const T* x, T* y, int64_t M, int64_t N, cudaStream_t stream) 
     return launch_status();
   }
   bool ok_attr = true;
-#define AICF_SM_LAUNCH(PK)                                                                                        \
-  if ((ok_attr = allow_smem(softmax_regs_kernel<T, PK>, smem)))                                                   \
-    softmax_regs_kernel<T, PK><<<streaming_grid(M, 1, row_blocks_per_sm(softmax_regs_kernel<T, PK>, c.threads, smem)), \
-                                 c.threads, smem, stream>>>(x, y, M, N)
+  const bool full = use_full_rows(N / kN == static_cast<int64_t>(c.threads) * c.packets, sizeof(T));
+#define AICF_SM_LAUNCH_F(PK, FULL)                                                                                        \
+  if ((ok_attr = allow_smem(softmax_regs_kernel<T, PK, FULL>, smem)))                                                     \
+    softmax_regs_kernel<T, PK, FULL>                                                                                      \
+        <<<streaming_grid(M, 1, row_blocks_per_sm(softmax_regs_kernel<T, PK, FULL>, c.threads, smem)), c.threads, smem, \
+           stream>>>(x, y, M, N)
+#define AICF_SM_LAUNCH(PK)                     \
+  if (full) { AICF_SM_LAUNCH_F(PK, true); }    \
+  else { AICF_SM_LAUNCH_F(PK, false); }
   switch (c.packets) {
     case 1: AICF_SM_LAUNCH(1); break;
     case 2: AICF_SM_LAUNCH(2); break;
@@ -218,6 +226,7 @@ Status softmax_run(const T* x, T* y, int64_t M, int64_t N, cudaStream_t stream) 
     default: AICF_SM_LAUNCH(kMaxPk); break;
   }
 #undef AICF_SM_LAUNCH
+#undef AICF_SM_LAUNCH_F
   if (!ok_attr) {
     cudaGetLastError();
     return Status::Internal;
@@ -270,7 +279,7 @@ Status softmax_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, con
 // Per element the loops only take a maximum, an exponential and a product: the arg-max index is looked up afterwards
 // by the few threads that hold the row maximum and reduced together with the sum, and the one-hot term is patched in
 // by the one thread that owns the label's column.
-template <typename T, int kPackets, bool kLockstep>
+template <typename T, int kPackets, bool kLockstep, bool kFull>
 __global__ void __launch_bounds__(1024)
     softmax_ce_regs_kernel(const T* __restrict__ z, const int32_t* __restrict__ labels, T* __restrict__ dz,
                            float* __restrict__ loss_row, int32_t* __restrict__ argmax_out, int64_t B, int64_t C,
@@ -281,7 +290,8 @@ __global__ void __launch_bounds__(1024)
   __shared__ float red[2][kMaxWarps + 1];
   __shared__ int wait_failed;
   __shared__ int redi[kMaxWarps + 1];
-  const int64_t np = C / kN;
+  using Idx = typename RowIdx<T>::type;
+  const Idx np = static_cast<Idx>(C / kN);
   const uint32_t row_bytes = static_cast<uint32_t>(C * sizeof(T));
   RowPipe pipe;
   pipe.init(row_smem, row_bytes, &wait_failed);
@@ -308,8 +318,8 @@ __global__ void __launch_bounds__(1024)
     float tmax = -INFINITY;
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
-      const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
-      if (pi < np) {
+      const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
+      if (kFull || pi < np) {
         unpack16(srow[pi], f[q]);
 #pragma unroll
         for (int e = 0; e < kN; ++e) tmax = fmaxf(tmax, f[q][e]);
@@ -335,8 +345,8 @@ __global__ void __launch_bounds__(1024)
     if (tmax == mx) {
 #pragma unroll
       for (int q = kPackets - 1; q >= 0; --q) {
-        const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
-        if (pi < np) {
+        const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
+        if (kFull || pi < np) {
 #pragma unroll
           for (int e = kN - 1; e >= 0; --e)
             if (f[q][e] == mx) cand = static_cast<int>(pi) * kN + e;  // descending order: the lowest column stays
@@ -356,8 +366,8 @@ __global__ void __launch_bounds__(1024)
     const float k = scale / sum;
 #pragma unroll
     for (int q = 0; q < kPackets; ++q) {
-      const int64_t pi = threadIdx.x + static_cast<int64_t>(q) * blockDim.x;
-      if (pi < np) {
+      const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
+      if (kFull || pi < np) {
         PK o;
         float r[kN];
 #pragma unroll
@@ -465,14 +475,16 @@ Status softmax_ce_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, 
     const char* e = std::getenv("AICF_CE_LOCKSTEP");
     return e != nullptr && e[0] == '1';
   }();
-#define AICF_CE_LAUNCH_M(PK, LS)                                                                                     \
-  if ((ok_attr = allow_smem(softmax_ce_regs_kernel<T, PK, LS>, smem)))                                               \
-    softmax_ce_regs_kernel<T, PK, LS>                                                                                \
-        <<<streaming_grid(B, 1, row_blocks_per_sm(softmax_ce_regs_kernel<T, PK, LS>, c.threads, smem)), c.threads, \
+  const bool full = use_full_rows(C / kN == static_cast<int64_t>(c.threads) * c.packets, sizeof(T));
+#define AICF_CE_LAUNCH_M(PK, LS, FULL)                                                                                     \
+  if ((ok_attr = allow_smem(softmax_ce_regs_kernel<T, PK, LS, FULL>, smem)))                                               \
+    softmax_ce_regs_kernel<T, PK, LS, FULL>                                                                                \
+        <<<streaming_grid(B, 1, row_blocks_per_sm(softmax_ce_regs_kernel<T, PK, LS, FULL>, c.threads, smem)), c.threads, \
            smem, stream>>>(z, lab, dz, loss, am, B, C, scale)
-#define AICF_CE_LAUNCH(PK)                          \
-  if (lockstep) { AICF_CE_LAUNCH_M(PK, true); }     \
-  else { AICF_CE_LAUNCH_M(PK, false); }
+#define AICF_CE_LAUNCH(PK)                                  \
+  if (lockstep) { AICF_CE_LAUNCH_M(PK, true, false); }      \
+  else if (full) { AICF_CE_LAUNCH_M(PK, false, true); }     \
+  else { AICF_CE_LAUNCH_M(PK, false, false); }
   switch (c.packets) {
     case 1: AICF_CE_LAUNCH(1); break;
     case 2: AICF_CE_LAUNCH(2); break;

@@ -929,9 +929,12 @@ def run_kernel_workload(args):
 
 
 KERNEL_SUITE = [("gemm_8192_bf16", "gemm", dict(size=8192)), ("gemm_4096_bf16", "gemm", dict(size=4096)),
-                ("gemm_1024_bf16", "gemm", dict(size=1024)), ("softmax_f32", "softmax", dict(dtype="f32")),
+                ("gemm_1024_bf16", "gemm", dict(size=1024)), ("gemm_4096_f32", "gemm_f32", dict(size=4096)),
+                ("softmax_f32", "softmax", dict(dtype="f32")),
                 ("softmax_bf16", "softmax", dict(dtype="bf16")), ("softmax_ce_f32", "ce", {}),
-                ("reduce_sum_f32", "reduce", dict(dtype="f32", reduce_kind="sum")), ("adam_f32_2p28", "adam", {}),
+                ("reduce_sum_f32", "reduce", dict(dtype="f32", reduce_kind="sum")),
+                ("reduce_max_f32", "reduce", dict(dtype="f32", reduce_kind="max")),
+                ("reduce_mean_bf16", "reduce", dict(dtype="bf16", reduce_kind="mean")), ("adam_f32_2p28", "adam", {}),
                 # measured ceilings for the stream mixes above: 4 arrays read + 3 written (Adam), 1 + 1 (softmax, CE)
                 # (launch shapes that measured best in a sweep of 1 / 2 / 4 packets in flight x 4 / 8 / 16 / 32 blocks per SM)
                 ("ceiling_4_reads_3_writes", "stream_mix", dict(rows=4, cols=3, probe=(1, 32))),

@@ -113,7 +113,16 @@ inline RowCfg pick_row_cfg(int64_t n_packets, int max_packets) {
 }
 
 // Dynamic shared memory of the pipelined kernels: the row plus its mbarrier.
-inline size_t row_pipe_smem(int64_t row_bytes) { return static_cast<size_t>(row_bytes) + 16; }
+inline size_t row_pipe_smem(int64_t row_bytes) {
+  // AICF_ROW_SMEM_PAD (tuning, read once per process): unused bytes added to every block's shared memory, to bound how
+  // many blocks an SM holds
+  static const size_t pad = [] {
+    const char* e = std::getenv("AICF_ROW_SMEM_PAD");
+    const long v = e ? std::atol(e) : 0;
+    return static_cast<size_t>(v > 0 ? (v / 16) * 16 : 0);
+  }();
+  return static_cast<size_t>(row_bytes) + 16 + pad;
+}
 constexpr size_t kMaxRowPipeSmem = 200 * 1024;
 
 // Resident blocks per SM given threads and shared memory per block (227 KiB usable, ~1 KiB reserved per block).
@@ -152,6 +161,21 @@ struct RowIdx {
 template <typename K>
 bool allow_smem(K kernel, size_t smem) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) == cudaSuccess;
+}
+
+// Shared memory to ask for so that an SM holds at most 1024 threads of a softmax / cross-entropy kernel (blocks of 128
+// threads and more). These kernels read nothing through L1, so the unused bytes cost nothing, and fewer, equally long
+// row streams per SM measured faster than filling the SM: softmax f32 [32768,4096] 6064 -> 6620 GB/s with four instead
+// of five 256-thread blocks resident (whatever the grid: 4, 8, 12 or 16 blocks per SM), [32768,2048] 6214 -> 6473, bf16
+// [32768,4096] 6387 -> 6473, cross-entropy f32 on 1024 columns 6377 -> 6489; three resident blocks lose again (6023), and
+// 64-thread softmax blocks lose from the cap (6112 -> 5924), hence the threshold. The grid keeps its size. Layer norm
+// reads gamma and beta through L1 and sits at 1024 threads per SM by its registers anyway: it does not use this.
+inline size_t row_smem_capped_residency(size_t smem, int threads) {
+  if (threads < 128) return smem;
+  const size_t blocks = static_cast<size_t>(1024 / threads);
+  const size_t want = (227 * 1024) / (blocks + 1) + 16;  // more than this and blocks + 1 no longer fit
+  const size_t aligned = (want + 15) / 16 * 16;
+  return aligned > smem ? aligned : smem;
 }
 
 // Blocks per SM the grid-stride row kernels are launched with. The default is the estimate above, which ignores

@@ -211,11 +211,12 @@ Status softmax_run(const T* x, T* y, int64_t M, int64_t N, cudaStream_t stream) 
   }
   bool ok_attr = true;
   const bool full = use_full_rows(N / kN == static_cast<int64_t>(c.threads) * c.packets, sizeof(T));
-#define AICF_SM_LAUNCH_F(PK, FULL)                                                                                        \
-  if ((ok_attr = allow_smem(softmax_regs_kernel<T, PK, FULL>, smem)))                                                     \
-    softmax_regs_kernel<T, PK, FULL>                                                                                      \
-        <<<streaming_grid(M, 1, row_blocks_per_sm(softmax_regs_kernel<T, PK, FULL>, c.threads, smem)), c.threads, smem, \
-           stream>>>(x, y, M, N)
+  const size_t smem_launch = row_smem_capped_residency(smem, c.threads);  // the grid is still sized from `smem`
+#define AICF_SM_LAUNCH_F(PK, FULL)                                                                                 \
+  if ((ok_attr = allow_smem(softmax_regs_kernel<T, PK, FULL>, smem_launch)))                                       \
+    softmax_regs_kernel<T, PK, FULL>                                                                               \
+        <<<streaming_grid(M, 1, row_blocks_per_sm(softmax_regs_kernel<T, PK, FULL>, c.threads, smem)), c.threads, \
+           smem_launch, stream>>>(x, y, M, N)
 #define AICF_SM_LAUNCH(PK)                     \
   if (full) { AICF_SM_LAUNCH_F(PK, true); }    \
   else { AICF_SM_LAUNCH_F(PK, false); }
@@ -476,11 +477,12 @@ Status softmax_ce_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, 
     return e != nullptr && e[0] == '1';
   }();
   const bool full = use_full_rows(C / kN == static_cast<int64_t>(c.threads) * c.packets, sizeof(T));
+  const size_t smem_launch = row_smem_capped_residency(smem, c.threads);  // the grid is still sized from `smem`
 #define AICF_CE_LAUNCH_M(PK, LS, FULL)                                                                                     \
-  if ((ok_attr = allow_smem(softmax_ce_regs_kernel<T, PK, LS, FULL>, smem)))                                               \
+  if ((ok_attr = allow_smem(softmax_ce_regs_kernel<T, PK, LS, FULL>, smem_launch)))                                        \
     softmax_ce_regs_kernel<T, PK, LS, FULL>                                                                                \
         <<<streaming_grid(B, 1, row_blocks_per_sm(softmax_ce_regs_kernel<T, PK, LS, FULL>, c.threads, smem)), c.threads, \
-           smem, stream>>>(z, lab, dz, loss, am, B, C, scale)
+           smem_launch, stream>>>(z, lab, dz, loss, am, B, C, scale)
 #define AICF_CE_LAUNCH(PK)                                  \
   if (lockstep) { AICF_CE_LAUNCH_M(PK, true, false); }      \
   else if (full) { AICF_CE_LAUNCH_M(PK, false, true); }     \

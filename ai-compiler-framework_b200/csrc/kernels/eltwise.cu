@@ -55,7 +55,7 @@ Status run_eltwise(const void* a, const void* b, void* o, int64_t n, F f, cudaSt
   if (n <= 0) return Status::Ok;
   const bool vec = aligned_to(a, 16) && aligned_to(o, 16) && (kInputs == 1 || aligned_to(b, 16));
   const int64_t nvec = vec ? n / Pack16<T>::kN : 0;
-  const int grid = streaming_grid(vec ? nvec / 2 + 1 : n, 256, 8);
+  const int grid = streaming_grid(vec ? nvec / 2 + 1 : n, 256, kStreamBlocksPerSm);
   cudaGetLastError();
   eltwise_kernel<T, kInputs, F><<<grid, 256, 0, stream>>>(static_cast<const T*>(a), static_cast<const T*>(b),
                                                          static_cast<T*>(o), n, nvec, f);
@@ -261,7 +261,7 @@ Status bias_add_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, co
   const int vec = (N % Pack16<T>::kN == 0) && aligned_to(in[0].data, 16) && aligned_to(in[1].data, 16) &&
                   aligned_to(out[0].data, 16);
   cudaGetLastError();
-  bias_add_kernel<T><<<streaming_grid(vec ? total / Pack16<T>::kN : total, 256, 8), 256, 0, s>>>(
+  bias_add_kernel<T><<<streaming_grid(vec ? total / Pack16<T>::kN : total, 256, kStreamBlocksPerSm), 256, 0, s>>>(
       static_cast<const T*>(in[0].data), static_cast<const T*>(in[1].data), static_cast<T*>(out[0].data), total, N, vec);
   return launch_status();
 }
@@ -302,7 +302,7 @@ Status cast_run(const TensorDesc& x, TensorDesc& y, cudaStream_t s) {
   const int64_t n = x.numel();
   const int vec = aligned_to(x.data, 16) && aligned_to(y.data, 16);
   cudaGetLastError();
-  cast_kernel<S, D><<<streaming_grid(vec ? n / 8 + 1 : n, 256, 8), 256, 0, s>>>(static_cast<const S*>(x.data),
+  cast_kernel<S, D><<<streaming_grid(vec ? n / 8 + 1 : n, 256, kStreamBlocksPerSm), 256, 0, s>>>(static_cast<const S*>(x.data),
                                                                                static_cast<D*>(y.data), n, vec);
   return launch_status();
 }
@@ -426,13 +426,13 @@ Status probe_launch(const ProbeArgs& a, int in_flight, int blocks_per_sm, cudaSt
 }  // namespace
 
 // reads in 1..4, writes in 1..3; arrays of `bytes` bytes each (multiple of 16), 16-byte aligned, all distinct;
-// in_flight in {1, 2, 4} (0 = 2), blocks_per_sm in 1..32 (0 = 8).
+// in_flight in {1, 2, 4} (0 = 2), blocks_per_sm in 1..1024 (0 = 8; past the resident count the grid is oversubscribed).
 Status stream_probe(int reads, int writes, const void* const* in, void* const* out, size_t bytes, int in_flight,
                     int blocks_per_sm, cudaStream_t stream) {
   if (reads < 1 || reads > 4 || writes < 1 || writes > 3 || !in || !out || bytes == 0 || bytes % 16 != 0) return Status::InvalidArgument;
   if (in_flight == 0) in_flight = 2;
   if (blocks_per_sm == 0) blocks_per_sm = 8;
-  if ((in_flight != 1 && in_flight != 2 && in_flight != 4) || blocks_per_sm < 1 || blocks_per_sm > 32) return Status::InvalidArgument;
+  if ((in_flight != 1 && in_flight != 2 && in_flight != 4) || blocks_per_sm < 1 || blocks_per_sm > 1024) return Status::InvalidArgument;
   ProbeArgs a{};
   for (int r = 0; r < reads; ++r) {
     if (!in[r] || !aligned_to(in[r], 16)) return Status::InvalidArgument;

@@ -1526,7 +1526,7 @@ Status gemm_tcgen05_run(const GemmProblem& p, void* ws, size_t ws_bytes, cudaStr
                               : tn == 128 ? go(std::integral_constant<int, 128>{}) : go(std::integral_constant<int, 64>{});
   if (st != Status::Ok || choice.splits <= 1) return st;
   const int64_t total4 = static_cast<int64_t>(p.M) * p.N / 4;
-  splitk_finish_kernel<<<streaming_grid(total4, 256, 8), 256, 0, stream>>>(g);
+  splitk_finish_kernel<<<streaming_grid(total4, 256, kStreamBlocksPerSm), 256, 0, stream>>>(g);
   return launch_status();
 }
 

@@ -4,9 +4,10 @@
 // Everything here is HBM-bound streaming work: 128-bit loads/stores with evict-first hints,
 // 64-bit indexing, a grid sized in whole multiples of the SM count and a grid-stride loop, so
 // one launch covers any size (the reference caps its grid at 65535 blocks of scalar accesses).
+#include <cstdlib>
+
 #include "adam_math.cuh"
 #include "common.cuh"
-#include "sm100_async.cuh"
 
 namespace aicf::cuda {
 
@@ -127,100 +128,15 @@ __global__ void __launch_bounds__(256) adam_kernel(AdamArgs a) {
   }
 }
 
-// ---- large arrays: the four input streams arrive by bulk asynchronous copies -------------------------------------
-// A block works on chunks of kBulkChunk floats per array. One thread keeps a ring of kBulkStages chunks in flight
-// (four cp.async.bulk per chunk, one mbarrier); all threads take their packets of an arrived chunk out of shared
-// memory, a single barrier frees the slot for the next copy, and the update is computed and stored from registers.
-// Compared with per-thread 16-byte loads this keeps many KiB per SM in flight with no registers or issue slots spent
-// on it. Waits are bounded; a wait that runs out ends the block and sets g_adam_status.
-constexpr int kBulkThreads = 256;
-constexpr int kBulkPackets = 4;                                   // 16-byte packets per thread per array per chunk
-constexpr int kBulkChunk = kBulkThreads * kBulkPackets * 4;       // floats per array per chunk (16 KiB)
-constexpr int kBulkStages = 3;
-constexpr uint32_t kBulkArrayBytes = kBulkChunk * 4;
-constexpr size_t kBulkSmem = size_t(kBulkStages) * 4 * kBulkArrayBytes + 8 * kBulkStages + 16;
-constexpr unsigned long long kBulkWaitBudgetNs = 1000000000ull;
-__device__ int g_adam_status = 0;
-
-template <bool kDivisorScalars, int kLp>
-__global__ void __launch_bounds__(kBulkThreads) adam_bulk_kernel(AdamArgs a, int64_t nchunks) {
-  extern __shared__ __align__(128) uint8_t ring[];
-  __shared__ int wait_failed;
-  float d1, d2;
-  if (kDivisorScalars) {
-    d1 = a.bc1[0];
-    d2 = a.bc2[0];
-  } else {
-    adam_inverse_corrections(a.h, a.step[0], d1, d2);
-  }
-  using V4 = Pack16<float>;
-  const uint32_t buf0 = sm100::smem_addr(ring);
-  const uint32_t bar0 = buf0 + kBulkStages * 4 * kBulkArrayBytes;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kBulkStages; ++s) sm100::mbar_init(bar0 + 8u * s, 1);
-    sm100::mbar_init_fence();
-    wait_failed = 0;
-  }
-  __syncthreads();
-  auto fetch = [&](int64_t chunk, int slot) {  // thread 0 only
-    const uint32_t bar = bar0 + 8u * slot, buf = buf0 + static_cast<uint32_t>(slot) * 4 * kBulkArrayBytes;
-    const int64_t off = chunk * kBulkChunk;
-    sm100::mbar_expect_tx(bar, 4 * kBulkArrayBytes);
-    sm100::bulk_copy_g2s(buf, a.p + off, kBulkArrayBytes, bar);
-    sm100::bulk_copy_g2s(buf + kBulkArrayBytes, a.g + off, kBulkArrayBytes, bar);
-    sm100::bulk_copy_g2s(buf + 2 * kBulkArrayBytes, a.m + off, kBulkArrayBytes, bar);
-    sm100::bulk_copy_g2s(buf + 3 * kBulkArrayBytes, a.v + off, kBulkArrayBytes, bar);
-  };
-  if (threadIdx.x == 0)
-    for (int s = 0; s < kBulkStages; ++s) {
-      const int64_t c = blockIdx.x + static_cast<int64_t>(s) * gridDim.x;
-      if (c < nchunks) fetch(c, s);
-    }
-  int slot = 0;
-  uint32_t parity = 0;
-  for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
-    if (!sm100::mbar_wait_bounded(bar0 + 8u * slot, parity, kBulkWaitBudgetNs)) wait_failed = 1;
-    const V4* sp = reinterpret_cast<const V4*>(ring + static_cast<size_t>(slot) * 4 * kBulkArrayBytes);
-    V4 p[kBulkPackets], g[kBulkPackets], m[kBulkPackets], v[kBulkPackets];
-#pragma unroll
-    for (int u = 0; u < kBulkPackets; ++u) {
-      const int j = threadIdx.x + u * kBulkThreads;
-      p[u] = sp[j];
-      g[u] = sp[kBulkChunk / 4 + j];
-      m[u] = sp[2 * (kBulkChunk / 4) + j];
-      v[u] = sp[3 * (kBulkChunk / 4) + j];
-    }
-    __syncthreads();  // every thread holds its packets: the slot may be refilled; the flag is seen by all
-    if (wait_failed) {
-      if (threadIdx.x == 0) atomicExch(&g_adam_status, 1);
-      break;
-    }
-    if (threadIdx.x == 0) {
-      const int64_t ahead = c + static_cast<int64_t>(kBulkStages) * gridDim.x;
-      if (ahead < nchunks) {
-        sm100::fence_generic_to_async_smem();
-        fetch(ahead, slot);
-      }
-    }
-    const int64_t base = c * (kBulkChunk / 4);
-#pragma unroll
-    for (int u = 0; u < kBulkPackets; ++u) {
-      const int64_t j = base + threadIdx.x + u * kBulkThreads;
-      V4 po, mo, vo;
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        adam_one<kDivisorScalars>(p[u].v[e], g[u].v[e], m[u].v[e], v[u].v[e], a.h, d1, d2, po.v[e], mo.v[e], vo.v[e]);
-      st_stream(reinterpret_cast<V4*>(a.m_out) + j, mo);
-      st_stream(reinterpret_cast<V4*>(a.v_out) + j, vo);
-      st_stream(reinterpret_cast<V4*>(a.p_out) + j, po);
-      if (kLp) store_lp_x4<kLp>(a.p_lp, j, po);
-    }
-    if (++slot == kBulkStages) {
-      slot = 0;
-      parity ^= 1u;
-    }
-  }
-}
+// ---- grid of the streaming Adam kernels ----------------------------------------------------------------------------
+// Every thread takes two 16-byte packets per array and the grid is as large as the array needs, up to kAdamBlocksPerSm
+// blocks per SM: far more blocks than an SM holds at once. Measured on 2^28 elements (7.5 GB moved per launch), GB/s by
+// blocks of 256 threads per SM: 4 (all resident, a long grid-stride loop each) 5983, 8 6171, 16 6321, 32 6421, 64 6522,
+// 128 6615, 256 6761, 512 6857, 768 6919, 1024 (no loop left) 6911; a plain copy-like probe with the same four reads and
+// three writes follows the same curve (6473 at 32, 6920 at 1024). A kernel that kept a ring of 16 KiB bulk copies per SM
+// in flight instead (one persistent block per SM) reached 6277 and was dropped.
+constexpr int kAdamThreads = 256;
+constexpr int kAdamBlocksPerSm = kStreamBlocksPerSm;
 
 template <bool kDiv, int kLp>
 Status launch_adam(AdamArgs a, cudaStream_t stream) {
@@ -229,37 +145,17 @@ Status launch_adam(AdamArgs a, cudaStream_t stream) {
   bool vec_ok = true;
   for (const void* q : ptrs) vec_ok = vec_ok && aligned_to(q, 16);
   if (kLp) vec_ok = vec_ok && aligned_to(a.p_lp, 8);
-  // Whole chunks of a large, aligned array go through the bulk-copy kernel; the rest (and small or unaligned
-  // arrays) through the per-thread-load kernel below.
-  const int64_t nchunks = vec_ok ? a.n / kBulkChunk : 0;
-  if (nchunks >= 2 * static_cast<int64_t>(sm_count())) {
-    static PerDeviceOnce smem_opt_in;  // function attributes are per device
-    const bool attr_ok = smem_opt_in.run([] {
-      return cudaFuncSetAttribute(adam_bulk_kernel<kDiv, kLp>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  static_cast<int>(kBulkSmem)) == cudaSuccess;
-    });
-    if (attr_ok) {
-      const int per_sm = static_cast<int>((227 * 1024) / (kBulkSmem + 1024));
-      const int grid = streaming_grid(nchunks, 1, per_sm);
-      cudaGetLastError();
-      adam_bulk_kernel<kDiv, kLp><<<grid, kBulkThreads, kBulkSmem, stream>>>(a, nchunks);
-      if (launch_status() != Status::Ok) return Status::Internal;
-      const int64_t done = nchunks * kBulkChunk;
-      if (done == a.n) return Status::Ok;
-      a.p += done; a.g += done; a.m += done; a.v += done;
-      a.p_out += done; a.m_out += done; a.v_out += done;
-      if (kLp) a.p_lp = static_cast<uint8_t*>(a.p_lp) + done * 2;
-      a.n -= done;
-    } else {
-      cudaGetLastError();
-    }
-  }
+  // AICF_ADAM_GRID=n (tuning, read once per process): blocks per SM instead of kAdamBlocksPerSm
+  static const int blocks_per_sm = [] {
+    const char* e = std::getenv("AICF_ADAM_GRID");
+    const int v = e ? std::atoi(e) : 0;
+    return v >= 1 && v <= 1024 ? v : kAdamBlocksPerSm;
+  }();
   a.nvec = vec_ok ? (a.n >> 2) : 0;
-  constexpr int kThreads = 256;
   const int64_t items = vec_ok ? (a.nvec / 2 + 1) : a.n;
-  const int grid = streaming_grid(items, kThreads, 4);  // 64 regs x 256 threads: 4 blocks resident per SM
+  const int grid = streaming_grid(items, kAdamThreads, blocks_per_sm);
   cudaGetLastError();
-  adam_kernel<kDiv, kLp><<<grid, kThreads, 0, stream>>>(a);
+  adam_kernel<kDiv, kLp><<<grid, kAdamThreads, 0, stream>>>(a);
   return launch_status();
 }
 
@@ -352,10 +248,12 @@ Status adam_v1_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, con
 // (ops/adam_step/launcher.cu:188-243); a plan is free to batch them: a model's biases and small matrices are
 // launch-bound on their own and cannot fill the machine, and ten tails of ten grids add up.
 //
-// The grid walks one list of 16 KiB chunks over all tensors with the bulk-copy ring of adam_bulk_kernel; what is left
-// of each tensor past its whole chunks (and tensors smaller than a chunk) is finished by one block per tensor with
-// per-thread loads.
+// The grid walks one list of 8 KiB chunks over all tensors (a block per chunk: two packets per thread and array, the
+// shape of adam_kernel, and as many blocks as there are chunks up to kAdamBlocksPerSm per SM); what is left of each
+// tensor past its whole chunks (and tensors smaller than a chunk) is finished by one block per tensor.
 constexpr int kMultiMax = 16;
+constexpr int kMultiPackets = 2;                                  // 16-byte packets per thread per array per chunk
+constexpr int kMultiChunk = kAdamThreads * kMultiPackets * 4;     // floats per array per chunk
 struct AdamMultiArgs {
   float* p[kMultiMax];
   const float* g[kMultiMax];
@@ -380,88 +278,47 @@ __device__ __forceinline__ void adam_multi_store(const AdamMultiArgs& a, int t, 
   if (a.lp_kind[t] == 2) store_lp_x4<2>(a.lp[t], packet, po);
 }
 
-__global__ void __launch_bounds__(kBulkThreads) adam_multi_kernel(const AdamMultiArgs a) {
-  extern __shared__ __align__(128) uint8_t ring[];
-  __shared__ int wait_failed;
+__global__ void __launch_bounds__(kAdamThreads) adam_multi_kernel(const AdamMultiArgs a) {
   float d1, d2;
   adam_inverse_corrections(a.h, a.step[0], d1, d2);
   using V4 = Pack16<float>;
   const int64_t nchunks = a.chunk_begin[a.count];
-  const uint32_t buf0 = sm100::smem_addr(ring);
-  const uint32_t bar0 = buf0 + kBulkStages * 4 * kBulkArrayBytes;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kBulkStages; ++s) sm100::mbar_init(bar0 + 8u * s, 1);
-    sm100::mbar_init_fence();
-    wait_failed = 0;
-  }
-  __syncthreads();
   auto tensor_of = [&](int64_t chunk) {  // the tensor whose chunk range holds `chunk` (at most kMultiMax steps)
     int t = 0;
     while (t + 1 < a.count && chunk >= a.chunk_begin[t + 1]) ++t;
     return t;
   };
-  auto fetch = [&](int64_t chunk, int slot) {  // thread 0 only
-    const int t = tensor_of(chunk);
-    const int64_t off = (chunk - a.chunk_begin[t]) * kBulkChunk;
-    const uint32_t bar = bar0 + 8u * slot, buf = buf0 + static_cast<uint32_t>(slot) * 4 * kBulkArrayBytes;
-    sm100::mbar_expect_tx(bar, 4 * kBulkArrayBytes);
-    sm100::bulk_copy_g2s(buf, a.p[t] + off, kBulkArrayBytes, bar);
-    sm100::bulk_copy_g2s(buf + kBulkArrayBytes, a.g[t] + off, kBulkArrayBytes, bar);
-    sm100::bulk_copy_g2s(buf + 2 * kBulkArrayBytes, a.m[t] + off, kBulkArrayBytes, bar);
-    sm100::bulk_copy_g2s(buf + 3 * kBulkArrayBytes, a.v[t] + off, kBulkArrayBytes, bar);
-  };
-  if (threadIdx.x == 0)
-    for (int s = 0; s < kBulkStages; ++s) {
-      const int64_t c = blockIdx.x + static_cast<int64_t>(s) * gridDim.x;
-      if (c < nchunks) fetch(c, s);
-    }
-  int slot = 0;
-  uint32_t parity = 0;
   for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
-    if (!sm100::mbar_wait_bounded(bar0 + 8u * slot, parity, kBulkWaitBudgetNs)) wait_failed = 1;
-    const V4* sp = reinterpret_cast<const V4*>(ring + static_cast<size_t>(slot) * 4 * kBulkArrayBytes);
-    V4 p[kBulkPackets], g[kBulkPackets], m[kBulkPackets], v[kBulkPackets];
-#pragma unroll
-    for (int u = 0; u < kBulkPackets; ++u) {
-      const int j = threadIdx.x + u * kBulkThreads;
-      p[u] = sp[j];
-      g[u] = sp[kBulkChunk / 4 + j];
-      m[u] = sp[2 * (kBulkChunk / 4) + j];
-      v[u] = sp[3 * (kBulkChunk / 4) + j];
-    }
-    __syncthreads();  // every thread holds its packets: the slot may be refilled; the flag is seen by all
-    if (wait_failed) {
-      if (threadIdx.x == 0) atomicExch(&g_adam_status, 1);
-      break;
-    }
-    if (threadIdx.x == 0) {
-      const int64_t ahead = c + static_cast<int64_t>(kBulkStages) * gridDim.x;
-      if (ahead < nchunks) {
-        sm100::fence_generic_to_async_smem();
-        fetch(ahead, slot);
-      }
-    }
     const int t = tensor_of(c);
-    const int64_t base = (c - a.chunk_begin[t]) * (kBulkChunk / 4);
+    const int64_t base = (c - a.chunk_begin[t]) * (kMultiChunk / 4) + threadIdx.x;
+    const V4* P = reinterpret_cast<const V4*>(a.p[t]);
+    const V4* G = reinterpret_cast<const V4*>(a.g[t]);
+    const V4* M = reinterpret_cast<const V4*>(a.m[t]);
+    const V4* V = reinterpret_cast<const V4*>(a.v[t]);
+    V4 p[kMultiPackets], g[kMultiPackets], m[kMultiPackets], v[kMultiPackets];
 #pragma unroll
-    for (int u = 0; u < kBulkPackets; ++u) {
+    for (int u = 0; u < kMultiPackets; ++u) {
+      const int64_t j = base + u * kAdamThreads;
+      p[u] = ld_stream(P + j);
+      g[u] = ld_stream(G + j);
+      m[u] = ld_stream(M + j);
+      v[u] = ld_stream(V + j);
+    }
+#pragma unroll
+    for (int u = 0; u < kMultiPackets; ++u) {
       V4 po, mo, vo;
 #pragma unroll
       for (int e = 0; e < 4; ++e)
         adam_one<false>(p[u].v[e], g[u].v[e], m[u].v[e], v[u].v[e], a.h, d1, d2, po.v[e], mo.v[e], vo.v[e]);
-      adam_multi_store(a, t, base + threadIdx.x + u * kBulkThreads, po, mo, vo);
-    }
-    if (++slot == kBulkStages) {
-      slot = 0;
-      parity ^= 1u;
+      adam_multi_store(a, t, base + u * kAdamThreads, po, mo, vo);
     }
   }
   // what the whole chunks leave over, one block per tensor
   for (int t = blockIdx.x; t < a.count; t += gridDim.x) {
-    const int64_t done = (a.chunk_begin[t + 1] - a.chunk_begin[t]) * kBulkChunk;
+    const int64_t done = (a.chunk_begin[t + 1] - a.chunk_begin[t]) * kMultiChunk;
     const int64_t left = a.n[t] - done;
     const int64_t pk0 = done >> 2, pk1 = pk0 + (left >> 2);
-    for (int64_t j = pk0 + threadIdx.x; j < pk1; j += kBulkThreads) {
+    for (int64_t j = pk0 + threadIdx.x; j < pk1; j += kAdamThreads) {
       const V4 p = ld_stream(reinterpret_cast<const V4*>(a.p[t]) + j), g = ld_stream(reinterpret_cast<const V4*>(a.g[t]) + j),
                m = ld_stream(reinterpret_cast<const V4*>(a.m[t]) + j), v = ld_stream(reinterpret_cast<const V4*>(a.v[t]) + j);
       V4 po, mo, vo;
@@ -469,7 +326,7 @@ __global__ void __launch_bounds__(kBulkThreads) adam_multi_kernel(const AdamMult
       for (int e = 0; e < 4; ++e) adam_one<false>(p.v[e], g.v[e], m.v[e], v.v[e], a.h, d1, d2, po.v[e], mo.v[e], vo.v[e]);
       adam_multi_store(a, t, j, po, mo, vo);
     }
-    for (int64_t k = (pk1 << 2) + threadIdx.x; k < a.n[t]; k += kBulkThreads) {
+    for (int64_t k = (pk1 << 2) + threadIdx.x; k < a.n[t]; k += kAdamThreads) {
       float po, mo, vo;
       adam_one<false>(a.p[t][k], a.g[t][k], a.m[t][k], a.v[t][k], a.h, d1, d2, po, mo, vo);
       a.m[t][k] = mo;
@@ -542,7 +399,7 @@ Status adam_multi_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, 
     a.m[t] = static_cast<float*>(in[4 * t + 2].data);
     a.v[t] = static_cast<float*>(in[4 * t + 3].data);
     a.n[t] = numel_raw(in[4 * t]);
-    a.chunk_begin[t + 1] = a.chunk_begin[t] + a.n[t] / kBulkChunk;
+    a.chunk_begin[t + 1] = a.chunk_begin[t] + a.n[t] / kMultiChunk;
     o += 3;
     if ((at.lp_mask >> t) & 1u) {
       a.lp[t] = out[o].data;
@@ -550,19 +407,10 @@ Status adam_multi_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, 
       ++o;
     }
   }
-  static PerDeviceOnce smem_opt_in;
-  if (!smem_opt_in.run([] {
-        return cudaFuncSetAttribute(adam_multi_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(kBulkSmem)) == cudaSuccess;
-      })) {
-    cudaGetLastError();
-    return Status::Internal;
-  }
-  const int per_sm = static_cast<int>((227 * 1024) / (kBulkSmem + 1024));
   const int64_t work = a.chunk_begin[a.count] > a.count ? a.chunk_begin[a.count] : a.count;
-  const int grid = streaming_grid(work, 1, per_sm);
+  const int grid = streaming_grid(work, 1, kAdamBlocksPerSm);
   cudaGetLastError();
-  adam_multi_kernel<<<grid, kBulkThreads, kBulkSmem, stream>>>(a);
+  adam_multi_kernel<<<grid, kAdamThreads, 0, stream>>>(a);
   return launch_status();
 }
 
@@ -682,7 +530,7 @@ Status sgd_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, const v
   const bool vec = aligned_to(in[0].data, 16) && aligned_to(in[1].data, 16) && aligned_to(out[0].data, 16);
   const int64_t nvec = vec ? n / Pack16<T>::kN : 0;
   cudaGetLastError();
-  sgd_kernel<T><<<streaming_grid(vec ? nvec + 1 : n, 256, 8), 256, 0, stream>>>(
+  sgd_kernel<T><<<streaming_grid(vec ? nvec + 1 : n, 256, kStreamBlocksPerSm), 256, 0, stream>>>(
       static_cast<const T*>(in[0].data), static_cast<const T*>(in[1].data), static_cast<T*>(out[0].data), n, nvec, lr);
   return launch_status();
 }
@@ -703,18 +551,7 @@ KernelVariant make(const char* name, uint32_t schema_gate,
 }  // namespace
 
 // Reads (optionally clears) the status word of the bulk-copy Adam kernel's bounded waits. Synchronises the device.
-int adam_pipeline_status(bool clear) {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_adam_status, sizeof(int)) != cudaSuccess) {
-    cudaGetLastError();
-    return -1;
-  }
-  if (clear && v != 0) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(g_adam_status, &zero, sizeof(int));
-  }
-  return v;
-}
+int adam_pipeline_status(bool) { return 0; }  // the Adam kernels have no device-side waits (they had, with a bulk-copy ring)
 
 KernelVariant make_adam_step_f32_variant() { return make("adam_step_f32_sm100", schema::kAdam, adam_v0_launch, adam_v0_supported); }
 KernelVariant make_adam_step_f32_fused_variant() { return make("adam_step_f32_fused_sm100", schema::kAdam, adam_v1_launch, adam_v1_supported); }

@@ -7,6 +7,7 @@
 // gives a column to a whole block and reads it with stride N). Rows are split over gridDim.y so the
 // grid fills the SMs; with more than one split the per-split partial sums go to a scratch buffer
 // [splits, N] (fp32) and a second kernel adds them in split order.
+#include <cstdlib>
 #include <mutex>
 #include <string>
 
@@ -275,7 +276,13 @@ Status rowreduce_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, c
   int64_t M = 0, N = 0;
   rows_cols_any(in[0], &M, &N);
   const int vec = aligned_to(in[0].data, 16) && (N % Pack16<T>::kN == 0);
-  const int grid = streaming_grid(M, 8, 8);  // 8 warps (rows) per block
+  // AICF_ROWREDUCE_GRID=n (tuning, read once per process): blocks per SM
+  static const int per_sm = [] {
+    const char* e = std::getenv("AICF_ROWREDUCE_GRID");
+    const int v = e ? std::atoi(e) : 0;
+    return v >= 1 && v <= 4096 ? v : kStreamBlocksPerSm;
+  }();
+  const int grid = streaming_grid(M, 8, per_sm);  // 8 warps (rows) per block
   cudaGetLastError();
   rowreduce_kernel<T, kOp><<<grid, 256, 0, stream>>>(static_cast<const T*>(in[0].data),
                                                     static_cast<float*>(out[0].data), M, N, vec);

@@ -192,7 +192,7 @@ int row_blocks_per_sm(K kernel, int threads, size_t smem) {
     if (e == nullptr || e[0] == 0) return 0;
     if (e[0] == 'o') return -1;
     const int v = std::atoi(e);
-    return v < 1 ? 0 : (v > 32 ? 32 : v);
+    return v < 1 ? 0 : (v > 4096 ? 4096 : v);
   }();
   if (forced > 0) return forced;
   if (forced == 0) return row_pipe_blocks_per_sm(threads, smem);

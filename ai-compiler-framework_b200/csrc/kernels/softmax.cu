@@ -178,6 +178,66 @@ __global__ void __launch_bounds__(1024) softmax_regs_kernel(const T* __restrict_
   }
 }
 
+// One row per block, straight from global memory into registers: no staging buffer, no barrier object, nothing that
+// outlives the row. The grid has a block per row (grid-stride past the launch limit), so an SM always has several
+// rows at different stages and the hardware's block scheduler does the load balancing.
+template <typename T, int kPackets, bool kFull>
+__global__ void __launch_bounds__(1024) softmax_direct_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M,
+                                                             int64_t N) {
+  using PK = Pack16<T>;
+  constexpr int kN = PK::kN;
+  __shared__ float red[2][kMaxWarps + 1];
+  using Idx = typename RowIdx<T>::type;
+  const Idx np = static_cast<Idx>(N / kN);
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const PK* xr = reinterpret_cast<const PK*>(x + row * N);
+    PK* yr = reinterpret_cast<PK*>(y + row * N);
+    PK raw[kPackets];
+#pragma unroll
+    for (int q = 0; q < kPackets; ++q) {
+      const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
+      if (kFull || pi < np) raw[q] = ld_stream(xr + pi);
+    }
+    float f[kPackets][kN];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int q = 0; q < kPackets; ++q) {
+      const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
+      if (kFull || pi < np) {
+        unpack16(raw[q], f[q]);
+#pragma unroll
+        for (int e = 0; e < kN; ++e) mx = fmaxf(mx, f[q][e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < kN; ++e) f[q][e] = -INFINITY;
+      }
+    }
+    mx = block_reduce_2b<true>(mx, red[0]);
+    float sum = 0.0f;
+#pragma unroll
+    for (int q = 0; q < kPackets; ++q)
+#pragma unroll
+      for (int e = 0; e < kN; ++e) {
+        f[q][e] = exp_shifted(f[q][e], mx);
+        sum += f[q][e];
+      }
+    sum = block_reduce_2b<false>(sum, red[1]);
+    const float inv = 1.0f / sum;
+#pragma unroll
+    for (int q = 0; q < kPackets; ++q) {
+      const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
+      if (kFull || pi < np) {
+        PK o;
+        float r[kN];
+#pragma unroll
+        for (int e = 0; e < kN; ++e) r[e] = f[q][e] * inv;
+        pack16(o, r);
+        st_stream(yr + pi, o);
+      }
+    }
+  }
+}
+
 // Fallback: any N, any alignment; reads the row three times.
 template <typename T>
 __global__ void __launch_bounds__(256) softmax_multipass_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M,
@@ -211,6 +271,34 @@ Status softmax_run(const T* x, T* y, int64_t M, int64_t N, cudaStream_t stream) 
   }
   bool ok_attr = true;
   const bool full = use_full_rows(N / kN == static_cast<int64_t>(c.threads) * c.packets, sizeof(T));
+  // Rows that small blocks (up to 128 threads) hold at four packets per thread go one row per block, straight into
+  // registers, when the row fills those packets exactly (1536 columns of bf16, three packets of four used: 5422 direct,
+  // 5934 pipelined); longer rows keep the persistent blocks with the prefetched row buffer, shorter ones too. GB/s, direct
+  // against pipelined: f32 1024 columns 6873 / 6142, 2048 6741 / 6483, 4096 (256 threads) 6471 / 6624, 8192 5880 /
+  // 6405, 256 5636 / 6058; bf16 1024 6540 / 5584, 2048 6496 / 6275, 4096 (128 threads) 6522 / 6475, 8192 6041 / 6227.
+  // AICF_SOFTMAX_DIRECT=0|1 (tuning, read once per process) forces one or the other.
+  static const int direct_override = [] {
+    const char* e = std::getenv("AICF_SOFTMAX_DIRECT");
+    return (e == nullptr || e[0] == 0) ? -1 : (e[0] == '0' ? 0 : 1);
+  }();
+  const bool exact_fit = N / kN == static_cast<int64_t>(c.threads) * c.packets;
+  const bool direct = direct_override >= 0 ? direct_override != 0 : (c.threads <= 128 && c.packets >= 4 && exact_fit);
+  if (direct) {
+    const int grid = streaming_grid(M, 1, kStreamBlocksPerSm);
+#define AICF_SM_DIRECT(PK, FULL) softmax_direct_kernel<T, PK, FULL><<<grid, c.threads, 0, stream>>>(x, y, M, N)
+#define AICF_SM_DIRECT_F(PK)            \
+  if (full) { AICF_SM_DIRECT(PK, true); } \
+  else { AICF_SM_DIRECT(PK, false); }
+    switch (c.packets) {
+      case 1: AICF_SM_DIRECT_F(1); break;
+      case 2: AICF_SM_DIRECT_F(2); break;
+      case 4: AICF_SM_DIRECT_F(4); break;
+      default: AICF_SM_DIRECT_F(kMaxPk); break;
+    }
+#undef AICF_SM_DIRECT_F
+#undef AICF_SM_DIRECT
+    return launch_status();
+  }
   const size_t smem_launch = row_smem_capped_residency(smem, c.threads);  // the grid is still sized from `smem`
 #define AICF_SM_LAUNCH_F(PK, FULL)                                                                                 \
   if ((ok_attr = allow_smem(softmax_regs_kernel<T, PK, FULL>, smem_launch)))                                       \

@@ -972,7 +972,7 @@ def main():
     ap.add_argument("--reduce-kind", default="sum")
     ap.add_argument("--transb", action="store_true")
     ap.add_argument("--probe-in-flight", type=int, default=0, help="stream_mix: 16-byte packets per array in flight per thread (1, 2, 4)")
-    ap.add_argument("--probe-blocks", type=int, default=0, help="stream_mix: 256-thread blocks per SM (1-32)")
+    ap.add_argument("--probe-blocks", type=int, default=0, help="stream_mix: 256-thread blocks per SM (1-1024)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed NumPy baseline")
     ap.add_argument("--no-check", action="store_true", help="skip the oracle comparison of read-back samples (never timed)")
     ap.add_argument("--no-kernels", action="store_true", help="N = 1 MLP line without the single-kernel measurements")

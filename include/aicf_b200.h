@@ -168,7 +168,7 @@ int aicf_b200_device_pci_bus_id(int device, char* out, int capacity);
  * bytes_each bytes (16-byte aligned, multiple of 16) with 16-byte evict-first accesses - the bandwidth ceiling of this
  * device for a kernel with that mix of input and output streams (fused Adam: 4 + 3), which a plain copy's rate
  * overstates. packets_in_flight (1, 2 or 4; 0 = 2) is the number of 16-byte packets per array each thread has in
- * flight, blocks_per_sm (1-32; 0 = 8) the number of 256-thread blocks per SM: the ceiling is the best rate over
+ * flight, blocks_per_sm (1-1024; 0 = 8) the number of 256-thread blocks per SM: the ceiling is the best rate over
  * those choices. No counterpart in the reference. */
 int aicf_b200_stream_probe(int reads, int writes, const void* const* inputs, void* const* outputs, size_t bytes_each,
                            int packets_in_flight, int blocks_per_sm, aicf_stream stream);

@@ -103,8 +103,15 @@ struct RowCfg {
 // f32 cross-entropy 0.74 -> 0.91; on [262144,256] f32 softmax 0.51 -> 0.92.
 inline RowCfg pick_row_cfg(int64_t n_packets, int max_packets) {
   RowCfg c;
+  // AICF_ROW_PACKETS=n (tuning, read once per process): packets a thread may hold before the block grows (default 4)
+  static const int per_thread = [] {
+    const char* e = std::getenv("AICF_ROW_PACKETS");
+    const int v = e ? std::atoi(e) : 0;
+    return (v == 1 || v == 2 || v == 4 || v == 8) ? v : 4;
+  }();
+  const int grow_at = per_thread < max_packets ? per_thread : max_packets;
   int threads = 32;
-  while (threads < 1024 && static_cast<int64_t>(threads) * 4 < n_packets) threads *= 2;
+  while (threads < 1024 && static_cast<int64_t>(threads) * grow_at < n_packets) threads *= 2;
   const int64_t per = (n_packets + threads - 1) / threads;
   c.threads = threads;
   c.packets = per <= 1 ? 1 : per <= 2 ? 2 : per <= 4 ? 4 : per <= 8 ? 8 : 0;

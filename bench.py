@@ -936,9 +936,10 @@ KERNEL_SUITE = [("gemm_8192_bf16", "gemm", dict(size=8192)), ("gemm_4096_bf16", 
                 ("reduce_max_f32", "reduce", dict(dtype="f32", reduce_kind="max")),
                 ("reduce_mean_bf16", "reduce", dict(dtype="bf16", reduce_kind="mean")), ("adam_f32_2p28", "adam", {}),
                 # measured ceilings for the stream mixes above: 4 arrays read + 3 written (Adam), 1 + 1 (softmax, CE)
-                # (launch shapes that measured best in a sweep of 1 / 2 / 4 packets in flight x 4 / 8 / 16 / 32 blocks per SM)
-                ("ceiling_4_reads_3_writes", "stream_mix", dict(rows=4, cols=3, probe=(1, 32))),
-                ("ceiling_1_read_1_write", "stream_mix", dict(rows=1, cols=1, probe=(4, 32)))]
+                # (launch shapes that measured best in a sweep of 1 / 2 / 4 packets in flight x 4 ... 1024 blocks per SM:
+                # the rate keeps rising with the grid until every thread has one or two packets per array)
+                ("ceiling_4_reads_3_writes", "stream_mix", dict(rows=4, cols=3, probe=(1, 1024))),
+                ("ceiling_1_read_1_write", "stream_mix", dict(rows=1, cols=1, probe=(2, 1024)))]
 
 
 def run_kernel_suite(args):

@@ -476,6 +476,159 @@ __global__ void __launch_bounds__(1024)
   }
 }
 
+// ---- very long rows: one row per thread-block cluster ----------------------------------------------------------------
+// A row that no single block can hold in registers is split over the 2, 4 or 8 CTAs of a cluster: each CTA keeps a
+// contiguous slice of the row in registers, loaded straight from global memory, and the CTAs exchange the two per-row
+// scalars (maximum, then sum and arg-max candidate) through each other's shared memory between cluster barriers. The row
+// is still read once and written once. Partial sums are added in rank order, so the result does not depend on timing.
+constexpr int kClusterThreads = 256;
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_index() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_count() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+  return r;
+}
+// Every thread of every CTA of the cluster; orders shared-memory writes before it against peers' reads after it.
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The 4-byte word at `local`'s offset in the shared memory of CTA `rank` of this cluster.
+template <typename V>
+__device__ __forceinline__ V ld_peer_shared(const V* local, uint32_t rank) {
+  static_assert(sizeof(V) == 4, "4-byte words only");
+  const uint32_t mine = static_cast<uint32_t>(__cvta_generic_to_shared(local));
+  uint32_t remote, bits;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(mine), "r"(rank));
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(bits) : "r"(remote) : "memory");
+  V v;
+  memcpy(&v, &bits, 4);
+  return v;
+}
+
+template <typename T, int kPackets>
+__global__ void __launch_bounds__(kClusterThreads, 4)  // four CTAs per SM: 64 registers
+    softmax_ce_cluster_kernel(const T* __restrict__ z, const int32_t* __restrict__ labels, T* __restrict__ dz,
+                              float* __restrict__ loss_row, int32_t* __restrict__ argmax_out, int64_t B, int64_t C,
+                              float scale, int slice /* packets per CTA */) {
+  using PK = Pack16<T>;
+  constexpr int kN = PK::kN;
+  __shared__ float red[2][kMaxWarps + 1];
+  __shared__ int redi[kMaxWarps + 1];
+  __shared__ float x_max, x_sum;  // this CTA's share of the row's maximum and sum, read by its peers
+  __shared__ int x_cand;          // and its lowest column holding the row maximum
+  const uint32_t rank = cluster_rank(), nranks = cluster_size();
+  const int np = static_cast<int>(C / kN);
+  const int p0 = static_cast<int>(rank) * slice;               // first packet of this CTA's slice
+  const int pn = np - p0 < slice ? (np - p0 > 0 ? np - p0 : 0) : slice;  // packets in it
+  for (int64_t row = cluster_index(); row < B; row += cluster_count()) {
+    const PK* zr = reinterpret_cast<const PK*>(z + row * C) + p0;
+    PK* dr = reinterpret_cast<PK*>(dz + row * C) + p0;
+    const int label = labels[row];
+    const bool label_ok = label >= 0 && label < C;
+    // the one thread of the cluster whose packets hold column `label`: it patches the one-hot term and writes the loss
+    const int lp = label_ok ? label / kN - p0 : -1;
+    const bool owner = lp >= 0 && lp < pn && lp % kClusterThreads == static_cast<int>(threadIdx.x);
+    const float z_label = owner ? Cvt<T>::to_f(z[row * C + label]) : 0.0f;
+    PK raw[kPackets];
+#pragma unroll
+    for (int q = 0; q < kPackets; ++q) {
+      const int pi = static_cast<int>(threadIdx.x) + q * kClusterThreads;
+      if (pi < pn) raw[q] = ld_stream(zr + pi);
+    }
+    float f[kPackets][kN];
+    float tmax = -INFINITY;
+#pragma unroll
+    for (int q = 0; q < kPackets; ++q) {
+      const int pi = static_cast<int>(threadIdx.x) + q * kClusterThreads;
+      if (pi < pn) {
+        unpack16(raw[q], f[q]);
+#pragma unroll
+        for (int e = 0; e < kN; ++e) tmax = fmaxf(tmax, f[q][e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < kN; ++e) f[q][e] = -INFINITY;
+      }
+    }
+    const float local_max = block_reduce_2b<true>(tmax, red[0]);
+    if (threadIdx.x == 0) x_max = local_max;
+    cluster_barrier();
+    float mx = -INFINITY;
+    for (uint32_t r = 0; r < nranks; ++r) mx = fmaxf(mx, ld_peer_shared(&x_max, r));
+    int cand = 0x7fffffff;
+    if (tmax == mx) {
+#pragma unroll
+      for (int q = kPackets - 1; q >= 0; --q) {
+        const int pi = static_cast<int>(threadIdx.x) + q * kClusterThreads;
+        if (pi < pn) {
+#pragma unroll
+          for (int e = kN - 1; e >= 0; --e)
+            if (f[q][e] == mx) cand = (p0 + pi) * kN + e;  // descending order: the lowest column stays
+        }
+      }
+    }
+    float sum = 0.0f;
+#pragma unroll
+    for (int q = 0; q < kPackets; ++q)
+#pragma unroll
+      for (int e = 0; e < kN; ++e) {
+        f[q][e] = exp_shifted(f[q][e], mx);  // exp(-inf) == 0 for the padding
+        sum += f[q][e];
+      }
+    const SumMin local = block_sum_min<false>(sum, cand, red[1], redi);
+    if (threadIdx.x == 0) {
+      x_sum = local.sum;
+      x_cand = local.idx;
+    }
+    cluster_barrier();  // every CTA is past its reads of x_max, too: the next row may overwrite it
+    float total = 0.0f;
+    int best = 0x7fffffff;
+    for (uint32_t r = 0; r < nranks; ++r) {
+      total += ld_peer_shared(&x_sum, r);
+      const int c = ld_peer_shared(&x_cand, r);
+      best = c < best ? c : best;
+    }
+    const float k = scale / total;
+#pragma unroll
+    for (int q = 0; q < kPackets; ++q) {
+      const int pi = static_cast<int>(threadIdx.x) + q * kClusterThreads;
+      if (pi < pn) {
+        PK o;
+        float r[kN];
+#pragma unroll
+        for (int e = 0; e < kN; ++e) r[e] = f[q][e] * k;
+        pack16(o, r);
+        st_stream(dr + pi, o);
+      }
+    }
+    if (owner) {
+      const float g = exp_shifted(z_label, mx) * k - scale;  // the same bits the loop above produced, minus the one-hot term
+      dz[row * C + label] = Cvt<T>::from_f(g);
+      loss_row[row] = logf(total) + mx - z_label;
+    }
+    if (rank == 0 && threadIdx.x == 0) {
+      if (!label_ok) loss_row[row] = 0.0f;
+      if (argmax_out) argmax_out[row] = best;
+    }
+    // x_sum / x_cand of this row are read before a peer arrives at the next row's first cluster barrier, and they are
+    // next written after that barrier: no third barrier needed inside the loop
+  }
+  cluster_barrier();  // nobody leaves while a peer may still be reading its shared memory
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
     softmax_ce_multipass_kernel(const T* __restrict__ z, const int32_t* __restrict__ labels, T* __restrict__ dz,
@@ -534,6 +687,31 @@ template <DType kDt>
 bool softmax_ce_supported(const TensorDesc* in, int ni, const TensorDesc* out, int no, const void*) {
   return softmax_ce_check<kDt>(in, ni, out, no);
 }
+template <typename T, int kPackets>
+Status launch_ce_cluster(int nranks, int slice, const T* z, const int32_t* lab, T* dz, float* loss, int32_t* am, int64_t B,
+                         int64_t C, float scale, cudaStream_t stream) {
+  const int64_t max_clusters = static_cast<int64_t>(sm_count()) * kStreamBlocksPerSm / nranks;
+  const int64_t clusters = B < max_clusters ? B : max_clusters;
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(nranks);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3(static_cast<unsigned>(clusters * nranks));
+  cfg.blockDim = dim3(kClusterThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaGetLastError();
+  if (cudaLaunchKernelEx(&cfg, softmax_ce_cluster_kernel<T, kPackets>, z, lab, dz, loss, am, B, C, scale, slice) != cudaSuccess) {
+    cudaGetLastError();
+    return Status::Internal;
+  }
+  return launch_status();
+}
+
 template <DType kDt, typename T>
 Status softmax_ce_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, const void* attr, void*, size_t,
                          cudaStream_t stream) {
@@ -552,6 +730,42 @@ Status softmax_ce_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, 
   const size_t smem = row_pipe_smem(C * static_cast<int64_t>(sizeof(T)));
   const RowCfg c = (vec && smem <= kMaxRowPipeSmem) ? pick_row_cfg(C / kN, kMaxPk) : RowCfg{};
   cudaGetLastError();
+  // Rows too long for one block's registers (more than 32768 fp32 columns) go one row per cluster of up to 8 small CTAs
+  // and stay single-pass up to 65536 columns ([4096,65536] f32: 3712 GB/s against 1383 for the three-read fallback).
+  // Where one block can hold the row, the persistent pipelined kernel is faster ([8192,32000] f32: 6318 GB/s against
+  // 4010 as clusters of four: a cluster lives for one row, and its launch, its load latency and its three cluster
+  // barriers are exposed at four resident CTAs per SM). AICF_CE_CLUSTER=0|1 (tuning, read once per process) forces the
+  // choice wherever the row can be split that way.
+  static const int cluster_override = [] {
+    const char* e = std::getenv("AICF_CE_CLUSTER");
+    return (e == nullptr || e[0] == 0) ? -1 : (e[0] == '0' ? 0 : 1);
+  }();
+  const int64_t row_packets = C / kN;
+  if (vec && (cluster_override >= 0 ? cluster_override != 0 : c.packets == 0)) {
+    // AICF_CE_CLUSTER_PACKETS=n (tuning, read once per process): packets a thread may hold before the cluster grows
+    static const int pk_limit = [] {
+      const char* e = std::getenv("AICF_CE_CLUSTER_PACKETS");
+      const int v = e ? std::atoi(e) : 0;
+      return (v == 1 || v == 2 || v == 4 || v == 8) ? v : 0;
+    }();
+    // 64 registers hold 32 fp32 elements per thread, or 16 elements of a 16-bit type next to their packed form
+    constexpr int kClusterMaxPk = sizeof(T) == 4 ? 8 : 2;
+    const int64_t per_cta_max =
+        static_cast<int64_t>(kClusterThreads) * (pk_limit > 0 && pk_limit < kClusterMaxPk ? pk_limit : kClusterMaxPk);
+    int nranks = 2;
+    while (nranks < 8 && (row_packets + nranks - 1) / nranks > per_cta_max) nranks *= 2;
+    const int64_t slice = (row_packets + nranks - 1) / nranks;
+    if (slice <= per_cta_max && row_packets >= nranks) {
+      const int64_t per = (slice + kClusterThreads - 1) / kClusterThreads;
+      const int sl = static_cast<int>(slice);
+      if (per <= 1) return launch_ce_cluster<T, 1>(nranks, sl, z, lab, dz, loss, am, B, C, scale, stream);
+      if (per <= 2) return launch_ce_cluster<T, 2>(nranks, sl, z, lab, dz, loss, am, B, C, scale, stream);
+      if constexpr (sizeof(T) == 4) {
+        if (per <= 4) return launch_ce_cluster<T, 4>(nranks, sl, z, lab, dz, loss, am, B, C, scale, stream);
+        return launch_ce_cluster<T, 8>(nranks, sl, z, lab, dz, loss, am, B, C, scale, stream);
+      }
+    }
+  }
   if (c.packets == 0) {
     softmax_ce_multipass_kernel<T><<<streaming_grid(B, 1, 8), 256, 0, stream>>>(z, lab, dz, loss, am, B, C, scale);
     return launch_status();

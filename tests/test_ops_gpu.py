@@ -84,7 +84,7 @@ def test_adam_fused_step_counter_weight_decay_and_bf16_copy(gpu, n, wd, dec):
     assert np.array_equal(lp.numpy(), f32_to_bf16_bits(P.numpy()))  # bf16 copy is the rounded new parameter
 
 
-def test_adam_v0_large_out_of_place_uses_the_bulk_copy_kernel(gpu):
+def test_adam_v0_large_out_of_place(gpu):
     n = 4096 * 320 + 8
     p, g, m, v = rnd((n,), 1), rnd((n,), 2, 1e-2), rnd((n,), 3, 1e-2), np.abs(rnd((n,), 4, 1e-3))
     bc1, bc2 = 1 - 0.9 ** 3, 1 - 0.999 ** 3
@@ -338,6 +338,31 @@ def test_softmax_ce_ties_and_out_of_range_labels(gpu):
     assert list(A.numpy()) == [5, 63, 0, 0] == list(wa)
     assert_close_f32(host(L), wl, atol=1e-6)
     assert_close_f32(host(D), wd, atol=1e-9)
+
+
+@pytest.mark.parametrize("Cn", [32772, 50000, 65536])
+def test_softmax_ce_rows_beyond_one_block_are_split_over_a_cluster(gpu, Cn):
+    """fp32 rows of more than 32768 columns do not fit one block's registers: up to 65536 columns a cluster of CTAs
+    takes a row, each CTA a slice, and the row is still read once. Ties of the maximum in different slices (the lowest
+    column wins), labels in the first and last slice and out of range, against the oracle."""
+    B = 6
+    z, y = oracle.ce_inputs(B, Cn, seed=5)
+    z[0, :] = 0.0
+    z[0, [Cn - 1, Cn // 2, 7]] = 4.0          # three-way tie across slices
+    z[1, Cn - 1] = 50.0                        # maximum in the last column
+    y[:] = [7, Cn - 1, 0, Cn, -3, Cn // 3]     # rows 3 and 4: out of range
+    D, L, A = Tensor.empty((B, Cn)), Tensor.empty((B,)), Tensor.empty((B,), "i32")
+    by_id("softmax_ce_f32_i32_v0", OpKind.SoftmaxCE, [dev(z), dev(y)], [D, L, A])
+    assert _C.wait_status() == 0
+    wd, wl, wa = oracle.softmax_ce(z, y)
+    assert list(A.numpy()[:2]) == [7, Cn - 1]
+    assert np.array_equal(A.numpy(), wa)
+    assert_close_f32(host(L), wl, rtol=1e-5, atol=1e-6, what="loss rows")
+    assert host(L)[3] == 0.0 and host(L)[4] == 0.0
+    assert_close_f32(host(D), wd, rtol=1e-5, atol=1e-12, what="dlogits")
+    again = Tensor.empty((B, Cn))
+    by_id("softmax_ce_f32_i32_v0", OpKind.SoftmaxCE, [dev(z), dev(y)], [again, L, A])
+    assert np.array_equal(host(again), host(D)), "partial sums are added in rank order"
 
 
 # ------------------------------------------------------------------ multi-tensor Adam (one launch for a whole model)

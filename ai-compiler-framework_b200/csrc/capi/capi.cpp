@@ -374,6 +374,10 @@ int aicf_b200_host_alloc_pinned(void** ptr, size_t bytes) {
   if (!ptr) return fail(Status::InvalidArgument, "host_alloc_pinned: null out pointer");
   return check_cuda(cudaMallocHost(ptr, bytes ? bytes : 1), "cudaMallocHost");
 }
+int aicf_b200_host_alloc_staging(void** ptr, size_t bytes) {
+  if (!ptr) return fail(Status::InvalidArgument, "host_alloc_staging: null out pointer");
+  return check_cuda(cudaHostAlloc(ptr, bytes ? bytes : 1, cudaHostAllocWriteCombined), "cudaHostAlloc(write-combined)");
+}
 int aicf_b200_host_free_pinned(void* ptr) { return check_cuda(cudaFreeHost(ptr), "cudaFreeHost"); }
 int aicf_b200_memcpy_h2d(void* dst, const void* src, size_t bytes, aicf_stream stream) {
   return check_cuda(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, as_stream(stream)), "cudaMemcpyAsync(h2d)");

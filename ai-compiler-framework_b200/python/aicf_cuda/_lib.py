@@ -87,6 +87,7 @@ PROTOTYPES = {
     "aicf_b200_malloc": (_i, [_P(_vp), _sz]),
     "aicf_b200_free": (_i, [_vp]),
     "aicf_b200_host_alloc_pinned": (_i, [_P(_vp), _sz]),
+    "aicf_b200_host_alloc_staging": (_i, [_P(_vp), _sz]),
     "aicf_b200_host_free_pinned": (_i, [_vp]),
     "aicf_b200_memcpy_h2d": (_i, [_vp, _vp, _sz, _u64]),
     "aicf_b200_memcpy_d2h": (_i, [_vp, _vp, _sz, _u64]),

@@ -189,11 +189,16 @@ class Events:
         return float(ms.value)
 
 
-def pinned_array(lib, shape, dtype):
+def pinned_array(lib, shape, dtype, staging=False):
+    """A NumPy view of pinned host memory. staging=True: write-combined memory, for a buffer the host only fills and the
+    device reads (AICF_BENCH_STAGING=0 keeps it cacheable, to compare)."""
     import ctypes as C
     n = int(np.prod(shape)) * np.dtype(dtype).itemsize
     p = C.c_void_p()
-    rc = lib.aicf_b200_host_alloc_pinned(C.byref(p), n)
+    if staging and os.environ.get("AICF_BENCH_STAGING", "1") != "0":
+        rc = lib.aicf_b200_host_alloc_staging(C.byref(p), n)
+    else:
+        rc = lib.aicf_b200_host_alloc_pinned(C.byref(p), n)
     if rc != 0:
         raise RuntimeError("pinned host allocation failed")
     buf = (C.c_uint8 * n).from_address(p.value)
@@ -387,7 +392,7 @@ def run_mlp(args, dist: Dist):
     init_mlp_params(aicf_cuda, plan, dims, seed=4)
 
     # host inputs in pinned memory: rank r owns rows [r*batch, (r+1)*batch) of the one global batch
-    x_host, _ = pinned_array(lib, (batch, dims[0]), np.float32)
+    x_host, _ = pinned_array(lib, (batch, dims[0]), np.float32, staging=True)
     y_host, _ = pinned_array(lib, (batch,), np.int32)
     fill_global_batch_rows(x_host, y_host, rank * batch, gbatch, dims[-1])
     x_dev, y_dev, loss_dev = plan.tensor("x"), plan.tensor("labels"), plan.tensor("loss")

@@ -175,6 +175,10 @@ int aicf_b200_stream_probe(int reads, int writes, const void* const* inputs, voi
 int aicf_b200_malloc(void** ptr, size_t bytes);
 int aicf_b200_free(void* ptr);
 int aicf_b200_host_alloc_pinned(void** ptr, size_t bytes);
+/* Pinned host memory for buffers the host only WRITES and the device reads (the staging buffer of a step's input batch):
+ * write-combined, so device reads of it are not snooped through the CPU caches; host reads of it are very slow. Freed
+ * with aicf_b200_host_free_pinned. What a torch user gets nowhere (torch pins cacheable memory only). */
+int aicf_b200_host_alloc_staging(void** ptr, size_t bytes);
 int aicf_b200_host_free_pinned(void* ptr);
 int aicf_b200_memcpy_h2d(void* dst, const void* src, size_t bytes, aicf_stream stream); /* async on `stream` */
 int aicf_b200_memcpy_d2h(void* dst, const void* src, size_t bytes, aicf_stream stream);

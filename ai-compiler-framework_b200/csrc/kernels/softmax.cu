@@ -368,7 +368,7 @@ Status softmax_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, con
 // Per element the loops only take a maximum, an exponential and a product: the arg-max index is looked up afterwards
 // by the few threads that hold the row maximum and reduced together with the sum, and the one-hot term is patched in
 // by the one thread that owns the label's column.
-template <typename T, int kPackets, bool kLockstep, bool kFull>
+template <typename T, int kPackets, bool kLockstep, bool kFull, bool kEarlyRefill>
 __global__ void __launch_bounds__(1024)
     softmax_ce_regs_kernel(const T* __restrict__ z, const int32_t* __restrict__ labels, T* __restrict__ dz,
                            float* __restrict__ loss_row, int32_t* __restrict__ argmax_out, int64_t B, int64_t C,
@@ -403,6 +403,17 @@ __global__ void __launch_bounds__(1024)
     float z_label = 0.0f;
     if (label_ok && (threadIdx.x == 0 || static_cast<int>(threadIdx.x) == owner))
       z_label = Cvt<T>::to_f(reinterpret_cast<const T*>(row_smem)[label]);
+    // With kEarlyRefill (one block per SM: nobody else keeps the SM's loads going) the row is first only taken out of
+    // shared memory, a barrier of its own follows at once and the next row is requested before any arithmetic, instead
+    // of after the maximum's reduction: the time an SM has no load in flight shrinks from the copy, the maximum and its
+    // two barriers to the copy and one barrier.
+    constexpr bool early = !kLockstep && kEarlyRefill;
+    auto refill = [&]() {  // after a block-wide barrier: every thread holds its packets, a failed wait is seen by all
+      if (threadIdx.x == 0 && row + gridDim.x < B) {
+        sm100::fence_generic_to_async_smem();
+        pipe.fetch(z + (row + gridDim.x) * C, row_bytes);
+      }
+    };
     float f[kPackets][kN];
     float tmax = -INFINITY;
 #pragma unroll
@@ -410,23 +421,34 @@ __global__ void __launch_bounds__(1024)
       const Idx pi = static_cast<Idx>(threadIdx.x) + static_cast<Idx>(q) * static_cast<Idx>(blockDim.x);
       if (kFull || pi < np) {
         unpack16(srow[pi], f[q]);
+        if constexpr (!early) {
 #pragma unroll
-        for (int e = 0; e < kN; ++e) tmax = fmaxf(tmax, f[q][e]);
+          for (int e = 0; e < kN; ++e) tmax = fmaxf(tmax, f[q][e]);
+        }
       } else {
 #pragma unroll
         for (int e = 0; e < kN; ++e) f[q][e] = -INFINITY;
       }
     }
-    // past the barriers of the reduction every thread holds its part of the row (the buffer may be refilled), and a
-    // wait that ran out is seen by all threads
-    const float mx = kLockstep ? block_reduce<true>(tmax, red[0]) : block_reduce_2b<true>(tmax, red[0]);
-    if (wait_failed) {
-      if (threadIdx.x == 0) atomicExch(&g_row_pipeline_status, 1);
-      break;
+    if constexpr (early) {
+      __syncthreads();
+      if (wait_failed) {
+        if (threadIdx.x == 0) atomicExch(&g_row_pipeline_status, 1);
+        break;
+      }
+      refill();
+#pragma unroll
+      for (int q = 0; q < kPackets; ++q)
+#pragma unroll
+        for (int e = 0; e < kN; ++e) tmax = fmaxf(tmax, f[q][e]);  // the padding is -inf
     }
-    if (threadIdx.x == 0 && row + gridDim.x < B) {
-      sm100::fence_generic_to_async_smem();
-      pipe.fetch(z + (row + gridDim.x) * C, row_bytes);
+    const float mx = kLockstep ? block_reduce<true>(tmax, red[0]) : block_reduce_2b<true>(tmax, red[0]);
+    if (!early) {
+      if (wait_failed) {
+        if (threadIdx.x == 0) atomicExch(&g_row_pipeline_status, 1);
+        break;
+      }
+      refill();
     }
     // arg-max: only the (few) threads that hold the row maximum look for its lowest column among their elements;
     // the block-wide minimum of those candidates rides along with the sum reduction below
@@ -780,15 +802,26 @@ Status softmax_ce_launch(const TensorDesc* in, int ni, TensorDesc* out, int no, 
   }();
   const bool full = use_full_rows(C / kN == static_cast<int64_t>(c.threads) * c.packets, sizeof(T));
   const size_t smem_launch = row_smem_capped_residency(smem, c.threads);  // the grid is still sized from `smem`
-#define AICF_CE_LAUNCH_M(PK, LS, FULL)                                                                                     \
-  if ((ok_attr = allow_smem(softmax_ce_regs_kernel<T, PK, LS, FULL>, smem_launch)))                                        \
-    softmax_ce_regs_kernel<T, PK, LS, FULL>                                                                                \
-        <<<streaming_grid(B, 1, row_blocks_per_sm(softmax_ce_regs_kernel<T, PK, LS, FULL>, c.threads, smem)), c.threads, \
-           smem_launch, stream>>>(z, lab, dz, loss, am, B, C, scale)
-#define AICF_CE_LAUNCH(PK)                                  \
-  if (lockstep) { AICF_CE_LAUNCH_M(PK, true, false); }      \
-  else if (full) { AICF_CE_LAUNCH_M(PK, false, true); }     \
-  else { AICF_CE_LAUNCH_M(PK, false, false); }
+  // AICF_CE_EARLY_REFILL=0|1 (tuning, read once per process); default: when an SM holds one block. GB/s without / with:
+  // [8192,32000] f32 (one block per SM) 6322 / 6550; [16384,16384] (two) 5760 / 5560; [16384,8192] 6243 / 6317;
+  // [65536,1024] 6375 / 5975.
+  static const int early_override = [] {
+    const char* e = std::getenv("AICF_CE_EARLY_REFILL");
+    return (e == nullptr || e[0] == 0) ? -1 : (e[0] == '0' ? 0 : 1);
+  }();
+  const int early_refill = early_override >= 0 ? early_override : (row_pipe_blocks_per_sm(c.threads, smem_launch) == 1 ? 1 : 0);
+#define AICF_CE_LAUNCH_M(PK, LS, FULL, EARLY)                                                                              \
+  if ((ok_attr = allow_smem(softmax_ce_regs_kernel<T, PK, LS, FULL, EARLY>, smem_launch)))                                 \
+    softmax_ce_regs_kernel<T, PK, LS, FULL, EARLY>                                                                         \
+        <<<streaming_grid(B, 1, row_blocks_per_sm(softmax_ce_regs_kernel<T, PK, LS, FULL, EARLY>, c.threads, smem)),       \
+           c.threads, smem_launch, stream>>>(z, lab, dz, loss, am, B, C, scale)
+#define AICF_CE_LAUNCH(PK)                                                \
+  if (lockstep) { AICF_CE_LAUNCH_M(PK, true, false, false); }             \
+  else if (early_refill) {                                                \
+    if (full) { AICF_CE_LAUNCH_M(PK, false, true, true); }                \
+    else { AICF_CE_LAUNCH_M(PK, false, false, true); }                    \
+  } else if (full) { AICF_CE_LAUNCH_M(PK, false, true, false); }          \
+  else { AICF_CE_LAUNCH_M(PK, false, false, false); }
   switch (c.packets) {
     case 1: AICF_CE_LAUNCH(1); break;
     case 2: AICF_CE_LAUNCH(2); break;

@@ -84,6 +84,29 @@ def test_softmax_benchmark_shape(gpu, dt):
     assert np.allclose(got[rows[:64]], second, rtol=1e-5 if dt == "f32" else STEP16[dt], atol=1e-7)
 
 
+@pytest.mark.parametrize("M,N,dt", [(8192, 8192, "bf16"), (16384, 3072, "bf16"), (16384, 3072, "f32"), (4096, 16384, "f16"),
+                                    (65536, 1024, "f32"), (65536, 1024, "bf16"), (20000, 2048, "f16")])
+def test_softmax_both_row_kernels_in_steady_state(gpu, M, N, dt):
+    """Rows of 128 threads and fewer that fill their packets exactly go one row per block straight into registers; all
+    others (long rows, ragged rows) go through the persistent blocks with the prefetched row buffer, several rows per
+    block. Both against the oracle on shapes with many more rows than blocks can be resident: every row a probability
+    vector, sampled rows element by element."""
+    x = ROUND[dt](oracle.softmax_inputs(M, N, seed=7))
+    Y = Tensor.empty((M, N), dt)
+    by_id(f"softmax_lastdim_{dt}_v0", OpKind.Softmax, [dev(x, dt)], [Y])
+    assert _C.wait_status() == 0
+    got = host(Y)
+    sums = got.sum(axis=1, dtype=np.float64)
+    assert np.abs(sums - 1).max() <= (1e-5 if dt == "f32" else 3.9e-3 if dt == "bf16" else 5e-4)
+    rows = sample_rows(M, 256)
+    want = oracle.softmax(x[rows])
+    if dt == "f32":
+        assert_close_f32(got[rows], want, rtol=1e-5, atol=1e-10, what="sampled rows")
+        assert np.array_equal(got.argmax(axis=1), x.argmax(axis=1))
+    else:
+        assert np.allclose(got[rows], want, rtol=STEP16[dt], atol=1e-7)
+
+
 # ------------------------------------------------------------------------------------------ softmax cross-entropy
 def _ce_launch(z, y, dt, B, Cn):
     D, L, A = Tensor.empty((B, Cn), dt), Tensor.empty((B,)), Tensor.empty((B,), "i32")

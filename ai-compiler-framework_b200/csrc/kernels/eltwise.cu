@@ -2,7 +2,8 @@
 // grad_zero. All are one-pass HBM-bound kernels built from one template: 16-byte packets with
 // evict-first hints, 64-bit grid-stride indexing (no element-count ceiling; the reference's relu
 // rejects numel > INT_MAX and its relu_bwd silently skips elements past 65535*256), scalar path for
-// the ragged tail or unaligned views.
+// the ragged tail or unaligned views. Grids are as large as the array needs at two packets per thread, up to
+// kStreamBlocksPerSm blocks per SM.
 #include "common.cuh"
 
 namespace aicf::cuda {

@@ -2,8 +2,9 @@
 // bias-correction scalars, SGD.
 //
 // Everything here is HBM-bound streaming work: 128-bit loads/stores with evict-first hints,
-// 64-bit indexing, a grid sized in whole multiples of the SM count and a grid-stride loop, so
-// one launch covers any size (the reference caps its grid at 65535 blocks of scalar accesses).
+// 64-bit indexing, and a grid as large as the array needs at two packets per thread (up to
+// kStreamBlocksPerSm blocks per SM, a grid-stride loop past that), so one launch covers any size
+// (the reference caps its grid at 65535 blocks of scalar accesses).
 #include <cstdlib>
 
 #include "adam_math.cuh"

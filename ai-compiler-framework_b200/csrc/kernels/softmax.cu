@@ -7,8 +7,12 @@
 // row-sized read in flight and the load / reduce / store phases of a block overlap with each other.
 // Row max / sum are warp-shuffle reductions joined through shared memory in a fixed order, hence
 // deterministic.
-// Rows wider than 32768 elements, or rows that are not 16-byte aligned, take a three-read fallback
-// kernel.
+// Two more single-pass forms beside these persistent, pipelined kernels: softmax rows that 128 threads or
+// fewer hold at exactly four packets each go one row per block straight from global memory into
+// registers (softmax_direct_kernel), and fp32 cross-entropy rows too long for one block's registers
+// (32768 to 65536 columns) go one row per thread-block cluster (softmax_ce_cluster_kernel).
+// Everything else (softmax rows wider than 32768 elements, rows that are not 16-byte aligned) takes a
+// three-read fallback kernel.
 #include <cstdlib>
 
 #include "row_pipeline.cuh"

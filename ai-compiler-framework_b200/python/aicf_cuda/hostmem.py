@@ -63,8 +63,9 @@ def device_pci_bus_id(device: int) -> str:
 
 def bind_to_device_node(device: int, *, bus_id: Optional[str] = None, sysfs: Path = SYSFS,
                         setaffinity=None, allowed=None) -> dict:
-    """Restricts the calling process to the CPUs of the NUMA node of `device` (intersected with the CPUs it may already
-    use). Call it before allocating pinned buffers. Returns what it found and did; does nothing, and says why, when the
+    """Restricts the calling thread, and with it the threads it starts afterwards, to the CPUs of the NUMA node of
+    `device` (intersected with the CPUs it may already use; threads that already exist keep their own masks). Call it
+    from the thread that allocates the pinned buffers, before it does so. Returns what it found and did; does nothing, and says why, when the
     host does not expose a node, the node has no CPU the process may use, or AICF_HOST_AFFINITY=0."""
     info = {"device": device, "bus_id": None, "numa_node": None, "cpus": None, "bound": False, "why_not": None}
     if os.environ.get("AICF_HOST_AFFINITY", "1") == "0":
